@@ -1,0 +1,179 @@
+/*
+ * libzipage_b200 — C ABI of the compressed-PagedAttention hot path for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes raw DEVICE pointers, explicit sizes/strides (in ELEMENTS unless the
+ * name says bytes) and a CUDA stream (cudaStream_t passed as void*; NULL = legacy default
+ * stream).  Calls are asynchronous with respect to the host, never synchronise the device, keep
+ * no global mutable state (safe to call from several host threads on different streams) and,
+ * unless stated otherwise, allocate nothing: scratch memory is passed in by the caller and its
+ * size comes from the matching *_workspace_bytes query.
+ *
+ * Return value: ZP_OK (0) or a negative ZP_ERR_* code; zp_last_error() then returns a
+ * thread-local description.  There is no CPU fallback.
+ *
+ * Layouts (the reference's, unchanged):
+ *   K/V cache    [L, P, BS, Hkv, D]   L layers (a chunk), P pages, BS = 256 slots per page
+ *   query cache  [L, C, QCL, Hq, D]   observation window: last QCL queries of each sequence
+ *   score cache  [L, P, BS, Hkv]
+ *   scores/flags [L, B, Hkv, NB, BS]  B sequences of the call, NB = padded table length
+ *   block_table  [B, NB] int32        -1 padding, id >= 0 page, -(id)-2 = last page of the sequence
+ *   target table [B, NT] int32        destination pages of the compaction (NT = budget + 1)
+ * Only the two leading strides of a cache (layer, page) are free; the rest is contiguous.
+ * dtype codes select the cache element type T.
+ */
+#ifndef ZIPAGE_B200_H_
+#define ZIPAGE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ZP_OK 0
+#define ZP_ERR_INVALID_ARGUMENT (-1)
+#define ZP_ERR_CUDA (-2)
+#define ZP_ERR_UNSUPPORTED (-3)
+#define ZP_ERR_WORKSPACE (-4)
+
+#define ZP_DTYPE_BF16 0
+#define ZP_DTYPE_F32 1
+#define ZP_DTYPE_F16 2
+
+/* kernel families a call may use: ZP_IMPL_AUTO picks tcgen05 kernels for 16-bit caches with
+ * head_dim 128 and the portable SIMT kernels otherwise (fp32 caches always use SIMT fp32 maths). */
+#define ZP_IMPL_AUTO 0
+#define ZP_IMPL_SIMT 1
+#define ZP_IMPL_TCGEN05 2
+
+const char* zp_last_error(void);
+int zp_version(void);
+
+/* Replaces store_kvcache, zipage/layers/attention.py:12-50.
+ * key/value [N, Hkv, D] (row stride given), caches contiguous [P*BS, Hkv, D];
+ * row i goes to flat slot slot_mapping[i]; slot -1 is skipped. */
+int zp_store_kv(const void* key, const void* value, void* k_cache, void* v_cache,
+                const int32_t* slot_mapping, int n_tokens, int num_kv_heads, int head_dim,
+                int64_t key_stride0, int64_t value_stride0, int dtype, void* stream);
+
+/* Replaces store_query_cache, zipage/kernel/store_query_cache.py:7-68.
+ * query [N, Hq, D]; query_cache [C, QCL, Hq, D] (one layer); triples [n, 3] int32 =
+ * (row of query, query_id, window index). */
+int zp_store_query(const void* query, void* query_cache, const int32_t* triples, int n_triples,
+                   int num_heads, int head_dim, int64_t query_stride0, int64_t cache_stride_seq,
+                   int64_t cache_stride_slot, int dtype, void* stream);
+
+/* Replaces attention_score, zipage/kernel/attention_score.py:8-250 (kernel + torch glue), without
+ * the [L,B,Hq,QCL,NB,BS] logits buffer: softmax over the sequence of the window queries' logits,
+ * max over the query heads of a KV group, mean (reduce_mode 0) or max (1) over the window rows.
+ * scores_out [L,B,Hkv,NB,BS] T (padded pages get 0).  logits_out is NULL or a
+ * [L,B,Hq,QCL,NB,BS] T buffer that receives the masked logits (return_logits=True). */
+int zp_window_score(const void* k_cache, const void* query_cache, const int32_t* seq_idx,
+                    const int32_t* block_table, void* scores_out, void* logits_out, int L, int B,
+                    int NB, int Hq, int Hkv, int D, int QCL, int BS, int64_t k_stride_layer,
+                    int64_t k_stride_page, int64_t q_stride_layer, int64_t q_stride_seq,
+                    float softmax_scale, int reduce_mode, int dtype, int impl, void* stream);
+
+/* Replaces global_score, zipage/kernel/global_score.py:8-120 (activate 0 = max, 1 = sum), plus the
+ * optional max-normalisation that precedes it, zipage/engine/model_runner.py:482-487
+ * (max_norm != 0: scores are first divided by their per-(layer, seq, head) maximum).
+ * scores [L,B,Hkv,NB,BS] and score_cache [L,P,BS,Hkv] are both updated in place. */
+int zp_global_score(void* scores, void* score_cache, const int32_t* block_table,
+                    const uint8_t* compressed, int L, int B, int NB, int Hkv, int BS,
+                    int64_t sc_stride_layer, int64_t sc_stride_page, float decay, int activate,
+                    int max_norm, int dtype, void* stream);
+
+/* Replaces key_norm, zipage/kernel/key_norm.py:8-113: norm_out [L,B,Hkv,NB,BS] T, floor 1e-6
+ * (padded pages hold the floor). */
+int zp_key_norm(const void* k_cache, const int32_t* block_table, void* norm_out, int L, int B,
+                int NB, int Hkv, int D, int BS, int64_t k_stride_layer, int64_t k_stride_page,
+                float eps, int dtype, void* stream);
+
+/* Replaces the kernels of lightning_redudancy_score (zipage/kernel/lightning_redudancy_score.py:
+ * 10-169) and raw_redudancy_score (zipage/kernel/raw_redudancy_score.py:10-155, :218): cosine
+ * similarity of key pairs (same page / whole sequence), diagonal zeroed, per column the entry of
+ * the latest row above `threshold` zeroed, row sums.  logits_out [L,B,Hkv,NB,BS] T, padded pages
+ * -inf.  The exact form needs scratch: zp_redundancy_exact_workspace_bytes(L,B,NB,Hkv,BS). */
+int zp_redundancy_lightning(const void* k_cache, const int32_t* block_table, void* logits_out,
+                            int L, int B, int NB, int Hkv, int D, int BS, int64_t k_stride_layer,
+                            int64_t k_stride_page, float threshold, int dtype, int impl,
+                            void* stream);
+size_t zp_redundancy_exact_workspace_bytes(int L, int B, int NB, int Hkv, int BS);
+int zp_redundancy_exact(const void* k_cache, const int32_t* block_table, void* logits_out, int L,
+                        int B, int NB, int Hkv, int D, int BS, int64_t k_stride_layer,
+                        int64_t k_stride_page, float threshold, int dtype, int impl,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* The torch epilogue of both redundancy functions (lightning :248-252, raw :226-229): in place,
+ * logits / (temperature * divisor), minus the row maximum, softmax over the sequence, each step
+ * rounded to T.  per_sequence_len != 0: divisor = BS * (#valid pages) (exact form), else BS. */
+int zp_redundancy_softmax(void* logits_inout, const int32_t* block_table, int L, int B, int NB,
+                          int Hkv, int BS, float temperature, int per_sequence_len, int dtype,
+                          void* stream);
+
+/* Selection parameters of zp_select (zipage/engine/model_runner.py:499-602). */
+typedef struct zp_select_params {
+  int32_t top_k;               /* rows kept per (layer, seq, head): BS * budget              */
+  int32_t query_cache_len;     /* window length: last QCL slots of the last page <- +inf      */
+  int32_t pooling_size;        /* 0 = no pooling, else odd kernel of max_pool1d (reference: 5) */
+  int32_t continues_pooling;   /* pool sequences that were compressed before as well          */
+  int32_t use_redundancy;      /* 0 none, 1 lightning (divisor BS), 2 exact (divisor length)   */
+  int32_t redundancy_max_norm; /* divide the redundancy by its maximum (global score+max_norm) */
+  int32_t sink_len;            /* 0 = off, else first sink_len tokens <- +inf                 */
+  float redundancy_lambda;
+  float redundancy_temperature;
+} zp_select_params;
+
+/* Replaces the pooling / combine / sink / window_mask / pad mask / topk_mask stages
+ * (zipage/engine/model_runner.py:499-602, zipage/kernel/window_mask.py:8-72,
+ * zipage/kernel/utils.py:21-36).  scores [L,B,Hkv,NB,BS] T (after the global-score stage) and
+ * red_logits (same shape, output of zp_redundancy_*; NULL when use_redundancy == 0) are read;
+ * keep_out [L,B,Hkv,NB,BS] uint8 receives 1 for the top_k entries of every row — equal scores go
+ * to the LOWEST index.  final_out is NULL or receives the selection scores (T). */
+int zp_select(const void* scores, const void* red_logits, const int32_t* block_table,
+              const uint8_t* compressed, uint8_t* keep_out, void* final_out, int L, int B, int NB,
+              int Hkv, int BS, const zp_select_params* params, int dtype, void* stream);
+
+/* Replaces compress_kv (zipage/kernel/compress_kv.py:8-141) and compress_score
+ * (zipage/kernel/compress_score.py:8-99): stable forward compaction of the kept rows of every
+ * (layer, seq, head) into the pages of target_table, in place.  score_cache may be NULL (then
+ * only K/V move); k_cache/v_cache may be NULL (then only the score cache moves).  Requires, as the
+ * reference does, that a destination never lies after the row being read (block_manager.py:129-169)
+ * and that no more than NT*BS rows are kept. */
+int zp_compact(void* k_cache, void* v_cache, void* score_cache, const uint8_t* keep,
+               const int32_t* block_table, const int32_t* target_table, int L, int B, int NB,
+               int NT, int Hkv, int D, int BS, int64_t kv_stride_layer, int64_t kv_stride_page,
+               int64_t sc_stride_layer, int64_t sc_stride_page, int dtype, void* stream);
+
+/* Device-side table update after a compaction (no reference kernel: the reference does this on
+ * the host in zipage/engine/scheduler.py:150-156 and model_runner.py:633-675).  For each sequence:
+ * new_table[b, :] = target_table[b, :]; context_len[b] = BS*(NT-1) + 1;
+ * next_slot[b] = target_table[b, NT-1] * BS (the slot the next token's K/V is stored to). */
+int zp_update_tables(const int32_t* target_table, int32_t* new_table, int32_t* context_len,
+                     int32_t* next_slot, int B, int NT, int new_table_stride, int BS, void* stream);
+
+/* Replaces flash_attn_with_kvcache as called at zipage/layers/attention.py:95-103: one query token
+ * per sequence over its paged K/V.  q,out [B, Hq, D]; caches [P, BS, Hkv, D] (page stride given);
+ * cache_seqlens [B]; block_table [B, NBmax] (-1 padded).  Scratch from
+ * zp_paged_decode_workspace_bytes. */
+size_t zp_paged_decode_workspace_bytes(int B, int Hq, int D, int max_splits);
+int zp_paged_decode(const void* q, const void* k_cache, const void* v_cache,
+                    const int32_t* cache_seqlens, const int32_t* block_table, void* out, int B,
+                    int NBmax, int Hq, int Hkv, int D, int BS, int64_t kv_stride_page,
+                    float softmax_scale, int dtype, void* workspace, size_t workspace_bytes,
+                    void* stream);
+
+/* Replaces flash_attn_varlen_func as called at zipage/layers/attention.py:79-93: causal
+ * (bottom-right aligned) variable-length attention.  q,out [sum_q, Hq, D].  block_table == NULL:
+ * k,v dense [sum_k, Hkv, D]; else k,v are the paged caches [P, BS, Hkv, D] and block_table
+ * [B, NBmax] lists each sequence's pages. */
+int zp_varlen_prefill(const void* q, const void* k, const void* v, const int32_t* cu_seqlens_q,
+                      const int32_t* cu_seqlens_k, const int32_t* block_table, void* out, int B,
+                      int max_seqlen_q, int NBmax, int Hq, int Hkv, int D, int BS,
+                      int64_t kv_stride_page, float softmax_scale, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZIPAGE_B200_H_ */
