@@ -121,7 +121,9 @@ typedef struct zp_select_params {
   int32_t use_redundancy;      /* 0 none, 1 lightning (divisor BS), 2 exact (divisor length)   */
   int32_t redundancy_max_norm; /* divide the redundancy by its maximum (global score+max_norm) */
   int32_t sink_len;            /* 0 = off, else first sink_len tokens <- +inf                 */
-  float redundancy_lambda;
+  int32_t pad_mask;            /* padded pages <- -inf (model_runner.py:592-593); 0 = leave    */
+  float redundancy_lambda;           /* lambda                                              */
+  float redundancy_one_minus_lambda; /* 1 - lambda, evaluated in double by the caller        */
   float redundancy_temperature;
 } zp_select_params;
 

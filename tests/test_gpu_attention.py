@@ -1,0 +1,105 @@
+"""Paged decode and varlen prefill attention against the fp32 oracle (parity unpinned: the
+reference calls flash-attn here, which has no golden vectors in its tree)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+BS = 256
+
+
+def _setup(dtype, P=40, Hkv=8, D=128, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    kc = torch.randn(P, BS, Hkv, D, generator=g).to(dtype)
+    vc = torch.randn(P, BS, Hkv, D, generator=g).to(dtype)
+    return g, kc, vc
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float16, 2e-2), (torch.float32, 1e-3)])
+@pytest.mark.parametrize("Hq,Hkv,B", [(32, 8, 5), (8, 8, 3), (16, 2, 70), (64, 8, 2)])
+def test_paged_decode(dtype, tol, Hq, Hkv, B):
+    from oracle import zipage_oracle as O
+    from zipage_b200.layers.attention import paged_decode_attention
+    dev = torch.device("cuda:0")
+    P = max(40, B * 2 + 4)
+    g, kc, vc = _setup(dtype, P=P, Hkv=Hkv)
+    NBmax = 9
+    lens = torch.randint(1, NBmax * BS + 1, (B,), generator=g).to(torch.int32)
+    lens[0] = 2049
+    lens[-1] = 1
+    if B > 2:
+        lens[1] = NBmax * BS
+    table = torch.full((B, NBmax), -1, dtype=torch.int32)
+    for b in range(B):
+        npg = (int(lens[b]) + BS - 1) // BS
+        table[b, :npg] = torch.randperm(P, generator=g)[:npg].to(torch.int32)
+    q = torch.randn(B, 1, Hq, 128, generator=g).to(dtype)
+    ref = O.paged_decode_attention(q, kc, vc, lens, table)
+    out = paged_decode_attention(q.to(dev), kc.to(dev), vc.to(dev), lens.to(dev), table.to(dev)).cpu()
+    err = (out.float() - ref.float()).abs().max().item()
+    assert err <= tol * ref.float().abs().max().item(), err
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float32, 1e-3)])
+def test_varlen_prefill_dense_and_paged(dtype, tol):
+    from oracle import zipage_oracle as O
+    from zipage_b200.layers.attention import varlen_prefill_attention
+    dev = torch.device("cuda:0")
+    Hq, Hkv, D = 8, 2, 128
+    g, kc, vc = _setup(dtype, P=12, Hkv=Hkv)
+    lens_k = [300, 1, 64, 517]
+    # dense: q and k lengths equal
+    cu = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32)
+    tot = int(cu[-1])
+    q = torch.randn(tot, Hq, D, generator=g).to(dtype)
+    k = torch.randn(tot, Hkv, D, generator=g).to(dtype)
+    v = torch.randn(tot, Hkv, D, generator=g).to(dtype)
+    ref = O.varlen_prefill_attention(q, k, v, cu, cu)
+    out = varlen_prefill_attention(q.to(dev), k.to(dev), v.to(dev), max(lens_k), cu.to(dev),
+                                   max(lens_k), cu.to(dev)).cpu()
+    assert (out.float() - ref.float()).abs().max() <= tol * ref.float().abs().max()
+    # paged with a cached prefix: fewer queries than keys, bottom-right aligned
+    lens_q = [44, 1, 64, 5]
+    cuq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    table = torch.full((4, 3), -1, dtype=torch.int32)
+    perm = torch.randperm(12, generator=g)
+    pos = 0
+    for b, lk in enumerate(lens_k):
+        npg = (lk + BS - 1) // BS
+        table[b, :npg] = perm[pos:pos + npg].to(torch.int32)
+        pos += npg
+    q2 = torch.randn(int(cuq[-1]), Hq, D, generator=g).to(dtype)
+    ref2 = O.varlen_prefill_attention(q2, kc, vc, cuq, cu, block_table=table)
+    out2 = varlen_prefill_attention(q2.to(dev), kc.to(dev), vc.to(dev), max(lens_q), cuq.to(dev),
+                                    max(lens_k), cu.to(dev), block_table=table.to(dev)).cpu()
+    assert (out2.float() - ref2.float()).abs().max() <= tol * ref2.float().abs().max()
+
+
+def test_attention_layer_contract():
+    """Attention.forward: store K/V + window queries, then decode attention, as the reference layer."""
+    from oracle import zipage_oracle as O
+    from zipage_b200.layers.attention import Attention
+    from zipage_b200.utils.context import reset_context, set_context
+    dev = torch.device("cuda:0")
+    dtype = torch.bfloat16
+    Hq, Hkv, D, QCL, B = 8, 2, 128, 16, 3
+    g, kc, vc = _setup(dtype, P=10, Hkv=Hkv)
+    layer = Attention(Hq, D, D ** -0.5, Hkv)
+    kc_d, vc_d = kc.to(dev), vc.to(dev)
+    qcache = torch.zeros(4, QCL, Hq, D, dtype=dtype)
+    layer.k_cache, layer.v_cache, layer.q_cache = kc_d, vc_d, qcache.to(dev)
+    lens = torch.tensor([250, 513, 7], dtype=torch.int32)
+    table = torch.tensor([[3, -1, -1], [0, 5, 8], [9, -1, -1]], dtype=torch.int32)
+    slots = torch.tensor([3 * BS + 249, 8 * BS + 0, 9 * BS + 6], dtype=torch.int32)
+    triples = torch.tensor([[0, 2, 249 - (BS - QCL)]], dtype=torch.int32)
+    q = torch.randn(B, Hq, D, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, D, generator=g).to(dtype)
+    v = torch.randn(B, Hkv, D, generator=g).to(dtype)
+    set_context(False, slot_mapping=slots.to(dev), context_lens=lens.to(dev),
+                block_tables=table.to(dev), query_slot_mapping=triples.to(dev))
+    out = layer(q.to(dev), k.to(dev), v.to(dev)).cpu()
+    reset_context()
+    O.store_kvcache(k, v, kc, vc, slots)
+    O.store_query_cache(q, qcache, triples)
+    ref = O.paged_decode_attention(q.unsqueeze(1), kc, vc, lens, table)
+    assert torch.equal(kc_d.cpu(), kc) and torch.equal(layer.q_cache.cpu(), qcache)
+    assert (out.float() - ref.float()).abs().max() <= 2e-2 * ref.float().abs().max()

@@ -1,0 +1,100 @@
+"""ctypes binding of libzipage_b200.so (the C ABI declared in include/zipage_b200.h).
+
+The library is the product; there is no Python or CPU fallback.  If the shared
+object has not been built, loading raises with the build command.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libzipage_b200.so"
+
+ZP_DTYPE = {torch.bfloat16: 0, torch.float32: 1, torch.float16: 2}
+IMPL = {"auto": 0, "simt": 1, "tcgen05": 2}
+
+
+class ZipageError(RuntimeError):
+    pass
+
+
+class SelectParams(C.Structure):
+    _fields_ = [
+        ("top_k", C.c_int32), ("query_cache_len", C.c_int32), ("pooling_size", C.c_int32),
+        ("continues_pooling", C.c_int32), ("use_redundancy", C.c_int32),
+        ("redundancy_max_norm", C.c_int32), ("sink_len", C.c_int32), ("pad_mask", C.c_int32),
+        ("redundancy_lambda", C.c_float), ("redundancy_one_minus_lambda", C.c_float),
+        ("redundancy_temperature", C.c_float),
+    ]
+
+
+_P, _I, _L, _F, _Z = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
+
+# name -> (restype, argtypes); mirrors include/zipage_b200.h one to one
+SIGNATURES = {
+    "zp_last_error": (C.c_char_p, []),
+    "zp_version": (_I, []),
+    "zp_store_kv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _L, _L, _I, _P]),
+    "zp_store_query": (_I, [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P]),
+    "zp_window_score": (_I, [_P, _P, _P, _P, _P, _P] + [_I] * 8 + [_L] * 4 + [_F, _I, _I, _I, _P]),
+    "zp_global_score": (_I, [_P, _P, _P, _P] + [_I] * 5 + [_L, _L, _F, _I, _I, _I, _P]),
+    "zp_key_norm": (_I, [_P, _P, _P] + [_I] * 6 + [_L, _L, _F, _I, _P]),
+    "zp_redundancy_lightning": (_I, [_P, _P, _P] + [_I] * 6 + [_L, _L, _F, _I, _I, _P]),
+    "zp_redundancy_exact_workspace_bytes": (_Z, [_I] * 5),
+    "zp_redundancy_exact": (_I, [_P, _P, _P] + [_I] * 6 + [_L, _L, _F, _I, _I, _P, _Z, _P]),
+    "zp_redundancy_softmax": (_I, [_P, _P] + [_I] * 5 + [_F, _I, _I, _P]),
+    "zp_select": (_I, [_P, _P, _P, _P, _P, _P] + [_I] * 5 + [C.POINTER(SelectParams), _I, _P]),
+    "zp_compact": (_I, [_P, _P, _P, _P, _P, _P] + [_I] * 7 + [_L] * 4 + [_I, _P]),
+    "zp_update_tables": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "zp_paged_decode_workspace_bytes": (_Z, [_I] * 4),
+    "zp_paged_decode": (_I, [_P] * 6 + [_I] * 6 + [_L, _F, _I, _P, _Z, _P]),
+    "zp_varlen_prefill": (_I, [_P] * 7 + [_I] * 7 + [_L, _F, _I, _P]),
+}
+
+_lib = None
+
+
+def load():
+    """Load the shared library once; raise (never fall back) when it is missing."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ZipageError(
+                f"{LIB_PATH} is missing: build it with `python -m zipage_b200.build` "
+                "(there is no CPU or PyTorch fallback for these kernels)")
+        lib = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def check(rc: int, what: str = ""):
+    if rc != 0:
+        msg = load().zp_last_error().decode(errors="replace")
+        raise ZipageError(f"{what or 'zipage_b200'} failed ({rc}): {msg}")
+
+
+def ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def stream_ptr():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return ZP_DTYPE[t.dtype]
+    except KeyError:
+        raise ZipageError(f"unsupported cache dtype {t.dtype}") from None
+
+
+def require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ZipageError("zipage_b200 kernels need CUDA tensors (no CPU path exists)")
