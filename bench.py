@@ -1,0 +1,332 @@
+#!/usr/bin/env python
+"""Benchmark of the compression op (the configuration the "compress HBM GB/s" metric is quoted on).
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's CUDA path
+    python bench.py --impl reference ...                     # the reference's CPU formulation
+    torchrun --nproc-per-node N bench.py --gpus N ...        # one rank per GPU, KV heads sharded
+
+One step = one pass of the whole compression op (window scoring -> [global score] -> similarity
+redundancy -> pooling/combine/masks/top-k -> in-place compaction) over every layer of a batch of
+sequences that each hold budget+1 = 9 pages.  `value` is algorithmic bytes moved per second with
+all inputs resident in HBM; `e2e` is the same through the host-facing call (host lists of block
+tables -> pinned memory -> device, kernels, stream sync, read-back of the new tables).
+Prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "compress_hbm_gbs"
+UNIT = "GB/s"
+BS = 256
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="zipage_b200", choices=["zipage_b200", "reference"])
+    ap.add_argument("--variant", default="lightning", choices=["lightning", "exact", "none"])
+    ap.add_argument("--batch", type=int, default=512, help="sequences per GPU at N=1 (reduced to fit)")
+    ap.add_argument("--layers", type=int, default=36)
+    ap.add_argument("--layer-chunk", type=int, default=0, help="layers per kernel call (0 = all)")
+    ap.add_argument("--global-score", action="store_true")
+    ap.add_argument("--kernel-impl", default="auto", choices=["auto", "simt", "tcgen05"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--also-exact", action="store_true", help="time the exact variant as well")
+    return ap.parse_args()
+
+
+# workload constants: Qwen3-8B attention shapes, window 32, budget 8 pages of 256
+HKV, HQ, D, QCL, BUDGET = 8, 32, 128, 32, 8
+POOL, LAMBDA, TEMP = 7, 0.5, 0.4
+
+
+def make_cfg(variant, global_score):
+    from zipage_b200.compress import CompressConfig
+    return CompressConfig(
+        budget_blocks=BUDGET, query_cache_len=QCL, use_global_score=global_score, decay_factor=0.8,
+        use_redudancy=variant != "none", lightning_redudancy=variant == "lightning",
+        redudancy_lambda=LAMBDA, redudancy_temperature=TEMP, enable_pooling=True,
+        continues_pooling=True, pooling_size=POOL)
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx = max(mx, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_baseline_sample(variant, global_score, threads):
+    """The oracle (CPU restatement of the reference's PyTorch formulation) on a bounded sample of
+    the same workload: L=1, B=2 sequences of 9 pages, 8 KV heads, bf16."""
+    import torch
+    from oracle import zipage_oracle as O
+    from zipage_b200.synthetic import algorithmic_bytes_per_unit, make_compress_workload
+    torch.set_num_threads(threads)
+    Ls, Bs = 1, 2
+    w = make_compress_workload(Bs, Ls, HKV, HQ, D, QCL, BUDGET, dtype=torch.bfloat16, device="cpu",
+                               seed=7, with_score_cache=global_score)
+    ocfg = O.CompressConfig(budget_blocks=BUDGET, query_cache_len=QCL, use_global_score=global_score,
+                            use_redudancy=variant != "none", lightning_redudancy=variant == "lightning",
+                            redudancy_lambda=LAMBDA, redudancy_temperature=TEMP, enable_pooling=True,
+                            continues_pooling=True, pooling_size=POOL)
+    times = []
+    moved = None
+    for it in range(3):
+        k, v = w.kv_cache[0].clone(), w.kv_cache[1].clone()
+        sc = w.score_cache.clone() if w.score_cache is not None else None
+        t0 = time.perf_counter()
+        _, keep = O.compress(k, v, w.query_cache, sc, w.query_ids, w.block_tables, w.target_tables,
+                             w.compressed, ocfg)
+        times.append(time.perf_counter() - t0)
+        if moved is None:
+            moved = moved_rows_per_unit(keep)
+    t = statistics.median(times[1:]) if len(times) > 1 else times[0]
+    units = Ls * Bs * HKV
+    st = algorithmic_bytes_per_unit(BUDGET + 1, D, QCL, HQ // HKV, 2, variant != "none", global_score, moved)
+    return sum(st.values()) * units / t / 1e9, t, units
+
+
+def moved_rows_per_unit(keep):
+    """Mean number of kept rows whose slot changes: rows after the first dropped one."""
+    import torch
+    flat = keep.reshape(-1, keep.shape[-2] * keep.shape[-1])
+    first_drop = (~flat).float().argmax(dim=1)
+    any_drop = (~flat).any(dim=1)
+    idx = torch.arange(flat.shape[1], device=flat.device)[None, :]
+    moved = (flat & (idx > first_drop[:, None]) & any_drop[:, None]).sum(dim=1).float().mean().item()
+    return moved
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    vals, secs = [], []
+    for i in range(args.warmup + args.steps):
+        gbs, t, units = cpu_baseline_sample(args.variant, args.global_score, threads)
+        if i >= args.warmup:
+            vals.append(gbs); secs.append(t)
+    v = statistics.mean(vals)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": statistics.mean(secs) * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "compression op, Qwen3-8B attention shapes, 9->8 pages, window 32, "
+                               f"pool {POOL}, lambda {LAMBDA}, {args.variant} redundancy (config 2)",
+                   "sample": "L=1, B=2 sequences x 8 KV heads (16 units) per step"},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": "oracle.compress on L=1,B=2,Hkv=8,9 pages,bf16; median of 2 after 1 warm-up"},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from zipage_b200 import kernel as K
+    from zipage_b200.compress import compress_chunk
+    from zipage_b200.engine.compressor import Compressor
+    from zipage_b200.synthetic import (algorithmic_bytes_per_unit, bytes_per_sequence,
+                                       make_compress_workload)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # KV heads are sharded over ranks; per-rank work is held fixed (weak scaling): with 1/world of
+    # the heads per page a rank serves world x the sequences, as the engine's concurrency would.
+    hkv, hq = HKV // world, HQ // world
+    L = args.layers
+    itemsize = 2
+    per_seq = bytes_per_sequence(L, BUDGET + 1, hkv, hq, D, QCL, itemsize, args.global_score)
+    per_seq += L * hkv * (BUDGET + 1) * BS * 8  # scores, redundancy logits, flags, final
+    free, total = torch.cuda.mem_get_info()
+    B = min(args.batch * world, int((free - (8 << 30)) // per_seq))
+    B -= B % 8
+    assert B > 0, "no room for a single sequence"
+    cfg = make_cfg(args.variant, args.global_score)
+    w = make_compress_workload(B, L, hkv, hq, D, QCL, BUDGET, dtype=torch.bfloat16, device=dev,
+                               seed=1234 + rank, with_score_cache=args.global_score)
+    chunk = args.layer_chunk or L
+    comp = Compressor(w.kv_cache, w.query_cache, w.score_cache, cfg, layer_stride=chunk,
+                      impl=args.kernel_impl)
+    seq_tables = w.tables_plain.cpu().tolist()
+    seq_targets = w.target_tables.cpu().tolist()
+    seq_qids = w.query_ids.cpu().tolist()
+    seq_comp = w.compressed.cpu().tolist()
+
+    def device_step():
+        for l0 in range(0, L, chunk):
+            sl = slice(l0, min(L, l0 + chunk))
+            compress_chunk(w.kv_cache[0, sl], w.kv_cache[1, sl], w.query_cache[sl],
+                           None if w.score_cache is None else w.score_cache[sl], w.query_ids,
+                           w.block_tables, w.target_tables, w.compressed, cfg, impl=args.kernel_impl,
+                           workspace=comp.workspace)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        device_step()
+    barrier()
+    K.LAUNCHES = 0
+    with ClockSampler(local) as clocks:
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(args.steps):
+            device_step()
+        ev1.record()
+        barrier()
+        dev_ms = ev0.elapsed_time(ev1)
+    launches = K.LAUNCHES
+    # stage split (one extra untimed-by-the-headline step with per-stage events)
+    comp.time_record.clear()
+    comp.compress_tables(seq_tables, seq_targets, seq_qids, seq_comp, timed=True)
+    stage_ms = {k: v * 1e3 for k, v in comp.time_record.items() if k.endswith("_sum")}
+
+    # end to end through the host-facing call: host lists -> pinned -> H2D, kernels, sync, D2H
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        new_tables, ctx_lens = comp.compress_tables(seq_tables, seq_targets, seq_qids, seq_comp)
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / args.steps
+    h2d = comp.last_h2d_bytes
+    d2h = comp.last_d2h_bytes
+
+    # algorithmic bytes: moved rows counted from the flags of one more selection pass
+    dbg = compress_chunk(w.kv_cache[0, :1], w.kv_cache[1, :1], w.query_cache[:1],
+                         None if w.score_cache is None else w.score_cache[:1], w.query_ids,
+                         w.block_tables, w.target_tables, w.compressed, cfg, impl=args.kernel_impl,
+                         workspace=comp.workspace, return_debug=True)
+    moved = moved_rows_per_unit(dbg["keep"])
+    stages = algorithmic_bytes_per_unit(BUDGET + 1, D, QCL, hq // hkv, itemsize,
+                                        args.variant != "none", args.global_score, moved)
+    units = L * B * hkv
+    bytes_step = sum(stages.values()) * units
+
+    t = torch.tensor([dev_ms, e2e_s * 1e3], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = t.tolist()
+    ms_step = dev_ms / args.steps
+    value = bytes_step * world / (ms_step * 1e-3) / 1e9
+    e2e_val = bytes_step * world / (e2e_ms * 1e-3) / 1e9
+
+    if rank == 0:
+        peaks = {}
+        pk = ROOT / "MEASURED_PEAKS.json"
+        if pk.exists():
+            peaks = json.loads(pk.read_text())
+        hbm_peak = peaks.get("hbm_gbs", 6650.0)
+        # dominant kernel by the per-stage split
+        top = max(stage_ms, key=stage_ms.get) if stage_ms else "attention_score_sum"
+        stage_key = {"attention_score_sum": "window_score", "redudancy_score_sum": "redundancy",
+                     "topk_mask_sum": "select", "compress_kv_sum": "compact",
+                     "global_score_sum": "window_score"}.get(top, "window_score")
+        nlaunch = (L + chunk - 1) // chunk
+        top_ms = stage_ms.get(top, ms_step) / nlaunch
+        achieved = stages[stage_key] * units / nlaunch / (top_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {
+                "workload": "compression op, Qwen3-8B attention shapes, 9->8 pages, window 32, "
+                            f"pool {POOL}, lambda {LAMBDA}, {args.variant} redundancy (config 2)",
+                "sequences_per_gpu": B, "layers": L, "kv_heads_per_gpu": hkv, "q_heads_per_gpu": hq,
+                "head_dim": D, "pages_per_seq": BUDGET + 1, "budget_pages": BUDGET,
+                "units_per_gpu": units, "global_score": args.global_score,
+                "kernel_impl": args.kernel_impl, "layer_chunk": chunk,
+                "l2": "inputs (K/V pages of all sequences) are far larger than the 126 MB L2",
+                "parallelism": f"kv-head sharding x{world}, no data-path collective",
+            },
+            "units_per_s": units * world / (ms_step * 1e-3),
+            "algorithmic_bytes_per_unit": stages, "moved_rows_per_unit": moved,
+            "stage_ms": stage_ms,
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": launches,
+            "clocks": clocks.summary(),
+            "roofline": {"bound": "hbm", "kernel": stage_key, "achieved": achieved, "peak": hbm_peak,
+                         "unit": "GB/s", "frac": achieved / hbm_peak,
+                         "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
+                         "traffic": None},
+        }
+        if not args.no_cpu_baseline and world == 1:
+            threads = os.cpu_count() or 1
+            gbs, secs, cu = cpu_baseline_sample(args.variant, args.global_score, threads)
+            line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": f"oracle.compress on {cu} units (L=1,B=2,Hkv=8), {secs:.2f}s"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

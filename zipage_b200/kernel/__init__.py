@@ -19,6 +19,15 @@ __all__ = [
 ]
 
 
+# kernels launched through this module since it was last reset (a plain counter for benchmarks)
+LAUNCHES = 0
+
+
+def _count(n=1):
+    global LAUNCHES
+    LAUNCHES += n
+
+
 def _i32(t):
     if t.dtype != torch.int32 or not t.is_contiguous():
         raise ZipageError("index tensors must be contiguous int32")
@@ -44,6 +53,7 @@ def store_kvcache(key, value, k_cache, v_cache, slot_mapping):
     L.check(L.load().zp_store_kv(L.ptr(key), L.ptr(value), L.ptr(k_cache), L.ptr(v_cache),
                                  L.ptr(_i32(slot_mapping)), N, H, D, key.stride(0), value.stride(0),
                                  L.dtype_code(k_cache), L.stream_ptr()), "store_kvcache")
+    _count()
 
 
 def store_query_cache(query, query_cache, slot_mapping):
@@ -58,6 +68,7 @@ def store_query_cache(query, query_cache, slot_mapping):
                                     slot_mapping.shape[0], H, D, query.stride(0),
                                     query_cache.stride(0), query_cache.stride(1),
                                     L.dtype_code(query_cache), L.stream_ptr()), "store_query_cache")
+    _count()
 
 
 def attention_score(k_cache, query_cache, seq_idx, block_table, softmax_scale=None,
@@ -83,6 +94,7 @@ def attention_score(k_cache, query_cache, seq_idx, block_table, softmax_scale=No
         k_cache.stride(1), query_cache.stride(0), query_cache.stride(1), float(softmax_scale),
         0 if reduced == "mean" else 1, L.dtype_code(k_cache), L.IMPL[impl], L.stream_ptr()),
         "attention_score")
+    _count()
     if return_logits:
         return scores, logits
     return scores
@@ -102,6 +114,7 @@ def global_score(reduced_scores, score_cache, block_table, compressed, decay_fac
         Hkv, BS, score_cache.stride(0), score_cache.stride(1), float(decay_factor),
         0 if activate_method == "max" else 1, int(max_norm), L.dtype_code(reduced_scores),
         L.stream_ptr()), "global_score")
+    _count(2 if max_norm else 1)
     return reduced_scores
 
 
@@ -116,6 +129,7 @@ def key_norm(key_cache, block_table, norm_epsilon=1e-6):
                                  Hkv, D, BS, key_cache.stride(0), key_cache.stride(1),
                                  float(norm_epsilon), L.dtype_code(key_cache), L.stream_ptr()),
             "key_norm")
+    _count()
     return out
 
 
@@ -137,8 +151,10 @@ def redundancy_logits(key_cache, block_table, threshold=0.5, exact=True, impl="a
         L.check(lib.zp_redundancy_exact(*common, L.ptr(workspace),
                                         workspace.numel() * workspace.element_size(),
                                         L.stream_ptr()), "raw_redudancy_score")
+        _count(2)
     else:
         L.check(lib.zp_redundancy_lightning(*common, L.stream_ptr()), "lightning_redudancy_score")
+        _count()
     return out
 
 
@@ -149,6 +165,7 @@ def _redundancy(key_cache, block_table, threshold, temperature, return_logits, e
     L.check(L.load().zp_redundancy_softmax(L.ptr(red), L.ptr(block_table), Ln, B, NB, Hkv, BS,
                                            float(temperature), int(exact), L.dtype_code(red),
                                            L.stream_ptr()), "redundancy softmax")
+    _count()
     if return_logits:
         return (logits.view(Ln, B, Hkv, -1), red) if exact else (logits, red)
     return red
@@ -191,6 +208,7 @@ def select_keep(scores, block_table, compressed, top_k, query_cache_len, red_log
     L.check(L.load().zp_select(L.ptr(scores), L.ptr(red_logits), L.ptr(_i32(block_table)),
                                L.ptr(comp), L.ptr(keep), L.ptr(final), Ln, B, NB, Hkv, BS,
                                ctypes.byref(sp), L.dtype_code(scores), L.stream_ptr()), "select")
+    _count()
     keep = keep.view(torch.bool)
     return (keep, final) if return_final else keep
 
@@ -207,6 +225,7 @@ def window_mask(scores, block_table, query_cache_len):
     L.check(L.load().zp_select(L.ptr(scores), None, L.ptr(_i32(block_table)), L.ptr(comp),
                                L.ptr(keep), L.ptr(scores), Ln, B, NB, Hkv, BS, ctypes.byref(sp),
                                L.dtype_code(scores), L.stream_ptr()), "window_mask")
+    _count()
     return scores
 
 
@@ -239,6 +258,7 @@ def _compact(k, v, sc, flag, block_table, target_block_table, what):
         k.stride(0) if k is not None else 0, k.stride(1) if k is not None else 0,
         sc.stride(0) if sc is not None else 0, sc.stride(1) if sc is not None else 0,
         L.dtype_code(ref), L.stream_ptr()), what)
+    _count()
 
 
 def compress_kv(key, value, flag, block_table, target_block_table):
@@ -269,4 +289,5 @@ def update_tables(target_block_table, table_width=None):
     L.check(L.load().zp_update_tables(L.ptr(_i32(target_block_table)), L.ptr(new_table), L.ptr(ctx),
                                       L.ptr(nxt), B, NT, width, 256, L.stream_ptr()),
             "update_tables")
+    _count()
     return new_table, ctx, nxt
