@@ -50,6 +50,12 @@ extern "C" {
 const char* zp_last_error(void);
 int zp_version(void);
 
+/* The tcgen05 kernels bound every wait on a barrier; a wait that runs out makes the kernel return
+ * early and raises a device-side error word (no reference counterpart: the reference has no such
+ * kernels).  This call synchronises the device, stores the word in *code_out (0 = no error; else an
+ * internal code naming the wait) and clears it when reset != 0. */
+int zp_device_error(int* code_out, int reset);
+
 /* Replaces store_kvcache, zipage/layers/attention.py:12-50.
  * key/value [N, Hkv, D] (row stride given), caches contiguous [P*BS, Hkv, D];
  * row i goes to flat slot slot_mapping[i]; slot -1 is skipped. */

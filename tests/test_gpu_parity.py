@@ -254,3 +254,29 @@ def test_update_tables():
     assert nt.cpu().tolist() == [[5, 2, 9, -1, -1], [1, 7, 3, -1, -1]]
     assert ctx.cpu().tolist() == [2 * BS + 1] * 2
     assert nxt.cpu().tolist() == [9 * BS, 3 * BS]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("exact", [False, True])
+def test_redundancy_tcgen05_matches_simt_and_oracle(dtype, exact):
+    """The tensor-core similarity kernels against the SIMT kernels (same dtype) and the oracle."""
+    from oracle import zipage_oracle as O
+    from zipage_b200 import _lib, kernel as K
+    from zipage_b200.synthetic import make_compress_workload
+    dev = _gpu()
+    w = make_compress_workload(B=5, L=3, Hkv=2, Hq=4, QCL=16, budget=2, pages_per_seq=[3, 4, 3, 5, 3],
+                               dtype=dtype, device=dev, seed=21, similar_keys=True, spare_pages=2)
+    k, bt = w.kv_cache[0], w.block_tables
+    a = K.redundancy_logits(k, bt, 0.5, exact=exact, impl="tcgen05")
+    torch.cuda.synchronize()
+    assert _lib.device_error() == 0
+    b = K.redundancy_logits(k, bt, 0.5, exact=exact, impl="simt")
+    fn = O.raw_redudancy_score if exact else O.lightning_redudancy_score
+    lo, _ = fn(k.cpu(), bt.cpu(), 0.5, 0.4, return_logits=True)
+    a, b, lo = a.float().cpu().reshape(-1), b.float().cpu().reshape(-1), lo.float().reshape(-1)
+    fin = torch.isfinite(b)
+    assert torch.equal(fin, torch.isfinite(a)) and torch.equal(fin, torch.isfinite(lo))
+    scale = b[fin].abs().max()
+    assert scale > 2.0  # the similar keys make the exemption rule matter
+    assert (a[fin] - b[fin]).abs().max() <= 1e-2 * scale
+    assert (a[fin] - lo[fin]).abs().max() <= 2e-2 * scale

@@ -37,6 +37,7 @@ _P, _I, _L, _F, _Z = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 SIGNATURES = {
     "zp_last_error": (C.c_char_p, []),
     "zp_version": (_I, []),
+    "zp_device_error": (_I, [C.POINTER(C.c_int), _I]),
     "zp_store_kv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _L, _L, _I, _P]),
     "zp_store_query": (_I, [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P]),
     "zp_window_score": (_I, [_P, _P, _P, _P, _P, _P] + [_I] * 8 + [_L] * 4 + [_F, _I, _I, _I, _P]),
@@ -77,6 +78,13 @@ def check(rc: int, what: str = ""):
     if rc != 0:
         msg = load().zp_last_error().decode(errors="replace")
         raise ZipageError(f"{what or 'zipage_b200'} failed ({rc}): {msg}")
+
+
+def device_error(reset=True) -> int:
+    """Error word raised by a tcgen05 kernel whose bounded wait ran out (0 = none); synchronises."""
+    code = C.c_int(0)
+    check(load().zp_device_error(C.byref(code), int(reset)), "zp_device_error")
+    return code.value
 
 
 def ptr(t):

@@ -267,6 +267,23 @@ static int redundancy_simt(const RdParams& p, int D, int dtype, cudaStream_t st)
   return ZP_ERR_UNSUPPORTED;
 }
 
+// tcgen05 path (zp_redundancy_tc.cu)
+int redundancy_tc(const void* k_cache, const int32_t* block_table, void* logits_out, float* rowsum,
+                  long long* sub, int L, int B, int NB, int Hkv, int64_t k_stride_layer,
+                  int64_t k_stride_page, float threshold, float eps, int dtype, bool exact,
+                  cudaStream_t st);
+
+// which kernel family a call uses: 1 = tcgen05, 0 = SIMT, <0 = error already set
+static int pick_tc(int impl, int dtype, int D, int BS, const char* who) {
+  const bool can = (dtype == ZP_DTYPE_BF16 || dtype == ZP_DTYPE_F16) && D == 128 && BS == 256;
+  if (impl == ZP_IMPL_SIMT) return 0;
+  if (impl == ZP_IMPL_TCGEN05 && !can) {
+    set_error("%s: the tcgen05 kernels need a 16-bit cache, head_dim 128 and page size 256", who);
+    return ZP_ERR_UNSUPPORTED;
+  }
+  return can ? 1 : 0;
+}
+
 }  // namespace zp
 
 extern "C" int zp_key_norm(const void* k_cache, const int32_t* block_table, void* norm_out, int L,
@@ -302,7 +319,12 @@ extern "C" int zp_redundancy_lightning(const void* k_cache, const int32_t* block
   p.L = L; p.B = B; p.NB = NB; p.Hkv = Hkv; p.BS = BS;
   p.k_stride_layer = k_stride_layer; p.k_stride_page = k_stride_page;
   p.threshold = threshold; p.eps = 1e-6f; p.exact = 0;
-  (void)impl;
+  const int tc = zp::pick_tc(impl, dtype, D, BS, "zp_redundancy_lightning");
+  if (tc < 0) return tc;
+  if (tc)
+    return zp::redundancy_tc(k_cache, block_table, logits_out, nullptr, nullptr, L, B, NB, Hkv,
+                             k_stride_layer, k_stride_page, threshold, 1e-6f, dtype, false,
+                             (cudaStream_t)stream);
   return zp::redundancy_simt(p, D, dtype, (cudaStream_t)stream);
 }
 
@@ -337,8 +359,11 @@ extern "C" int zp_redundancy_exact(const void* k_cache, const int32_t* block_tab
   p.L = L; p.B = B; p.NB = NB; p.Hkv = Hkv; p.BS = BS;
   p.k_stride_layer = k_stride_layer; p.k_stride_page = k_stride_page;
   p.threshold = threshold; p.eps = 1e-6f; p.exact = 1;
-  (void)impl;
-  int rc = zp::redundancy_simt(p, D, dtype, st);
+  const int tc = zp::pick_tc(impl, dtype, D, BS, "zp_redundancy_exact");
+  if (tc < 0) return tc;
+  int rc = tc ? zp::redundancy_tc(k_cache, block_table, logits_out, rowsum, sub, L, B, NB, Hkv,
+                                  k_stride_layer, k_stride_page, threshold, 1e-6f, dtype, true, st)
+              : zp::redundancy_simt(p, D, dtype, st);
   if (rc) return rc;
   const int64_t total = (int64_t)n;
   const int blocks = (int)((total + 255) / 256);

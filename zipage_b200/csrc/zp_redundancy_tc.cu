@@ -1,0 +1,321 @@
+// Key-similarity redundancy on tcgen05 tensor cores (16-bit caches, head_dim 128, page size 256).
+//
+// S = K K^T is a dense contraction: the RAW key tiles (not normalised copies) are staged by TMA
+// (128-byte swizzle, one 64 KB page = 256 keys x 128 dims per stage), multiplied with
+// tcgen05.mma (M = 128 rows, N = 256 columns, K = 128) into fp32 accumulators in TMEM, and the
+// cosine normalisation is applied in the epilogue: S[m,n] = acc[m,n] / (|k_m| |k_n|), with the
+// norms computed from the same shared-memory tile and rounded to T as key_norm does.
+//
+// Roles (192 threads, 1 block per SM): warp 0 = TMA producer and TMEM owner, warp 1 = MMA issuer,
+// warps 2-5 = epilogue (thread <-> TMEM lane <-> similarity row).  A work item is (column page,
+// row half h): 128 rows x 256 columns = 256 TMEM columns; the two halves alternate between the two
+// halves of TMEM, so the MMA of one item overlaps the epilogue of the previous one.
+//   lightning: one block per unit; rows and columns are the same page (A = B tile).
+//   exact:     one block per (unit, row page); the row page stays resident, every page streams by.
+// The epilogue keeps row-wise state only (row sum, last column above the threshold and its value);
+// see zp_redundancy.cu for why that is enough.  The "subtract the exempted entries" step uses
+// 64-bit fixed-point atomics (2^-32 units), so the result does not depend on execution order.
+#include "zp_tc.cuh"
+
+namespace zp {
+
+using namespace tc;
+
+constexpr int RT_THREADS = 192;
+constexpr int RT_PAGE_BYTES = 65536;   // 256 keys x 128 dims x 2 bytes
+constexpr int RT_BLOCK_BYTES = 32768;  // one 64-column block of a page
+constexpr int RT_NBUF = 3;
+
+struct RtParams {
+  const int32_t* block_table;
+  void* logits_out;
+  float* rowsum;
+  long long* sub;
+  int* error_word;
+  int L, B, NB, Hkv;
+  float threshold, eps;
+};
+
+struct __align__(16) RtShared {
+  uint64_t full[RT_NBUF], empty[RT_NBUF], tfull[2], tempty[2], afull, norm_ready, fin_ready;
+  alignas(16) float rn[2][256];
+  float s_sum[256];
+  unsigned long long s_sub[256];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// sum of squares of one 128-element row of a swizzled [256][128] tile (two 64-column blocks)
+template <typename T>
+__device__ __forceinline__ float row_sumsq(const unsigned char* tile, int row) {
+  float ss = 0.f;
+#pragma unroll
+  for (int blk = 0; blk < 2; ++blk) {
+    const unsigned char* base = tile + blk * RT_BLOCK_BYTES + row * 128;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int4 raw = *reinterpret_cast<const int4*>(base + ((c ^ (row & 7)) << 4));
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const float x = Elem<T>::to_f32(e[j]); ss = fmaf(x, x, ss); }
+    }
+  }
+  return ss;
+}
+
+template <typename T, bool EXACT>
+__global__ void __launch_bounds__(RT_THREADS, 1)
+redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* bufs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  RtShared& sh = *reinterpret_cast<RtShared*>(bufs + RT_NBUF * RT_PAGE_BYTES);
+  constexpr int NS = EXACT ? 2 : 3;      // ring of streaming stages
+  constexpr int RING0 = EXACT ? 1 : 0;   // buffer 0 holds the resident row page in the exact form
+  auto stage_ptr = [&](int s) { return bufs + (RING0 + s) * RT_PAGE_BYTES; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int unit = EXACT ? blockIdx.x / p.NB : blockIdx.x;
+  const int mp = EXACT ? blockIdx.x % p.NB : 0;
+  const int h = unit % p.Hkv, b = (unit / p.Hkv) % p.B, l = unit / (p.Hkv * p.B);
+  const int32_t* table = p.block_table + (int64_t)b * p.NB;
+  PageRef rowpage{0, true, false};
+  if (EXACT) {
+    rowpage = decode_page(table[mp]);
+    if (!rowpage.valid) return;  // whole block; the finalize kernel writes -inf for padded pages
+  }
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < RT_NBUF; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 2); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 4); }
+    mbar_init(&sh.afull, 1);
+    mbar_init(&sh.norm_ready, 128);
+    mbar_init(&sh.fin_ready, 128);
+    sh.abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&sh.tmem_base, 512);
+    tmem_relinquish();
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = sh.tmem_base;
+  volatile int* abortp = &sh.abort_flag;
+  constexpr uint32_t IDESC = idesc_f16(UmmaFmt<T>::fmt, 128, 256);
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      prefetch_tensormap(&tmK);
+      if (EXACT) {
+        mbar_arrive_expect_tx(&sh.afull, RT_PAGE_BYTES);
+        tma_load_5d(bufs, &tmK, &sh.afull, 0, h, 0, rowpage.id, l);
+        tma_load_5d(bufs + RT_BLOCK_BYTES, &tmK, &sh.afull, 64, h, 0, rowpage.id, l);
+      }
+      int t = 0;
+      for (int pg = 0; pg < p.NB; ++pg) {
+        const PageRef cp = decode_page(table[pg]);
+        if (!cp.valid) continue;
+        const int s = t % NS, k = t / NS;
+        if (!mbar_wait(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 101)) break;
+        mbar_arrive_expect_tx(&sh.full[s], RT_PAGE_BYTES);
+        tma_load_5d(stage_ptr(s), &tmK, &sh.full[s], 0, h, 0, cp.id, l);
+        tma_load_5d(stage_ptr(s) + RT_BLOCK_BYTES, &tmK, &sh.full[s], 64, h, 0, cp.id, l);
+        ++t;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      bool ok = true;
+      if (EXACT) ok = mbar_wait(&sh.afull, 0, abortp, p.error_word, 201);
+      int t = 0;
+      for (int pg = 0; ok && pg < p.NB; ++pg) {
+        if (table[pg] == -1) continue;
+        const int s = t % NS, k = t / NS;
+        if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 202)) break;
+        const uint32_t b_addr = smem_u32(stage_ptr(s));
+        const uint32_t a_base = EXACT ? smem_u32(bufs) : b_addr;
+        for (int hh = 0; hh < 2; ++hh) {
+          if (!mbar_wait(&sh.tempty[hh], (t & 1) ^ 1, abortp, p.error_word, 203)) { ok = false; break; }
+          fence_after_sync();
+          umma_k128(tmem_base + hh * 256, a_base + hh * 16384, RT_BLOCK_BYTES, b_addr, RT_BLOCK_BYTES, IDESC);
+          umma_commit(&sh.tfull[hh]);
+        }
+        umma_commit(&sh.empty[s]);
+        ++t;
+      }
+    }
+  } else {
+    // ---------------- epilogue: thread r <-> rows r (half 0) and r + 128 (half 1) ----------------
+    const int q = warp & 3;           // TMEM lane quadrant this warp may read
+    const int r = q * 32 + lane;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const float eps_t = round_to<T>(p.eps);
+    float rsum[2] = {0.f, 0.f}, bval[2] = {0.f, 0.f}, rn_m[2] = {0.f, 0.f}, thr_m[2] = {0.f, 0.f};
+    int bcol[2] = {-1, -1};
+    bool ok = true;
+    if (EXACT) {
+      ok = mbar_wait(&sh.afull, 0, abortp, p.error_word, 301);
+      if (ok) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const float nrm = fmaxf(round_to<T>(sqrtf(row_sumsq<T>(bufs, r + 128 * hh))), eps_t);
+          rn_m[hh] = 1.f / nrm;
+          thr_m[hh] = p.threshold * nrm;
+        }
+      }
+    }
+    int t = 0;
+    for (int pg = 0; ok && pg < p.NB; ++pg) {
+      if (table[pg] == -1) {
+        if (!EXACT) {  // padded page: logits -inf
+          T* lout = reinterpret_cast<T*>(p.logits_out) + ((int64_t)unit * p.NB + pg) * 256;
+          lout[r] = Elem<T>::from_f32(-INFINITY);
+          lout[r + 128] = Elem<T>::from_f32(-INFINITY);
+        }
+        continue;
+      }
+      const int s = t % NS, k = t / NS;
+      if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 302)) break;
+      float* rn = sh.rn[t & 1];
+      float nrm[2];
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        nrm[hh] = fmaxf(round_to<T>(sqrtf(row_sumsq<T>(stage_ptr(s), r + 128 * hh))), eps_t);
+        rn[r + 128 * hh] = 1.f / nrm[hh];
+        if (!EXACT) sh.s_sub[r + 128 * hh] = 0ull;
+      }
+      mbar_arrive(&sh.norm_ready);
+      if (!mbar_wait(&sh.norm_ready, t & 1, abortp, p.error_word, 303)) break;
+      if (r == 0) mbar_arrive(&sh.empty[s]);  // every epilogue thread is done reading the stage
+      if (!EXACT) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          rn_m[hh] = 1.f / nrm[hh]; thr_m[hh] = p.threshold * nrm[hh];
+          rsum[hh] = 0.f; bcol[hh] = -1; bval[hh] = 0.f;
+        }
+      }
+      const bool diag_page = EXACT ? (pg == mp) : true;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        if (!mbar_wait(&sh.tfull[hh], t & 1, abortp, p.error_word, 304)) { ok = false; break; }
+        fence_after_sync();
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        for (int c = 0; c < 8; ++c) {
+          float v[32];
+          tmem_ld32(lane_base + hh * 256 + c * 32, v);
+          const float4* rn4 = reinterpret_cast<const float4*>(rn + c * 32);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 f = rn4[j];
+            v[4 * j] *= f.x; v[4 * j + 1] *= f.y; v[4 * j + 2] *= f.z; v[4 * j + 3] *= f.w;
+          }
+          if (diag_page && c == hh * 4 + q) {  // warp-uniform: the chunk that holds this warp's diagonal
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = (j == lane) ? 0.f : v[j];
+          }
+          float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            s0 += v[j]; s1 += v[j + 1]; s2 += v[j + 2]; s3 += v[j + 3];
+            m0 = fmaxf(m0, v[j]); m1 = fmaxf(m1, v[j + 1]); m2 = fmaxf(m2, v[j + 2]); m3 = fmaxf(m3, v[j + 3]);
+          }
+          if (fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) > thr_m[hh]) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (v[j] > thr_m[hh]) { bcol[hh] = pg * 256 + c * 32 + j; bval[hh] = v[j]; }
+          }
+        }
+        rsum[hh] += (s0 + s1) + (s2 + s3);
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.tempty[hh]);
+      }
+      if (!ok) break;
+      if (!EXACT) {
+        // page done: subtract the exempted entries, write the page's logits
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh)
+          if (bcol[hh] >= 0) {
+            const long long fx = __float2ll_rn(bval[hh] * rn_m[hh] * 4294967296.f);
+            atomicAdd(&sh.s_sub[bcol[hh] - pg * 256], (unsigned long long)fx);
+          }
+        mbar_arrive(&sh.fin_ready);
+        if (!mbar_wait(&sh.fin_ready, t & 1, abortp, p.error_word, 305)) break;
+        T* lout = reinterpret_cast<T*>(p.logits_out) + ((int64_t)unit * p.NB + pg) * 256;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const float sub = (float)((double)(long long)sh.s_sub[r + 128 * hh] * (1.0 / 4294967296.0));
+          lout[r + 128 * hh] = Elem<T>::from_f32(rsum[hh] * rn_m[hh] - sub);
+        }
+      }
+      ++t;
+    }
+    if (EXACT && ok && !*abortp) {
+      const int64_t base = (int64_t)unit * p.NB * 256;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        p.rowsum[base + mp * 256 + r + 128 * hh] = rsum[hh] * rn_m[hh];
+        if (bcol[hh] >= 0) {
+          const long long fx = __float2ll_rn(bval[hh] * rn_m[hh] * 4294967296.f);
+          atomicAdd(reinterpret_cast<unsigned long long*>(p.sub + base + bcol[hh]), (unsigned long long)fx);
+        }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <typename T>
+static int launch_redundancy_tc(const void* k_cache, const RtParams& p, int64_t k_stride_layer,
+                                int64_t k_stride_page, bool exact, cudaStream_t st) {
+  CUtensorMap tm;
+  const uint64_t pages = p.L > 1 ? (uint64_t)(k_stride_layer / k_stride_page) : (1ull << 30);
+  const uint64_t dims[5] = {128, (uint64_t)p.Hkv, 256, pages, (uint64_t)p.L};
+  const uint64_t strides[4] = {128, (uint64_t)p.Hkv * 128, (uint64_t)k_stride_page,
+                               (uint64_t)(p.L > 1 ? k_stride_layer : k_stride_page)};
+  const uint32_t box[5] = {64, 1, 256, 1, 1};
+  int rc = make_tensor_map_5d(&tm, UmmaFmt<T>::tm, k_cache, dims, strides, box, sizeof(T));
+  if (rc) return rc;
+  const size_t smem = RT_NBUF * RT_PAGE_BYTES + sizeof(RtShared) + 1024;
+  const int units = p.L * p.B * p.Hkv;
+  cudaError_t e;
+  if (exact) {
+    auto kern = redundancy_tc_kernel<T, true>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) kern<<<units * p.NB, RT_THREADS, smem, st>>>(tm, p);
+  } else {
+    auto kern = redundancy_tc_kernel<T, false>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) kern<<<units, RT_THREADS, smem, st>>>(tm, p);
+  }
+  if (e != cudaSuccess) { set_error("zp_redundancy(tcgen05): %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
+  return check_launch("zp_redundancy(tcgen05)");
+}
+
+// Called by the C entry points in zp_redundancy.cu.
+int redundancy_tc(const void* k_cache, const int32_t* block_table, void* logits_out, float* rowsum,
+                  long long* sub, int L, int B, int NB, int Hkv, int64_t k_stride_layer,
+                  int64_t k_stride_page, float threshold, float eps, int dtype, bool exact,
+                  cudaStream_t st) {
+  RtParams p;
+  p.block_table = block_table; p.logits_out = logits_out; p.rowsum = rowsum; p.sub = sub;
+  p.error_word = device_error_word();
+  p.L = L; p.B = B; p.NB = NB; p.Hkv = Hkv; p.threshold = threshold; p.eps = eps;
+  if (!p.error_word) { set_error("zp_redundancy(tcgen05): no device error word"); return ZP_ERR_CUDA; }
+  if (dtype == ZP_DTYPE_BF16)
+    return launch_redundancy_tc<__nv_bfloat16>(k_cache, p, k_stride_layer, k_stride_page, exact, st);
+  if (dtype == ZP_DTYPE_F16)
+    return launch_redundancy_tc<__half>(k_cache, p, k_stride_layer, k_stride_page, exact, st);
+  set_error("zp_redundancy(tcgen05): 16-bit caches only");
+  return ZP_ERR_UNSUPPORTED;
+}
+
+}  // namespace zp
