@@ -280,3 +280,29 @@ def test_redundancy_tcgen05_matches_simt_and_oracle(dtype, exact):
     assert scale > 2.0  # the similar keys make the exemption rule matter
     assert (a[fin] - b[fin]).abs().max() <= 1e-2 * scale
     assert (a[fin] - lo[fin]).abs().max() <= 2e-2 * scale
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("Hq,Hkv,QCL,reduced", [(8, 2, 32, "mean"), (4, 2, 16, "mean"), (2, 2, 16, "max"),
+                                                 (16, 2, 16, "mean")])
+def test_window_score_tcgen05_matches_simt_and_oracle(dtype, Hq, Hkv, QCL, reduced):
+    from oracle import zipage_oracle as O
+    from zipage_b200 import _lib, kernel as K
+    from zipage_b200.synthetic import make_compress_workload
+    dev = _gpu()
+    w = make_compress_workload(B=5, L=3, Hkv=Hkv, Hq=Hq, QCL=QCL, budget=2, pages_per_seq=[3, 4, 3, 5, 3],
+                               dtype=dtype, device=dev, seed=31, spare_pages=2)
+    a = K.attention_score(w.kv_cache[0], w.query_cache, w.query_ids, w.block_tables, reduced=reduced,
+                          impl="tcgen05")
+    torch.cuda.synchronize()
+    assert _lib.device_error() == 0
+    b = K.attention_score(w.kv_cache[0], w.query_cache, w.query_ids, w.block_tables, reduced=reduced,
+                          impl="simt")
+    o = O.attention_score(w.kv_cache[0].cpu(), w.query_cache.cpu(), w.query_ids.cpu(),
+                          w.block_tables.cpu(), reduced=reduced)
+    a, b, o = a.float().cpu(), b.float().cpu(), o.float()
+    scale = o.abs().max()
+    assert (a - b).abs().max() <= 2e-2 * scale
+    assert (a - o).abs().max() <= 2e-2 * scale
+    # the bulk agrees to the last bit of T; only isolated roundings differ
+    assert (a != o).float().mean() < 0.02

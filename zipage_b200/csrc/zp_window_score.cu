@@ -84,7 +84,6 @@ __global__ void __launch_bounds__(WS_THREADS, 1) window_score_kernel(const WsPar
   constexpr int LD = D + 4;
   extern __shared__ __align__(16) float smem[];
   const int G = p.Hq / p.Hkv;
-  const int R = G * p.QCL;                       // rows r = i*G + g
   const int ICH = min(p.QCL, WS_RC_MAX / G);     // window rows per chunk
   const int RC = ICH * G;                        // rows per chunk
   const int nchunk = (p.QCL + ICH - 1) / ICH;
@@ -292,6 +291,13 @@ int window_score_simt(const WsParams& p, int D, int dtype, cudaStream_t stream) 
   return ZP_ERR_UNSUPPORTED;
 }
 
+// tcgen05 path (zp_window_score_tc.cu)
+bool window_score_tc_supported(int dtype, int D, int BS, int Hq, int Hkv, int QCL, bool want_logits);
+int window_score_tc(const void* k_cache, const void* q_cache, const int32_t* seq_idx,
+                    const int32_t* block_table, void* scores_out, int L, int B, int NB, int Hq, int Hkv,
+                    int QCL, int64_t k_stride_layer, int64_t k_stride_page, int64_t q_stride_layer,
+                    int64_t q_stride_seq, float scale, int reduce_mode, int dtype, cudaStream_t st);
+
 }  // namespace zp
 
 extern "C" int zp_window_score(const void* k_cache, const void* query_cache, const int32_t* seq_idx,
@@ -317,6 +323,19 @@ extern "C" int zp_window_score(const void* k_cache, const void* query_cache, con
   p.k_stride_layer = k_stride_layer; p.k_stride_page = k_stride_page;
   p.q_stride_layer = q_stride_layer; p.q_stride_seq = q_stride_seq;
   p.scale = softmax_scale; p.reduce_mode = reduce_mode;
-  (void)impl;
+  ZP_REQUIRE(softmax_scale > 0.f, "zp_window_score: softmax_scale must be positive");
+  const bool can_tc = zp::window_score_tc_supported(dtype, D, BS, Hq, Hkv, QCL, logits_out != nullptr) &&
+                      ((uintptr_t)query_cache % 16 == 0) &&
+                      (q_stride_layer * zp::dtype_size(dtype)) % 16 == 0 &&
+                      (q_stride_seq * zp::dtype_size(dtype)) % 16 == 0;
+  if (impl == ZP_IMPL_TCGEN05 && !can_tc) {
+    zp::set_error("zp_window_score: the tcgen05 kernel needs a 16-bit cache, head_dim 128, page size "
+                  "256, a power-of-two group size with G*QCL <= 128, and no logits output");
+    return ZP_ERR_UNSUPPORTED;
+  }
+  if (impl != ZP_IMPL_SIMT && can_tc)
+    return zp::window_score_tc(k_cache, query_cache, seq_idx, block_table, scores_out, L, B, NB, Hq,
+                               Hkv, QCL, k_stride_layer, k_stride_page, q_stride_layer, q_stride_seq,
+                               softmax_scale, reduce_mode, dtype, (cudaStream_t)stream);
   return zp::window_score_simt(p, D, dtype, (cudaStream_t)stream);
 }
