@@ -172,6 +172,23 @@ int zp_paged_decode(const void* q, const void* k_cache, const void* v_cache,
                     float softmax_scale, int dtype, void* workspace, size_t workspace_bytes,
                     void* stream);
 
+/* No counterpart in the reference.  zp_paged_decode for callers that cannot hand over a workspace
+ * because they must not allocate device memory when they decode (an engine that gave all free
+ * memory to the KV cache, a latency-critical thread that cannot take cudaMalloc's implicit
+ * synchronisation).  The split-KV partial results go to a 4 MiB array built into the library
+ * (every GPU that loads the library holds it until exit); the call performs no allocation of any
+ * kind.  Batches whose split scratch exceeds zp_paged_decode_noalloc_max_scratch_bytes() are
+ * rejected with ZP_ERR_WORKSPACE.  The first call on each device looks up the array's device
+ * address (cudaGetSymbolAddress) and should therefore be made before any stream capture starts.
+ * All calls on a device share the array: it keeps the last call's partials (every entry a call
+ * reads is written by that call first, so nothing needs clearing), and two calls whose kernels
+ * overlap on the GPU (different streams) race on it — serialise them. */
+size_t zp_paged_decode_noalloc_max_scratch_bytes(void);
+int zp_paged_decode_noalloc(const void* q, const void* k_cache, const void* v_cache,
+                            const int32_t* cache_seqlens, const int32_t* block_table, void* out,
+                            int B, int NBmax, int Hq, int Hkv, int D, int BS,
+                            int64_t kv_stride_page, float softmax_scale, int dtype, void* stream);
+
 /* Replaces flash_attn_varlen_func as called at zipage/layers/attention.py:79-93: causal
  * (bottom-right aligned) variable-length attention.  q,out [sum_q, Hq, D].  block_table == NULL:
  * k,v dense [sum_k, Hkv, D]; else k,v are the paged caches [P, BS, Hkv, D] and block_table

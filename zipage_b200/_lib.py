@@ -52,6 +52,8 @@ SIGNATURES = {
     "zp_update_tables": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "zp_paged_decode_workspace_bytes": (_Z, [_I] * 4),
     "zp_paged_decode": (_I, [_P] * 6 + [_I] * 6 + [_L, _F, _I, _P, _Z, _P]),
+    "zp_paged_decode_noalloc_max_scratch_bytes": (_Z, []),
+    "zp_paged_decode_noalloc": (_I, [_P] * 6 + [_I] * 6 + [_L, _F, _I, _P]),
     "zp_varlen_prefill": (_I, [_P] * 7 + [_I] * 7 + [_L, _F, _I, _P]),
 }
 

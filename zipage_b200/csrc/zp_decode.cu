@@ -246,3 +246,61 @@ extern "C" int zp_paged_decode(const void* q, const void* k_cache, const void* v
   ZP_DISPATCH_DTYPE(dtype, T, { return zp::dispatch_decode<T>(a, D, G, st); });
   return ZP_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of zp_paged_decode.
+//
+// Some hosts of this library must not allocate device memory at the moment they decode: a serving
+// loop whose memory pool is fully handed out to the KV cache (the engine sizes the cache from all
+// free memory at start-up), a real-time thread where cudaMalloc's implicit device synchronisation
+// is unacceptable, or a caller running while a CUDA graph is being captured on another stream.
+// For them the split-KV partial results live in the fixed device array below instead of in a
+// caller-provided workspace.
+namespace zp {
+constexpr size_t DEC_STATIC_SCRATCH_BYTES = 4u << 20;  // 4 MiB per GPU that loads the library
+static __device__ __align__(256) unsigned char g_decode_scratch[DEC_STATIC_SCRATCH_BYTES];
+
+constexpr int DEC_MAX_DEVICES = 64;
+static void* g_decode_scratch_ptr[DEC_MAX_DEVICES];  // device address of the array, per device
+}  // namespace zp
+
+extern "C" size_t zp_paged_decode_noalloc_max_scratch_bytes(void) { return zp::DEC_STATIC_SCRATCH_BYTES; }
+
+extern "C" int zp_paged_decode_noalloc(const void* q, const void* k_cache, const void* v_cache,
+                                       const int32_t* cache_seqlens, const int32_t* block_table,
+                                       void* out, int B, int NBmax, int Hq, int Hkv, int D, int BS,
+                                       int64_t kv_stride_page, float softmax_scale, int dtype,
+                                       void* stream) {
+  if (B == 0) return ZP_OK;
+  ZP_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "zp_paged_decode_noalloc: Hq must be a multiple of Hkv");
+  // the same split choice as zp_paged_decode makes when given scratch
+  const int nsplit = zp::pick_splits(B, Hkv, NBmax);
+  const size_t need = nsplit > 1
+      ? (size_t)B * Hkv * nsplit * zp::gp_of(Hq / Hkv) * (D + 2) * sizeof(float) : 0;
+  if (need > zp::DEC_STATIC_SCRATCH_BYTES) {
+    zp::set_error("zp_paged_decode_noalloc: this batch needs %zu bytes of split scratch, the built-in "
+                  "array holds %zu; use zp_paged_decode with a caller workspace",
+                  need, zp::DEC_STATIC_SCRATCH_BYTES);
+    return ZP_ERR_WORKSPACE;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= zp::DEC_MAX_DEVICES) {
+    zp::set_error("zp_paged_decode_noalloc: cannot identify the current device");
+    return ZP_ERR_CUDA;
+  }
+  // Set-up, once per device, with that device current: the array's name is a host-side handle,
+  // the address a kernel can use has to be asked for.
+  void* scratch = __atomic_load_n(&zp::g_decode_scratch_ptr[dev], __ATOMIC_ACQUIRE);
+  if (!scratch) {
+    e = cudaGetSymbolAddress(&scratch, zp::g_decode_scratch);
+    if (e != cudaSuccess || !scratch) {
+      zp::set_error("zp_paged_decode_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return ZP_ERR_CUDA;
+    }
+    __atomic_store_n(&zp::g_decode_scratch_ptr[dev], scratch, __ATOMIC_RELEASE);
+  }
+  return zp_paged_decode(q, k_cache, v_cache, cache_seqlens, block_table, out, B, NBmax, Hq, Hkv, D,
+                         BS, kv_stride_page, softmax_scale, dtype, scratch,
+                         zp::DEC_STATIC_SCRATCH_BYTES, stream);
+}
