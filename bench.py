@@ -109,12 +109,12 @@ class ClockSampler:
 
 def cpu_baseline_sample(variant, global_score, threads):
     """The oracle (CPU restatement of the reference's PyTorch formulation) on a bounded sample of
-    the same workload: L=1, B=2 sequences of 9 pages, 8 KV heads, bf16."""
+    the same workload: L=2 layers, B=16 sequences of 9 pages, 8 KV heads, bf16 (256 units)."""
     import torch
     from oracle import zipage_oracle as O
     from zipage_b200.synthetic import algorithmic_bytes_per_unit, make_compress_workload
     torch.set_num_threads(threads)
-    Ls, Bs = 1, 2
+    Ls, Bs = 2, 16
     w = make_compress_workload(Bs, Ls, HKV, HQ, D, QCL, BUDGET, dtype=torch.bfloat16, device="cpu",
                                seed=7, with_score_cache=global_score)
     ocfg = O.CompressConfig(budget_blocks=BUDGET, query_cache_len=QCL, use_global_score=global_score,
@@ -167,9 +167,9 @@ def run_reference(args):
         "data": "synthetic",
         "config": {"workload": "compression op, Qwen3-8B attention shapes, 9->8 pages, window 32, "
                                f"pool {POOL}, lambda {LAMBDA}, {args.variant} redundancy (config 2)",
-                   "sample": "L=1, B=2 sequences x 8 KV heads (16 units) per step"},
+                   "sample": "L=2, B=16 sequences x 8 KV heads (256 units) per step"},
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": "oracle.compress on L=1,B=2,Hkv=8,9 pages,bf16; median of 2 after 1 warm-up"},
+                         "sample": "oracle.compress on L=2,B=16,Hkv=8,9 pages,bf16 (256 units); median of 2 after 1 warm-up"},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
@@ -322,7 +322,7 @@ def main():
             threads = os.cpu_count() or 1
             gbs, secs, cu = cpu_baseline_sample(args.variant, args.global_score, threads)
             line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
-                                    "sample": f"oracle.compress on {cu} units (L=1,B=2,Hkv=8), {secs:.2f}s"}
+                                    "sample": f"oracle.compress on {cu} units (L=2,B=16,Hkv=8,9 pages,bf16), {secs:.2f}s per pass"}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -6,10 +6,12 @@
 // cosine normalisation is applied in the epilogue: S[m,n] = acc[m,n] / (|k_m| |k_n|), with the
 // norms computed from the same shared-memory tile and rounded to T as key_norm does.
 //
-// Roles (192 threads, 1 block per SM): warp 0 = TMA producer and TMEM owner, warp 1 = MMA issuer,
-// warps 2-5 = epilogue (thread <-> TMEM lane <-> similarity row).  A work item is (column page,
-// row half h): 128 rows x 256 columns = 256 TMEM columns; the two halves alternate between the two
-// halves of TMEM, so the MMA of one item overlaps the epilogue of the previous one.
+// Roles (320 threads, 1 block per SM): warp 0 = TMA producer and TMEM owner, warp 1 = MMA issuer,
+// warps 2-9 = epilogue (thread <-> TMEM lane <-> similarity row; warps w and w+4 share a lane
+// quadrant and split the 256 columns of an item).  A work item is (column page, row half h): 128
+// rows x 256 columns = 256 TMEM columns; the two halves alternate between the two halves of TMEM,
+// so the MMA of one item overlaps the epilogue of the previous one; TMEM loads are software-
+// pipelined (the next 32-column chunk is in flight while one is processed).
 //   lightning: one block per unit; rows and columns are the same page (A = B tile).
 //   exact:     one block per (unit, row page); the row page stays resident, every page streams by.
 // The epilogue keeps row-wise state only (row sum, last column above the threshold and its value);
@@ -21,7 +23,7 @@ namespace zp {
 
 using namespace tc;
 
-constexpr int RT_THREADS = 192;
+constexpr int RT_THREADS = 320;
 constexpr int RT_PAGE_BYTES = 65536;   // 256 keys x 128 dims x 2 bytes
 constexpr int RT_BLOCK_BYTES = 32768;  // one 64-column block of a page
 constexpr int RT_NBUF = 3;
@@ -37,10 +39,12 @@ struct RtParams {
 };
 
 struct __align__(16) RtShared {
-  uint64_t full[RT_NBUF], empty[RT_NBUF], tfull[2], tempty[2], afull, norm_ready, fin_ready;
-  alignas(16) float rn[2][256];
-  float s_sum[256];
-  unsigned long long s_sub[256];
+  uint64_t full[RT_NBUF], empty[RT_NBUF], tfull[2], tempty[2], afull, sync_bar;
+  alignas(16) float rn[2][256];     // 1 / |k| of the column page (double-buffered over pages)
+  float s_sum[256];                 // combined row sums of a page (lightning)
+  float pb_sum[256], pb_val[256];   // partials of the upper column group, rows r and r + 128
+  int pb_col[256];
+  unsigned long long s_sub[256];    // fixed-point sums of exempted entries (lightning)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -86,10 +90,9 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < RT_NBUF; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 2); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 4); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 8); }
     mbar_init(&sh.afull, 1);
-    mbar_init(&sh.norm_ready, 128);
-    mbar_init(&sh.fin_ready, 128);
+    mbar_init(&sh.sync_bar, 256);
     sh.abort_flag = 0;
     fence_mbar_init();
   }
@@ -148,13 +151,23 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
       }
     }
   } else {
-    // ---------------- epilogue: thread r <-> rows r (half 0) and r + 128 (half 1) ----------------
-    const int q = warp & 3;           // TMEM lane quadrant this warp may read
+    // ---------------- epilogue ----------------
+    // thread (grp, r): rows r (half 0) and r + 128 (half 1) of every item, columns grp*128 .. +127
+    const int q = warp & 3;            // TMEM lane quadrant this warp may read
+    const int grp = (warp - 2) >> 2;   // column group
     const int r = q * 32 + lane;
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const int myrow = grp * 128 + r;   // the row this thread normalises / writes
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + grp * 128;
     const float eps_t = round_to<T>(p.eps);
     float rsum[2] = {0.f, 0.f}, bval[2] = {0.f, 0.f}, rn_m[2] = {0.f, 0.f}, thr_m[2] = {0.f, 0.f};
     int bcol[2] = {-1, -1};
+    uint32_t ph = 0;                   // phase of sync_bar (all 256 epilogue threads in lock step)
+    auto sync_epilogue = [&](int where) -> bool {
+      mbar_arrive(&sh.sync_bar);
+      const bool ok_ = mbar_wait(&sh.sync_bar, ph & 1, abortp, p.error_word, where);
+      ++ph;
+      return ok_;
+    };
     bool ok = true;
     if (EXACT) {
       ok = mbar_wait(&sh.afull, 0, abortp, p.error_word, 301);
@@ -170,30 +183,21 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
     int t = 0;
     for (int pg = 0; ok && pg < p.NB; ++pg) {
       if (table[pg] == -1) {
-        if (!EXACT) {  // padded page: logits -inf
-          T* lout = reinterpret_cast<T*>(p.logits_out) + ((int64_t)unit * p.NB + pg) * 256;
-          lout[r] = Elem<T>::from_f32(-INFINITY);
-          lout[r + 128] = Elem<T>::from_f32(-INFINITY);
-        }
+        if (!EXACT)  // padded page: logits -inf
+          reinterpret_cast<T*>(p.logits_out)[((int64_t)unit * p.NB + pg) * 256 + myrow] = Elem<T>::from_f32(-INFINITY);
         continue;
       }
       const int s = t % NS, k = t / NS;
       if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 302)) break;
       float* rn = sh.rn[t & 1];
-      float nrm[2];
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        nrm[hh] = fmaxf(round_to<T>(sqrtf(row_sumsq<T>(stage_ptr(s), r + 128 * hh))), eps_t);
-        rn[r + 128 * hh] = 1.f / nrm[hh];
-        if (!EXACT) sh.s_sub[r + 128 * hh] = 0ull;
-      }
-      mbar_arrive(&sh.norm_ready);
-      if (!mbar_wait(&sh.norm_ready, t & 1, abortp, p.error_word, 303)) break;
-      if (r == 0) mbar_arrive(&sh.empty[s]);  // every epilogue thread is done reading the stage
+      rn[myrow] = 1.f / fmaxf(round_to<T>(sqrtf(row_sumsq<T>(stage_ptr(s), myrow))), eps_t);
+      if (!EXACT) sh.s_sub[myrow] = 0ull;
+      if (!sync_epilogue(303)) break;
+      if (myrow == 0) mbar_arrive(&sh.empty[s]);  // every epilogue thread is done reading the stage
       if (!EXACT) {
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          rn_m[hh] = 1.f / nrm[hh]; thr_m[hh] = p.threshold * nrm[hh];
+          rn_m[hh] = rn[r + 128 * hh]; thr_m[hh] = p.threshold / rn_m[hh];
           rsum[hh] = 0.f; bcol[hh] = -1; bval[hh] = 0.f;
         }
       }
@@ -202,17 +206,19 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
       for (int hh = 0; hh < 2; ++hh) {
         if (!mbar_wait(&sh.tfull[hh], t & 1, abortp, p.error_word, 304)) { ok = false; break; }
         fence_after_sync();
+        const uint32_t tbase = lane_base + hh * 256;
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-        for (int c = 0; c < 8; ++c) {
+        auto process = [&](const uint32_t (&raw)[32], int c) {
+          const int cg = grp * 4 + c;  // chunk index within the 256 columns
+          const float4* rn4 = reinterpret_cast<const float4*>(rn + cg * 32);
           float v[32];
-          tmem_ld32(lane_base + hh * 256 + c * 32, v);
-          const float4* rn4 = reinterpret_cast<const float4*>(rn + c * 32);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const float4 f = rn4[j];
-            v[4 * j] *= f.x; v[4 * j + 1] *= f.y; v[4 * j + 2] *= f.z; v[4 * j + 3] *= f.w;
+            v[4 * j] = __uint_as_float(raw[4 * j]) * f.x; v[4 * j + 1] = __uint_as_float(raw[4 * j + 1]) * f.y;
+            v[4 * j + 2] = __uint_as_float(raw[4 * j + 2]) * f.z; v[4 * j + 3] = __uint_as_float(raw[4 * j + 3]) * f.w;
           }
-          if (diag_page && c == hh * 4 + q) {  // warp-uniform: the chunk that holds this warp's diagonal
+          if (diag_page && cg == hh * 4 + q) {  // warp-uniform: the chunk that holds this warp's diagonal
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = (j == lane) ? 0.f : v[j];
           }
@@ -225,42 +231,77 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
           if (fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) > thr_m[hh]) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (v[j] > thr_m[hh]) { bcol[hh] = pg * 256 + c * 32 + j; bval[hh] = v[j]; }
+              if (v[j] > thr_m[hh]) { bcol[hh] = pg * 256 + cg * 32 + j; bval[hh] = v[j]; }
           }
-        }
-        rsum[hh] += (s0 + s1) + (s2 + s3);
-        fence_before_sync();
+        };
+        uint32_t ra[32], rb[32];
+        tmem_ld32_issue(tbase, ra);
+        tmem_ld32_wait(ra);
+        tmem_ld32_issue(tbase + 32, rb);
+        process(ra, 0);
+        tmem_ld32_wait(rb);
+        tmem_ld32_issue(tbase + 64, ra);
+        process(rb, 1);
+        tmem_ld32_wait(ra);
+        tmem_ld32_issue(tbase + 96, rb);
+        process(ra, 2);
+        tmem_ld32_wait(rb);
+        fence_before_sync();   // every TMEM read of this item has landed in registers
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh.tempty[hh]);
+        process(rb, 3);
+        rsum[hh] += (s0 + s1) + (s2 + s3);
       }
       if (!ok) break;
       if (!EXACT) {
-        // page done: subtract the exempted entries, write the page's logits
+        // page done: merge the two column groups, subtract the exempted entries, write the logits
+        if (grp == 1) {
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh)
-          if (bcol[hh] >= 0) {
-            const long long fx = __float2ll_rn(bval[hh] * rn_m[hh] * 4294967296.f);
-            atomicAdd(&sh.s_sub[bcol[hh] - pg * 256], (unsigned long long)fx);
+          for (int hh = 0; hh < 2; ++hh) {
+            sh.pb_sum[r + 128 * hh] = rsum[hh]; sh.pb_col[r + 128 * hh] = bcol[hh]; sh.pb_val[r + 128 * hh] = bval[hh];
           }
-        mbar_arrive(&sh.fin_ready);
-        if (!mbar_wait(&sh.fin_ready, t & 1, abortp, p.error_word, 305)) break;
-        T* lout = reinterpret_cast<T*>(p.logits_out) + ((int64_t)unit * p.NB + pg) * 256;
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          const float sub = (float)((double)(long long)sh.s_sub[r + 128 * hh] * (1.0 / 4294967296.0));
-          lout[r + 128 * hh] = Elem<T>::from_f32(rsum[hh] * rn_m[hh] - sub);
         }
+        if (!sync_epilogue(305)) break;
+        if (grp == 0) {
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int row = r + 128 * hh;
+            const float total = rsum[hh] + sh.pb_sum[row];
+            const int bc = sh.pb_col[row] >= 0 ? sh.pb_col[row] : bcol[hh];   // upper columns win
+            const float bv = sh.pb_col[row] >= 0 ? sh.pb_val[row] : bval[hh];
+            sh.s_sum[row] = total * rn_m[hh];
+            if (bc >= 0) {
+              const long long fx = __float2ll_rn(bv * rn_m[hh] * 4294967296.f);
+              atomicAdd(&sh.s_sub[bc - pg * 256], (unsigned long long)fx);
+            }
+          }
+        }
+        if (!sync_epilogue(306)) break;
+        const float sub = (float)((double)(long long)sh.s_sub[myrow] * (1.0 / 4294967296.0));
+        reinterpret_cast<T*>(p.logits_out)[((int64_t)unit * p.NB + pg) * 256 + myrow] =
+            Elem<T>::from_f32(sh.s_sum[myrow] - sub);
       }
       ++t;
     }
     if (EXACT && ok && !*abortp) {
-      const int64_t base = (int64_t)unit * p.NB * 256;
+      if (grp == 1) {
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        p.rowsum[base + mp * 256 + r + 128 * hh] = rsum[hh] * rn_m[hh];
-        if (bcol[hh] >= 0) {
-          const long long fx = __float2ll_rn(bval[hh] * rn_m[hh] * 4294967296.f);
-          atomicAdd(reinterpret_cast<unsigned long long*>(p.sub + base + bcol[hh]), (unsigned long long)fx);
+        for (int hh = 0; hh < 2; ++hh) {
+          sh.pb_sum[r + 128 * hh] = rsum[hh]; sh.pb_col[r + 128 * hh] = bcol[hh]; sh.pb_val[r + 128 * hh] = bval[hh];
+        }
+      }
+      if (sync_epilogue(307) && grp == 0) {
+        const int64_t base = (int64_t)unit * p.NB * 256;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int row = r + 128 * hh;
+          const int bc = sh.pb_col[row] >= 0 ? sh.pb_col[row] : bcol[hh];
+          const float bv = sh.pb_col[row] >= 0 ? sh.pb_val[row] : bval[hh];
+          p.rowsum[base + mp * 256 + row] = (rsum[hh] + sh.pb_sum[row]) * rn_m[hh];
+          if (bc >= 0) {
+            const long long fx = __float2ll_rn(bv * rn_m[hh] * 4294967296.f);
+            atomicAdd(reinterpret_cast<unsigned long long*>(p.sub + base + bc), (unsigned long long)fx);
+          }
         }
       }
     }

@@ -10,15 +10,19 @@
 //            owns one key and sees all window rows, so the max over the query heads of the group
 //            and the mean/max over the window are register-local.
 // Rounding points are the reference's: logits, shifted logits and probabilities are rounded to T
-// (attention_score.py:129-130 and the torch ops at :220-243); exp uses ex2.approx.
-// Roles: warp 0 = TMA producer + TMEM owner, warp 1 = MMA issuer, warps 2-5 = epilogue.
+// (attention_score.py:129-130 and the torch ops at :220-243) — done two at a time with packed
+// 16-bit instructions; exp uses ex2.approx.
+// Roles (320 threads): warp 0 = TMA producer + TMEM owner, warp 1 = MMA issuer, warps 2-9 =
+// epilogue.  Epilogue warps w and w+4 share a TMEM lane quadrant and split the 256 columns of a
+// tile (sweeps 0/1: key slots 0-127 / 128-255; sweep 2: keys 0-127 / 128-255 of the page).  TMEM
+// loads are software-pipelined: the next 32-column chunk is in flight while one is processed.
 #include "zp_tc.cuh"
 
 namespace zp {
 
 using namespace tc;
 
-constexpr int WT_THREADS = 192;
+constexpr int WT_THREADS = 320;
 constexpr int WT_PAGE_BYTES = 65536;
 constexpr int WT_BLOCK_BYTES = 32768;
 constexpr int WT_QBLOCK_BYTES = 16384;  // 128 rows x 128 bytes
@@ -35,11 +39,14 @@ struct WtParams {
 };
 
 struct __align__(16) WtShared {
-  uint64_t full[WT_NS], empty[WT_NS], tfull[2], tempty[2], qfull, stats_ready;
-  alignas(16) float2 stats[128];  // (row maximum in T, 1 / row sum of exp)
+  uint64_t full[WT_NS], empty[WT_NS], tfull[2], tempty[2], qfull, stats_bar;
+  alignas(16) uint32_t colm[64];   // sweep 2, per pair of window rows: packed row maxima (T)
+  alignas(16) float colrz[128];    // sweep 2, per window row: 1 / row sum of exp
+  float part[2][128];              // per column-group partial row maximum / row sum
   uint32_t tmem_base;
   int abort_flag;
 };
+static_assert(sizeof(WtShared) <= 2048, "shared-memory budget: 3 stages + queries + this + 1 KB slack = 227 KB");
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -47,15 +54,30 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-// sum (or max) over window rows of the max over each group of G consecutive columns
-template <int G>
-__device__ __forceinline__ float group_reduce(const float (&p)[32], int ncols, bool use_max, float acc) {
+// Reduce 32 columns held as 16 packed pairs: max over each group of G adjacent columns, then
+// sum (or max) over the groups.  Columns >= ncols are ignored.
+template <typename T, int G>
+__device__ __forceinline__ float group_reduce(const typename Pair<T>::V (&pp)[16], int ncols, bool use_max,
+                                              float acc) {
+  using V = typename Pair<T>::V;
+  if constexpr (G == 1) {
 #pragma unroll
-  for (int j = 0; j < 32; j += G) {
-    float mx = p[j];
+    for (int jp = 0; jp < 16; ++jp) {
+      const float2 f = Pair<T>::unpack(pp[jp]);
+      if (2 * jp < ncols) acc = use_max ? fmaxf(acc, f.x) : acc + f.x;
+      if (2 * jp + 1 < ncols) acc = use_max ? fmaxf(acc, f.y) : acc + f.y;
+    }
+  } else {
+    constexpr int PG = G / 2;  // packed pairs per group
 #pragma unroll
-    for (int g = 1; g < G; ++g) mx = fmaxf(mx, p[j + g]);
-    if (j < ncols) acc = use_max ? fmaxf(acc, mx) : acc + mx;
+    for (int jp = 0; jp < 16; jp += PG) {
+      V m = pp[jp];
+#pragma unroll
+      for (int k = 1; k < PG; ++k) m = __hmax2(m, pp[jp + k]);
+      const float2 f = Pair<T>::unpack(m);
+      const float mx = fmaxf(f.x, f.y);
+      if (2 * jp < ncols) acc = use_max ? fmaxf(acc, mx) : acc + mx;
+    }
   }
   return acc;
 }
@@ -64,6 +86,7 @@ template <typename T>
 __global__ void __launch_bounds__(WT_THREADS, 1)
 window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmQ,
                        const WtParams p) {
+  using V = typename Pair<T>::V;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* bufs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* qbuf = bufs + WT_NS * WT_PAGE_BYTES;
@@ -80,9 +103,9 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < WT_NS; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 4); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 8); }
     mbar_init(&sh.qfull, 1);
-    mbar_init(&sh.stats_ready, 128);
+    mbar_init(&sh.stats_bar, 256);
     sh.abort_flag = 0;
     fence_mbar_init();
   }
@@ -152,102 +175,162 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       }
     }
   } else {
-    const int q = warp & 3;
-    const int r = q * 32 + lane;  // sweeps 0/1: window row r; sweep 2: key slots r and r + 128
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    // ---------------- epilogue ----------------
+    const int q = warp & 3;               // TMEM lane quadrant
+    const int grp = (warp - 2) >> 2;      // 0: columns 0-127 of a tile, 1: columns 128-255
+    const int r = q * 32 + lane;          // TMEM lane: window row (sweeps 0/1) or key (sweep 2)
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + grp * 128;
     const float LOG2E = 1.4426950408889634f;
-    const int my_i = r / G;       // window index of row r
-    float row_max = -INFINITY, row_m = 0.f, row_z = 0.f;
+    const int my_i = r / G;
+    const bool use_max = p.reduce_mode != 0;
+    float row_max = -INFINITY, row_z = 0.f;
+    V m2 = Pair<T>::pack(0.f, 0.f);       // this row's maximum, twice
     T* out = reinterpret_cast<T*>(p.scores_out) + (int64_t)unit * p.NB * 256;
-    // padded pages score exactly 0
-    for (int pg = 0; pg < p.NB; ++pg)
-      if (table[pg] == -1) { out[pg * 256 + r] = Elem<T>::from_f32(0.f); out[pg * 256 + 128 + r] = Elem<T>::from_f32(0.f); }
+    for (int pg = 0; pg < p.NB; ++pg)     // padded pages score exactly 0
+      if (table[pg] == -1) out[pg * 256 + grp * 128 + r] = Elem<T>::from_f32(0.f);
+    const int nch2 = (R + 31) / 32;       // chunks of sweep 2 that hold window rows
+
     for (int tt = 0; tt < ntiles; ++tt) {
       int sweep;
       const int pg = tile_page(tt, sweep);
       const bool last = table[pg] < -1;
       const int buf = tt & 1, u = tt >> 1;
-      if (tt == nvalid) row_m = round_to<T>(row_max * p.scale);
-      if (tt == 2 * nvalid) {
-        sh.stats[r] = make_float2(row_m, 1.f / row_z);
-        mbar_arrive(&sh.stats_ready);
-        if (!mbar_wait(&sh.stats_ready, 0, abortp, p.error_word, 311)) break;
+      if (tt == nvalid) {  // row maximum: combine the two column groups
+        sh.part[grp][r] = row_max;
+        mbar_arrive(&sh.stats_bar);
+        if (!mbar_wait(&sh.stats_bar, 0, abortp, p.error_word, 311)) break;
+        const float m = fmaxf(sh.part[0][r], sh.part[1][r]) * p.scale;
+        m2 = Pair<T>::pack(m, m);
+        mbar_arrive(&sh.stats_bar);  // everyone has read `part` before it is reused
+        if (!mbar_wait(&sh.stats_bar, 1, abortp, p.error_word, 312)) break;
       }
-      if (!mbar_wait(&sh.tfull[buf], u & 1, abortp, p.error_word, 312)) break;
+      if (tt == 2 * nvalid) {  // row sum: combine, publish per-column statistics for sweep 2
+        sh.part[grp][r] = row_z;
+        mbar_arrive(&sh.stats_bar);
+        if (!mbar_wait(&sh.stats_bar, 0, abortp, p.error_word, 313)) break;
+        if (grp == 0) {
+          const float z = sh.part[0][r] + sh.part[1][r];
+          reinterpret_cast<T*>(sh.colm)[r] = reinterpret_cast<const T*>(&m2)[0];
+          sh.colrz[r] = 1.f / z;
+        }
+        mbar_arrive(&sh.stats_bar);
+        if (!mbar_wait(&sh.stats_bar, 1, abortp, p.error_word, 314)) break;
+      }
+      if (!mbar_wait(&sh.tfull[buf], u & 1, abortp, p.error_word, 315)) break;
       fence_after_sync();
-      if (sweep < 2) {
-        // columns = key slots; row r sees slot <= 256 - QCL + i inside the last page
-        const int smax = last ? 256 - p.QCL + my_i : 256;
-        for (int c = 0; c < 8; ++c) {
-          float v[32];
-          tmem_ld32(lane_base + buf * 256 + c * 32, v);
-          const bool partial = c * 32 + 31 > smax;
-          if (sweep == 0) {
-            float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+
+      const uint32_t tbase = lane_base + buf * 256;
+      const int nch = sweep < 2 ? 4 : nch2;
+      // sweeps 0/1: row r sees key slot <= smax; sweep 2: key `slot` is hidden from columns < jmask
+      const int smax = last ? 256 - p.QCL + my_i : 256;
+      const int slot = grp * 128 + r;
+      const int jmask = last ? max(0, slot - (256 - p.QCL)) * G : 0;
+      float acc2 = use_max ? -INFINITY : 0.f;
+
+      auto process = [&](const uint32_t (&raw)[32], int c) {
+        if (sweep == 0) {
+          const int s0 = grp * 128 + c * 32;
+          float m0 = -INFINITY, m1 = -INFINITY, m2_ = -INFINITY, m3 = -INFINITY;
+          if (s0 + 31 > smax) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              if (partial) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) if (c * 32 + j + e > smax) v[j + e] = -INFINITY;
-              }
-              m0 = fmaxf(m0, v[j]); m1 = fmaxf(m1, v[j + 1]); m2 = fmaxf(m2, v[j + 2]); m3 = fmaxf(m3, v[j + 3]);
+            for (int j = 0; j < 32; ++j) {
+              const float x = s0 + j > smax ? -INFINITY : __uint_as_float(raw[j]);
+              m0 = fmaxf(m0, x);
             }
-            row_max = fmaxf(row_max, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
           } else {
-            float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-              float e4[4];
+              m0 = fmaxf(m0, __uint_as_float(raw[j])); m1 = fmaxf(m1, __uint_as_float(raw[j + 1]));
+              m2_ = fmaxf(m2_, __uint_as_float(raw[j + 2])); m3 = fmaxf(m3, __uint_as_float(raw[j + 3]));
+            }
+          }
+          row_max = fmaxf(row_max, fmaxf(fmaxf(m0, m1), fmaxf(m2_, m3)));
+        } else if (sweep == 1) {
+          const int s0 = grp * 128 + c * 32;
+          const bool partial = s0 + 31 > smax;
+          float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float lg = round_to<T>(v[j + e] * p.scale);
-                e4[e] = ex2_approx(round_to<T>(lg - row_m) * LOG2E);
-                if (partial && c * 32 + j + e > smax) e4[e] = 0.f;
+          for (int j = 0; j < 32; j += 4) {
+            const V la = Pair<T>::pack(__uint_as_float(raw[j]) * p.scale, __uint_as_float(raw[j + 1]) * p.scale);
+            const V lb = Pair<T>::pack(__uint_as_float(raw[j + 2]) * p.scale, __uint_as_float(raw[j + 3]) * p.scale);
+            const float2 da = Pair<T>::unpack(__hsub2(la, m2)), db = Pair<T>::unpack(__hsub2(lb, m2));
+            float e0 = ex2_approx(da.x * LOG2E), e1 = ex2_approx(da.y * LOG2E);
+            float e2 = ex2_approx(db.x * LOG2E), e3 = ex2_approx(db.y * LOG2E);
+            if (partial) {
+              if (s0 + j > smax) e0 = 0.f;
+              if (s0 + j + 1 > smax) e1 = 0.f;
+              if (s0 + j + 2 > smax) e2 = 0.f;
+              if (s0 + j + 3 > smax) e3 = 0.f;
+            }
+            z0 += e0; z1 += e1; z2 += e2; z3 += e3;
+          }
+          row_z += (z0 + z1) + (z2 + z3);
+        } else {
+          V pp[16];
+          const uint4* cm4 = reinterpret_cast<const uint4*>(&sh.colm[c * 16]);
+          const float4* rz4 = reinterpret_cast<const float4*>(&sh.colrz[c * 32]);
+#pragma unroll
+          for (int j4 = 0; j4 < 4; ++j4) {   // 4 pairs (8 columns) per step
+            const uint4 cm = cm4[j4];
+            const uint32_t cmv[4] = {cm.x, cm.y, cm.z, cm.w};
+            const float4 rza = rz4[2 * j4], rzb = rz4[2 * j4 + 1];
+            const float rzv[8] = {rza.x, rza.y, rza.z, rza.w, rzb.x, rzb.y, rzb.z, rzb.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int jp = 4 * j4 + k;
+              const V lg = Pair<T>::pack(__uint_as_float(raw[2 * jp]) * p.scale,
+                                         __uint_as_float(raw[2 * jp + 1]) * p.scale);
+              const float2 d = Pair<T>::unpack(__hsub2(lg, *reinterpret_cast<const V*>(&cmv[k])));
+              float e0 = ex2_approx(d.x * LOG2E) * rzv[2 * k];
+              float e1 = ex2_approx(d.y * LOG2E) * rzv[2 * k + 1];
+              if (jmask > 0) {
+                if (c * 32 + 2 * jp < jmask) e0 = 0.f;
+                if (c * 32 + 2 * jp + 1 < jmask) e1 = 0.f;
               }
-              z0 += e4[0]; z1 += e4[1]; z2 += e4[2]; z3 += e4[3];
-            }
-            row_z += (z0 + z1) + (z2 + z3);
-          }
-        }
-      } else {
-        // rows of D = key slots; columns = window rows j = i*G + g
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          const int slot = hh * 128 + r;
-          const int jmask = last ? max(0, slot - (256 - p.QCL)) * G : 0;  // columns below are masked
-          float acc = p.reduce_mode == 0 ? 0.f : -INFINITY;
-          for (int c = 0; c * 32 < R; ++c) {
-            float v[32];
-            tmem_ld32(lane_base + buf * 256 + hh * 128 + c * 32, v);
-            const float4* st4 = reinterpret_cast<const float4*>(&sh.stats[c * 32]);
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const float4 st = st4[j >> 1];
-              const float l0 = round_to<T>(v[j] * p.scale), l1 = round_to<T>(v[j + 1] * p.scale);
-              float p0 = round_to<T>(ex2_approx(round_to<T>(l0 - st.x) * LOG2E) * st.y);
-              float p1 = round_to<T>(ex2_approx(round_to<T>(l1 - st.z) * LOG2E) * st.w);
-              if (c * 32 + j < jmask) p0 = 0.f;
-              if (c * 32 + j + 1 < jmask) p1 = 0.f;
-              v[j] = p0; v[j + 1] = p1;
-            }
-            const int ncols = R - c * 32;
-            const bool um = p.reduce_mode != 0;
-            switch (G) {
-              case 1: acc = group_reduce<1>(v, ncols, um, acc); break;
-              case 2: acc = group_reduce<2>(v, ncols, um, acc); break;
-              case 4: acc = group_reduce<4>(v, ncols, um, acc); break;
-              case 8: acc = group_reduce<8>(v, ncols, um, acc); break;
-              case 16: acc = group_reduce<16>(v, ncols, um, acc); break;
-              default: acc = group_reduce<32>(v, ncols, um, acc); break;
+              pp[jp] = Pair<T>::pack(e0, e1);
             }
           }
-          const float res = p.reduce_mode == 0 ? acc / (float)p.QCL : acc;
-          out[pg * 256 + slot] = Elem<T>::from_f32(res);
+          const int ncols = R - c * 32;
+          switch (G) {
+            case 1: acc2 = group_reduce<T, 1>(pp, ncols, use_max, acc2); break;
+            case 2: acc2 = group_reduce<T, 2>(pp, ncols, use_max, acc2); break;
+            case 4: acc2 = group_reduce<T, 4>(pp, ncols, use_max, acc2); break;
+            case 8: acc2 = group_reduce<T, 8>(pp, ncols, use_max, acc2); break;
+            case 16: acc2 = group_reduce<T, 16>(pp, ncols, use_max, acc2); break;
+            default: acc2 = group_reduce<T, 32>(pp, ncols, use_max, acc2); break;
+          }
         }
+      };
+      auto release = [&]() {  // all TMEM reads of this tile have landed in registers
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.tempty[buf]);
+      };
+
+      uint32_t ra[32], rb[32];
+      tmem_ld32_issue(tbase, ra);
+      tmem_ld32_wait(ra);
+      if (nch > 1) tmem_ld32_issue(tbase + 32, rb); else release();
+      process(ra, 0);
+      if (nch > 1) {
+        tmem_ld32_wait(rb);
+        if (nch > 2) tmem_ld32_issue(tbase + 64, ra); else release();
+        process(rb, 1);
       }
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh.tempty[buf]);
+      if (nch > 2) {
+        tmem_ld32_wait(ra);
+        if (nch > 3) tmem_ld32_issue(tbase + 96, rb); else release();
+        process(ra, 2);
+      }
+      if (nch > 3) {
+        tmem_ld32_wait(rb);
+        release();
+        process(rb, 3);
+      }
+      if (sweep == 2) {
+        const float res = use_max ? acc2 : acc2 / (float)p.QCL;
+        out[pg * 256 + slot] = Elem<T>::from_f32(res);
+      }
     }
   }
   fence_before_sync();

@@ -20,6 +20,13 @@ from .. import kernel as K
 from ..compress import CompressConfig, compress_chunk
 
 
+def encode_block_tables(tables):
+    """Pad the sequences' page lists to a rectangle with -1 and mark each last page as -(id)-2
+    (zipage/engine/model_runner.py:440-441, :457-463)."""
+    nb = max(len(t) for t in tables)
+    return [list(t[:-1]) + [-t[-1] - 2] + [-1] * (nb - len(t)) for t in tables]
+
+
 class Compressor:
     def __init__(self, kv_cache, query_cache, score_cache, cfg: CompressConfig, layer_stride=8,
                  impl="auto", stream=None, block_size=256):
@@ -55,9 +62,8 @@ class Compressor:
         B = len(tables)
         if B == 0:
             return [], []
-        nb = max(len(t) for t in tables)
-        # < -1 marks the last page, -1 pads (model_runner.py:440-441, 457-463)
-        enc = [t[:-1] + [-t[-1] - 2] + [-1] * (nb - len(t)) for t in tables]
+        enc = encode_block_tables(tables)
+        nb = len(enc[0])
         pin = lambda data, dt: torch.tensor(data, dtype=dt, pin_memory=True)
         h_tables, h_targets = pin(enc, torch.int32), pin(targets, torch.int32)
         h_qids, h_comp = pin(query_ids, torch.int32), pin(compressed, torch.bool)

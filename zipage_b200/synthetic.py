@@ -110,3 +110,18 @@ def algorithmic_bytes_per_unit(NB, D, QCL, G, itemsize, redundancy, global_score
         "compact": moved_rows * D * e * 2 * 2 + N + (moved_rows * e * 2 if global_score else 0),
     }
     return stages
+
+
+def shard_kv_heads(w: CompressWorkload, rank: int, world: int) -> CompressWorkload:
+    """The slice of a workload that tensor-parallel rank `rank` of `world` owns: KV heads
+    [rank*Hkv/world, (rank+1)*Hkv/world) and their query heads (contiguous groups, as the
+    reference shards them: third_party/nanovllm/layers/linear.py:106-128).  Tables, targets and
+    query ids are replicated.  Units are independent, so no exchange is needed afterwards."""
+    Hkv, Hq = w.kv_cache.shape[4], w.query_cache.shape[3]
+    assert Hkv % world == 0 and Hq % world == 0
+    hk, hq = Hkv // world, Hq // world
+    kv = w.kv_cache[:, :, :, :, rank * hk:(rank + 1) * hk].contiguous()
+    qc = w.query_cache[:, :, :, rank * hq:(rank + 1) * hq].contiguous()
+    sc = None if w.score_cache is None else w.score_cache[..., rank * hk:(rank + 1) * hk].contiguous()
+    return CompressWorkload(kv, qc, sc, w.query_ids, w.block_tables, w.target_tables, w.compressed,
+                            w.tables_plain)
