@@ -12,21 +12,22 @@
 // Rounding points are the reference's: logits, shifted logits and probabilities are rounded to T
 // (attention_score.py:129-130 and the torch ops at :220-243) — done two at a time with packed
 // 16-bit instructions; exp uses ex2.approx.
-// Roles (320 threads): warp 0 = TMA producer + TMEM owner, warp 1 = MMA issuer, warps 2-9 =
-// epilogue.  Epilogue warps w and w+4 share a TMEM lane quadrant and split the 256 columns of a
-// tile (sweeps 0/1: key slots 0-127 / 128-255; sweep 2: keys 0-127 / 128-255 of the page).  TMEM
-// loads are software-pipelined: the next 32-column chunk is in flight while one is processed.
+// Roles (576 threads): warp 0 = TMA producer + TMEM owner, warp 1 = MMA issuer, warps 2-17 =
+// epilogue.  The four epilogue warps of a TMEM lane quadrant split the 256 columns of a tile in
+// four groups of 64 (sweeps 0/1: key slots; sweep 2: group g owns keys (g/2)*128.. and window-row
+// columns (g%2)*64.., the two partial sums of a key meet in shared memory).  Four warps per
+// scheduler hide the latency of the TMEM loads and of the dependent maths.
 #include "zp_tc.cuh"
 
 namespace zp {
 
 using namespace tc;
 
-constexpr int WT_THREADS = 320;
+constexpr int WT_THREADS = 576;
 constexpr int WT_PAGE_BYTES = 65536;
 constexpr int WT_BLOCK_BYTES = 32768;
 constexpr int WT_QBLOCK_BYTES = 16384;  // 128 rows x 128 bytes
-constexpr int WT_NS = 3;
+constexpr int WT_NS = 2;
 
 struct WtParams {
   const int32_t* seq_idx;
@@ -42,11 +43,11 @@ struct __align__(16) WtShared {
   uint64_t full[WT_NS], empty[WT_NS], tfull[2], tempty[2], qfull, stats_bar;
   alignas(16) uint32_t colm[64];   // sweep 2, per pair of window rows: packed row maxima (T)
   alignas(16) float colrz[128];    // sweep 2, per window row: 1 / row sum of exp
-  float part[2][128];              // per column-group partial row maximum / row sum
+  float part[4][128];              // per column-group partial row maximum / row sum
+  float acc[2][256];               // sweep 2: per key, sum (or max) over window rows; by tile parity
   uint32_t tmem_base;
   int abort_flag;
 };
-static_assert(sizeof(WtShared) <= 2048, "shared-memory budget: 3 stages + queries + this + 1 KB slack = 227 KB");
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -56,33 +57,41 @@ __device__ __forceinline__ float ex2_approx(float x) {
 
 // Reduce 32 columns held as 16 packed pairs: max over each group of G adjacent columns, then
 // sum (or max) over the groups.  Columns >= ncols are ignored.
-template <typename T, int G>
+// FULL: all 32 columns are window rows (no per-column test).
+template <typename T, int G, bool FULL>
 __device__ __forceinline__ float group_reduce(const typename Pair<T>::V (&pp)[16], int ncols, bool use_max,
                                               float acc) {
   using V = typename Pair<T>::V;
+  constexpr int PG = G >= 2 ? G / 2 : 1;  // packed pairs per group
+  constexpr int NG = 32 / G;
+  float part[NG];
   if constexpr (G == 1) {
 #pragma unroll
     for (int jp = 0; jp < 16; ++jp) {
       const float2 f = Pair<T>::unpack(pp[jp]);
-      if (2 * jp < ncols) acc = use_max ? fmaxf(acc, f.x) : acc + f.x;
-      if (2 * jp + 1 < ncols) acc = use_max ? fmaxf(acc, f.y) : acc + f.y;
+      part[2 * jp] = f.x; part[2 * jp + 1] = f.y;
     }
   } else {
-    constexpr int PG = G / 2;  // packed pairs per group
 #pragma unroll
     for (int jp = 0; jp < 16; jp += PG) {
       V m = pp[jp];
 #pragma unroll
       for (int k = 1; k < PG; ++k) m = __hmax2(m, pp[jp + k]);
       const float2 f = Pair<T>::unpack(m);
-      const float mx = fmaxf(f.x, f.y);
-      if (2 * jp < ncols) acc = use_max ? fmaxf(acc, mx) : acc + mx;
+      part[jp / PG] = fmaxf(f.x, f.y);
     }
+  }
+  if (use_max) {
+#pragma unroll
+    for (int g = 0; g < NG; ++g) if (FULL || g * G < ncols) acc = fmaxf(acc, part[g]);
+  } else {
+#pragma unroll
+    for (int g = 0; g < NG; ++g) if (FULL || g * G < ncols) acc += part[g];
   }
   return acc;
 }
 
-template <typename T>
+template <typename T, int G>
 __global__ void __launch_bounds__(WT_THREADS, 1)
 window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmQ,
                        const WtParams p) {
@@ -95,7 +104,7 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int unit = blockIdx.x;
   const int h = unit % p.Hkv, b = (unit / p.Hkv) % p.B, l = unit / (p.Hkv * p.B);
-  const int G = p.Hq / p.Hkv, R = G * p.QCL;
+  const int R = G * p.QCL;
   const int32_t* table = p.block_table + (int64_t)b * p.NB;
   int nvalid = 0;
   for (int pg = 0; pg < p.NB; ++pg) nvalid += table[pg] != -1;
@@ -103,12 +112,13 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < WT_NS; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 8); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 16); }
     mbar_init(&sh.qfull, 1);
-    mbar_init(&sh.stats_bar, 256);
+    mbar_init(&sh.stats_bar, 512);
     sh.abort_flag = 0;
     fence_mbar_init();
   }
+  if (threadIdx.x < 512) (&sh.acc[0][0])[threadIdx.x] = 0.f;
   if (warp == 0) {
     tmem_alloc(&sh.tmem_base, 512);
     tmem_relinquish();
@@ -119,16 +129,23 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   const uint32_t tmem_base = sh.tmem_base;
   volatile int* abortp = &sh.abort_flag;
 
-  // tile tt -> (sweep, table position): sweeps 0 and 2 walk the table forwards, sweep 1 backwards
-  // (the pages it starts with are the ones sweep 0 touched last, still in L2)
-  auto tile_page = [&](int tt, int& sweep) -> int {
-    sweep = tt / nvalid;
-    int idx = tt % nvalid;
-    if (sweep == 1) idx = nvalid - 1 - idx;
-    int seen = 0;
-    for (int pg = 0; pg < p.NB; ++pg)
-      if (table[pg] != -1) { if (seen == idx) return pg; ++seen; }
-    return 0;
+  // Tile order: sweeps 0 and 2 walk the table forwards, sweep 1 backwards (the pages it starts
+  // with are the ones sweep 0 touched last, still in L2).  Each role keeps a cursor, so finding
+  // the next valid table position costs one (cached) load instead of a scan of the table.
+  struct TileCursor {
+    const int32_t* table; int NB, nvalid, pg;
+    __device__ __forceinline__ int next(int tt) {
+      const int sweep = tt / nvalid;
+      if (tt % nvalid == 0) {
+        if (sweep == 1) { pg = NB - 1; while (table[pg] == -1) --pg; }
+        else { pg = 0; while (table[pg] == -1) ++pg; }
+      } else if (sweep == 1) {
+        do { --pg; } while (table[pg] == -1);
+      } else {
+        do { ++pg; } while (table[pg] == -1);
+      }
+      return pg;
+    }
   };
 
   if (warp == 0) {
@@ -139,9 +156,9 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       const int qid = p.seq_idx[b];
       tma_load_5d(qbuf, &tmQ, &sh.qfull, 0, h * G, 0, qid, l);
       tma_load_5d(qbuf + WT_QBLOCK_BYTES, &tmQ, &sh.qfull, 64, h * G, 0, qid, l);
+      TileCursor cur{table, p.NB, nvalid, 0};
       for (int tt = 0; tt < ntiles; ++tt) {
-        int sweep;
-        const int pg = tile_page(tt, sweep);
+        const int pg = cur.next(tt);
         const int s = tt % WT_NS, k = tt / WT_NS;
         if (!mbar_wait(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 111)) break;
         const int id = decode_page(table[pg]).id;
@@ -177,98 +194,118 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   } else {
     // ---------------- epilogue ----------------
     const int q = warp & 3;               // TMEM lane quadrant
-    const int grp = (warp - 2) >> 2;      // 0: columns 0-127 of a tile, 1: columns 128-255
+    const int grp = (warp - 2) >> 2;      // column group 0..3 (64 columns each)
     const int r = q * 32 + lane;          // TMEM lane: window row (sweeps 0/1) or key (sweep 2)
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + grp * 128;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + grp * 64;
     const float LOG2E = 1.4426950408889634f;
     const int my_i = r / G;
     const bool use_max = p.reduce_mode != 0;
     float row_max = -INFINITY, row_z = 0.f;
     V m2 = Pair<T>::pack(0.f, 0.f);       // this row's maximum, twice
     T* out = reinterpret_cast<T*>(p.scores_out) + (int64_t)unit * p.NB * 256;
-    for (int pg = 0; pg < p.NB; ++pg)     // padded pages score exactly 0
-      if (table[pg] == -1) out[pg * 256 + grp * 128 + r] = Elem<T>::from_f32(0.f);
-    const int nch2 = (R + 31) / 32;       // chunks of sweep 2 that hold window rows
+    if (grp < 2)
+      for (int pg = 0; pg < p.NB; ++pg)   // padded pages score exactly 0
+        if (table[pg] == -1) out[pg * 256 + grp * 128 + r] = Elem<T>::from_f32(0.f);
+    uint32_t ph = 0;                      // phase of stats_bar (all 512 epilogue threads in lock step)
+    auto sync_epilogue = [&](int where) -> bool {
+      mbar_arrive(&sh.stats_bar);
+      const bool ok_ = mbar_wait(&sh.stats_bar, ph & 1, abortp, p.error_word, where);
+      ++ph;
+      return ok_;
+    };
+    // sweep 2: this thread's key and the window-row columns it covers
+    const int hh = grp >> 1, cbase = (grp & 1) * 64;
+    const int slot = hh * 128 + r;
 
+    TileCursor cur{table, p.NB, nvalid, 0};
     for (int tt = 0; tt < ntiles; ++tt) {
-      int sweep;
-      const int pg = tile_page(tt, sweep);
+      const int pg = cur.next(tt);
+      const int sweep = tt / nvalid;
       const bool last = table[pg] < -1;
       const int buf = tt & 1, u = tt >> 1;
-      if (tt == nvalid) {  // row maximum: combine the two column groups
+      if (tt == nvalid) {  // row maximum: combine the four column groups
         sh.part[grp][r] = row_max;
-        mbar_arrive(&sh.stats_bar);
-        if (!mbar_wait(&sh.stats_bar, 0, abortp, p.error_word, 311)) break;
-        const float m = fmaxf(sh.part[0][r], sh.part[1][r]) * p.scale;
+        if (!sync_epilogue(311)) break;
+        const float m = fmaxf(fmaxf(sh.part[0][r], sh.part[1][r]), fmaxf(sh.part[2][r], sh.part[3][r])) * p.scale;
         m2 = Pair<T>::pack(m, m);
-        mbar_arrive(&sh.stats_bar);  // everyone has read `part` before it is reused
-        if (!mbar_wait(&sh.stats_bar, 1, abortp, p.error_word, 312)) break;
+        if (!sync_epilogue(312)) break;  // everyone has read `part` before it is reused
       }
       if (tt == 2 * nvalid) {  // row sum: combine, publish per-column statistics for sweep 2
         sh.part[grp][r] = row_z;
-        mbar_arrive(&sh.stats_bar);
-        if (!mbar_wait(&sh.stats_bar, 0, abortp, p.error_word, 313)) break;
+        if (!sync_epilogue(313)) break;
         if (grp == 0) {
-          const float z = sh.part[0][r] + sh.part[1][r];
+          const float z = (sh.part[0][r] + sh.part[1][r]) + (sh.part[2][r] + sh.part[3][r]);
           reinterpret_cast<T*>(sh.colm)[r] = reinterpret_cast<const T*>(&m2)[0];
           sh.colrz[r] = 1.f / z;
         }
-        mbar_arrive(&sh.stats_bar);
-        if (!mbar_wait(&sh.stats_bar, 1, abortp, p.error_word, 314)) break;
+        if (!sync_epilogue(314)) break;
       }
       if (!mbar_wait(&sh.tfull[buf], u & 1, abortp, p.error_word, 315)) break;
       fence_after_sync();
 
-      const uint32_t tbase = lane_base + buf * 256;
-      const int nch = sweep < 2 ? 4 : nch2;
-      // sweeps 0/1: row r sees key slot <= smax; sweep 2: key `slot` is hidden from columns < jmask
-      const int smax = last ? 256 - p.QCL + my_i : 256;
-      const int slot = grp * 128 + r;
-      const int jmask = last ? max(0, slot - (256 - p.QCL)) * G : 0;
-      float acc2 = use_max ? -INFINITY : 0.f;
-
-      auto process = [&](const uint32_t (&raw)[32], int c) {
-        if (sweep == 0) {
-          const int s0 = grp * 128 + c * 32;
-          float m0 = -INFINITY, m1 = -INFINITY, m2_ = -INFINITY, m3 = -INFINITY;
-          if (s0 + 31 > smax) {
+      if (sweep < 2) {
+        // columns = key slots grp*64 ..; row r sees slot <= smax inside the last page
+        const uint32_t tbase = lane_base + buf * 256;
+        const int smax = last ? 256 - p.QCL + my_i : 256;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t raw[32];
+          tmem_ld32_issue(tbase + c * 32, raw);
+          tmem_ld32_wait(raw);
+          if (c == 1) {  // all TMEM reads of this tile have landed in registers
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.tempty[buf]);
+          }
+          const int s0 = grp * 64 + c * 32;
+          if (s0 + 31 > smax) {  // masked key slots (last page only)
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float x = s0 + j > smax ? -INFINITY : __uint_as_float(raw[j]);
-              m0 = fmaxf(m0, x);
-            }
-          } else {
+            for (int j = 0; j < 32; ++j) if (s0 + j > smax) raw[j] = 0xff800000u;  // -inf
+          }
+          if (sweep == 0) {
+            float m0 = -INFINITY, m1 = -INFINITY, m2_ = -INFINITY, m3 = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               m0 = fmaxf(m0, __uint_as_float(raw[j])); m1 = fmaxf(m1, __uint_as_float(raw[j + 1]));
               m2_ = fmaxf(m2_, __uint_as_float(raw[j + 2])); m3 = fmaxf(m3, __uint_as_float(raw[j + 3]));
             }
-          }
-          row_max = fmaxf(row_max, fmaxf(fmaxf(m0, m1), fmaxf(m2_, m3)));
-        } else if (sweep == 1) {
-          const int s0 = grp * 128 + c * 32;
-          const bool partial = s0 + 31 > smax;
-          float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
+            row_max = fmaxf(row_max, fmaxf(fmaxf(m0, m1), fmaxf(m2_, m3)));
+          } else {
+            float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const V la = Pair<T>::pack(__uint_as_float(raw[j]) * p.scale, __uint_as_float(raw[j + 1]) * p.scale);
-            const V lb = Pair<T>::pack(__uint_as_float(raw[j + 2]) * p.scale, __uint_as_float(raw[j + 3]) * p.scale);
-            const float2 da = Pair<T>::unpack(__hsub2(la, m2)), db = Pair<T>::unpack(__hsub2(lb, m2));
-            float e0 = ex2_approx(da.x * LOG2E), e1 = ex2_approx(da.y * LOG2E);
-            float e2 = ex2_approx(db.x * LOG2E), e3 = ex2_approx(db.y * LOG2E);
-            if (partial) {
-              if (s0 + j > smax) e0 = 0.f;
-              if (s0 + j + 1 > smax) e1 = 0.f;
-              if (s0 + j + 2 > smax) e2 = 0.f;
-              if (s0 + j + 3 > smax) e3 = 0.f;
+            for (int j = 0; j < 32; j += 4) {
+              const V la = Pair<T>::pack(__uint_as_float(raw[j]) * p.scale, __uint_as_float(raw[j + 1]) * p.scale);
+              const V lb = Pair<T>::pack(__uint_as_float(raw[j + 2]) * p.scale, __uint_as_float(raw[j + 3]) * p.scale);
+              const float2 da = Pair<T>::unpack(__hsub2(la, m2)), db = Pair<T>::unpack(__hsub2(lb, m2));
+              z0 += ex2_approx(da.x * LOG2E); z1 += ex2_approx(da.y * LOG2E);
+              z2 += ex2_approx(db.x * LOG2E); z3 += ex2_approx(db.y * LOG2E);
             }
-            z0 += e0; z1 += e1; z2 += e2; z3 += e3;
+            row_z += (z0 + z1) + (z2 + z3);
           }
-          row_z += (z0 + z1) + (z2 + z3);
-        } else {
+        }
+      } else {
+        // rows of D = keys; columns = window rows j = i*G + g; key `slot` is hidden from columns < jmask
+        const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * 256 + hh * 128 + cbase;
+        const int jmask = last ? max(0, slot - (256 - p.QCL)) * G : 0;
+        float acc2 = use_max ? -INFINITY : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          const int col0 = cbase + c * 32;
+          if (col0 >= R) {  // no window rows in this chunk (R < 128)
+            if (c == 1) { fence_before_sync(); __syncwarp(); if (lane == 0) mbar_arrive(&sh.tempty[buf]); }
+            continue;
+          }
+          uint32_t raw[32];
+          tmem_ld32_issue(tbase + c * 32, raw);
+          tmem_ld32_wait(raw);
+          if (c == 1) {
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.tempty[buf]);
+          }
           V pp[16];
-          const uint4* cm4 = reinterpret_cast<const uint4*>(&sh.colm[c * 16]);
-          const float4* rz4 = reinterpret_cast<const float4*>(&sh.colrz[c * 32]);
+          const uint4* cm4 = reinterpret_cast<const uint4*>(&sh.colm[col0 >> 1]);
+          const float4* rz4 = reinterpret_cast<const float4*>(&sh.colrz[col0]);
 #pragma unroll
           for (int j4 = 0; j4 < 4; ++j4) {   // 4 pairs (8 columns) per step
             const uint4 cm = cm4[j4];
@@ -281,55 +318,31 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
               const V lg = Pair<T>::pack(__uint_as_float(raw[2 * jp]) * p.scale,
                                          __uint_as_float(raw[2 * jp + 1]) * p.scale);
               const float2 d = Pair<T>::unpack(__hsub2(lg, *reinterpret_cast<const V*>(&cmv[k])));
-              float e0 = ex2_approx(d.x * LOG2E) * rzv[2 * k];
-              float e1 = ex2_approx(d.y * LOG2E) * rzv[2 * k + 1];
-              if (jmask > 0) {
-                if (c * 32 + 2 * jp < jmask) e0 = 0.f;
-                if (c * 32 + 2 * jp + 1 < jmask) e1 = 0.f;
-              }
-              pp[jp] = Pair<T>::pack(e0, e1);
+              pp[jp] = Pair<T>::pack(ex2_approx(d.x * LOG2E) * rzv[2 * k], ex2_approx(d.y * LOG2E) * rzv[2 * k + 1]);
             }
           }
-          const int ncols = R - c * 32;
-          switch (G) {
-            case 1: acc2 = group_reduce<T, 1>(pp, ncols, use_max, acc2); break;
-            case 2: acc2 = group_reduce<T, 2>(pp, ncols, use_max, acc2); break;
-            case 4: acc2 = group_reduce<T, 4>(pp, ncols, use_max, acc2); break;
-            case 8: acc2 = group_reduce<T, 8>(pp, ncols, use_max, acc2); break;
-            case 16: acc2 = group_reduce<T, 16>(pp, ncols, use_max, acc2); break;
-            default: acc2 = group_reduce<T, 32>(pp, ncols, use_max, acc2); break;
+          if (jmask > col0) {  // some of this chunk's window rows cannot see this key (last page only)
+            const T zero = Elem<T>::from_f32(0.f);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < jmask) reinterpret_cast<T*>(pp)[j] = zero;
           }
+          const int ncols = R - col0;
+          acc2 = ncols >= 32 ? group_reduce<T, G, true>(pp, ncols, use_max, acc2)
+                             : group_reduce<T, G, false>(pp, ncols, use_max, acc2);
         }
-      };
-      auto release = [&]() {  // all TMEM reads of this tile have landed in registers
-        fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh.tempty[buf]);
-      };
-
-      uint32_t ra[32], rb[32];
-      tmem_ld32_issue(tbase, ra);
-      tmem_ld32_wait(ra);
-      if (nch > 1) tmem_ld32_issue(tbase + 32, rb); else release();
-      process(ra, 0);
-      if (nch > 1) {
-        tmem_ld32_wait(rb);
-        if (nch > 2) tmem_ld32_issue(tbase + 64, ra); else release();
-        process(rb, 1);
-      }
-      if (nch > 2) {
-        tmem_ld32_wait(ra);
-        if (nch > 3) tmem_ld32_issue(tbase + 96, rb); else release();
-        process(ra, 2);
-      }
-      if (nch > 3) {
-        tmem_ld32_wait(rb);
-        release();
-        process(rb, 3);
-      }
-      if (sweep == 2) {
-        const float res = use_max ? acc2 : acc2 / (float)p.QCL;
-        out[pg * 256 + slot] = Elem<T>::from_f32(res);
+        // the two column halves of a key meet in shared memory (two addends: order cannot matter)
+        float* accbuf = sh.acc[tt & 1];
+        if (cbase < R) {
+          if (use_max) atomicMax(reinterpret_cast<int*>(&accbuf[slot]), __float_as_int(fmaxf(acc2, 0.f)));
+          else atomicAdd(&accbuf[slot], acc2);
+        }
+        if (!sync_epilogue(316)) break;
+        if ((grp & 1) == 0) {
+          const float a = accbuf[slot];
+          accbuf[slot] = 0.f;
+          out[pg * 256 + slot] = Elem<T>::from_f32(use_max ? a : a / (float)p.QCL);
+        }
       }
     }
   }
@@ -366,7 +379,15 @@ static int launch_window_tc(const void* k_cache, const void* q_cache, const WtPa
     if (rc) return rc;
   }
   const size_t smem = WT_NS * WT_PAGE_BYTES + 2 * WT_QBLOCK_BYTES + sizeof(WtShared) + 1024;
-  auto kern = window_score_tc_kernel<T>;
+  void (*kern)(const CUtensorMap, const CUtensorMap, const WtParams) = nullptr;
+  switch (G) {
+    case 1: kern = window_score_tc_kernel<T, 1>; break;
+    case 2: kern = window_score_tc_kernel<T, 2>; break;
+    case 4: kern = window_score_tc_kernel<T, 4>; break;
+    case 8: kern = window_score_tc_kernel<T, 8>; break;
+    case 16: kern = window_score_tc_kernel<T, 16>; break;
+    default: kern = window_score_tc_kernel<T, 32>; break;
+  }
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_error("zp_window_score(tcgen05): %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
   kern<<<p.L * p.B * p.Hkv, WT_THREADS, smem, st>>>(tmK, tmQ, p);
