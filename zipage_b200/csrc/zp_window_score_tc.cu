@@ -1,8 +1,10 @@
 // Window-masked attention scoring on tcgen05 tensor cores (16-bit caches, head_dim 128, page
 // size 256, G*QCL <= 128 window rows, G a power of two).
 //
-// One block per unit (layer, sequence, kv head).  The unit's window queries (row r = i*G + g) are
-// loaded once by TMA; the unit's key pages stream through a 3-stage ring of 64 KB swizzled tiles.
+// Persistent blocks (one per SM) walk over the units (layer, sequence, kv head) with a fixed
+// stride, so the TMA/MMA pipeline never drains between units.  A unit's window queries (row
+// r = i*G + g) are loaded once by TMA (double-buffered across units); its key pages stream through
+// a ring of 64 KB swizzled tiles.
 // Three sweeps over the pages recompute the logits on the tensor cores instead of storing them:
 //   sweep 0: D[row][key]  = Q K^T (M = 128 rows, N = 256 keys)   -> row maximum
 //   sweep 1: same product                                         -> row sum of exp
@@ -37,10 +39,11 @@ struct WtParams {
   int L, B, NB, Hq, Hkv, QCL;
   float scale;
   int reduce_mode;
+  int total_units;
 };
 
 struct __align__(16) WtShared {
-  uint64_t full[WT_NS], empty[WT_NS], tfull[2], tempty[2], qfull, stats_bar;
+  uint64_t full[WT_NS], empty[WT_NS], tfull[2], tempty[2], qfull[2], qempty[2], stats_bar;
   alignas(16) uint32_t colm[64];   // sweep 2, per pair of window rows: packed row maxima (T)
   alignas(16) float colrz[128];    // sweep 2, per window row: 1 / row sum of exp
   float part[4][128];              // per column-group partial row maximum / row sum
@@ -98,23 +101,19 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   using V = typename Pair<T>::V;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* bufs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* qbuf = bufs + WT_NS * WT_PAGE_BYTES;
-  WtShared& sh = *reinterpret_cast<WtShared*>(qbuf + 2 * WT_QBLOCK_BYTES);
+  unsigned char* qbufs = bufs + WT_NS * WT_PAGE_BYTES;   // two query buffers of 2 x 16 KB
+  WtShared& sh = *reinterpret_cast<WtShared*>(qbufs + 4 * WT_QBLOCK_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int unit = blockIdx.x;
-  const int h = unit % p.Hkv, b = (unit / p.Hkv) % p.B, l = unit / (p.Hkv * p.B);
   const int R = G * p.QCL;
-  const int32_t* table = p.block_table + (int64_t)b * p.NB;
-  int nvalid = 0;
-  for (int pg = 0; pg < p.NB; ++pg) nvalid += table[pg] != -1;
-  const int ntiles = 3 * nvalid;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < WT_NS; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 16); }
-    mbar_init(&sh.qfull, 1);
-    mbar_init(&sh.stats_bar, 512);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 16);
+      mbar_init(&sh.qfull[i], 1); mbar_init(&sh.qempty[i], 1);
+    }
+    mbar_init(&sh.stats_bar, 16);  // one arrival per epilogue warp
     sh.abort_flag = 0;
     fence_mbar_init();
   }
@@ -129,22 +128,43 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   const uint32_t tmem_base = sh.tmem_base;
   volatile int* abortp = &sh.abort_flag;
 
-  // Tile order: sweeps 0 and 2 walk the table forwards, sweep 1 backwards (the pages it starts
-  // with are the ones sweep 0 touched last, still in L2).  Each role keeps a cursor, so finding
-  // the next valid table position costs one (cached) load instead of a scan of the table.
+  // Tile order within a unit: sweeps 0 and 2 walk the table forwards, sweep 1 backwards (the pages
+  // it starts with are the ones sweep 0 touched last, still in L2).  Each role keeps a cursor, so
+  // finding the next valid table position costs one (cached) load instead of a scan of the table.
   struct TileCursor {
-    const int32_t* table; int NB, nvalid, pg;
-    __device__ __forceinline__ int next(int tt) {
-      const int sweep = tt / nvalid;
-      if (tt % nvalid == 0) {
-        if (sweep == 1) { pg = NB - 1; while (table[pg] == -1) --pg; }
-        else { pg = 0; while (table[pg] == -1) ++pg; }
-      } else if (sweep == 1) {
-        do { --pg; } while (table[pg] == -1);
-      } else {
-        do { ++pg; } while (table[pg] == -1);
+    // The table entry of the tile after the current one is loaded one call ahead, so its latency
+    // is hidden behind the current tile's work.
+    const int32_t* table; int NB, nvalid, pg, nxt_pg, nxt_entry;
+    __device__ __forceinline__ void probe(int from, int step) {   // next valid position from `from`
+      int q = from;
+      int e = table[q];
+      while (e == -1) { q += step; e = table[q]; }
+      nxt_pg = q; nxt_entry = e;
+    }
+    __device__ __forceinline__ void start() { probe(0, 1); }
+    // returns the table position of tile tt and its (encoded) entry
+    __device__ __forceinline__ int next(int tt, int ntiles, int& entry) {
+      pg = nxt_pg; entry = nxt_entry;
+      const int t2 = tt + 1;
+      if (t2 < ntiles) {
+        const int sweep = t2 / nvalid;
+        if (t2 % nvalid == 0) { if (sweep == 1) probe(NB - 1, -1); else probe(0, 1); }
+        else if (sweep == 1) probe(pg - 1, -1);
+        else probe(pg + 1, 1);
       }
       return pg;
+    }
+  };
+  // Every role walks the same sequence of units and tiles; `gt` counts tiles since kernel start
+  // (it selects the shared-memory stage and the TMEM buffer), `n` counts this block's units.
+  struct Unit {
+    int h, b, l, nvalid, ntiles; const int32_t* table;
+    __device__ __forceinline__ Unit(const WtParams& p, int unit) {
+      h = unit % p.Hkv; b = (unit / p.Hkv) % p.B; l = unit / (p.Hkv * p.B);
+      table = p.block_table + (int64_t)b * p.NB;
+      nvalid = 0;
+      for (int pg = 0; pg < p.NB; ++pg) nvalid += table[pg] != -1;
+      ntiles = 3 * nvalid;
     }
   };
 
@@ -152,43 +172,64 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     if (lane == 0) {
       prefetch_tensormap(&tmK);
       prefetch_tensormap(&tmQ);
-      mbar_arrive_expect_tx(&sh.qfull, (uint32_t)(2 * R * 128));
-      const int qid = p.seq_idx[b];
-      tma_load_5d(qbuf, &tmQ, &sh.qfull, 0, h * G, 0, qid, l);
-      tma_load_5d(qbuf + WT_QBLOCK_BYTES, &tmQ, &sh.qfull, 64, h * G, 0, qid, l);
-      TileCursor cur{table, p.NB, nvalid, 0};
-      for (int tt = 0; tt < ntiles; ++tt) {
-        const int pg = cur.next(tt);
-        const int s = tt % WT_NS, k = tt / WT_NS;
-        if (!mbar_wait(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 111)) break;
-        const int id = decode_page(table[pg]).id;
-        mbar_arrive_expect_tx(&sh.full[s], WT_PAGE_BYTES);
-        tma_load_5d(bufs + s * WT_PAGE_BYTES, &tmK, &sh.full[s], 0, h, 0, id, l);
-        tma_load_5d(bufs + s * WT_PAGE_BYTES + WT_BLOCK_BYTES, &tmK, &sh.full[s], 64, h, 0, id, l);
+      int gt = 0, n = 0;  // n counts the units that have tiles (query buffer n & 1)
+      bool ok = true;
+      for (int unit = blockIdx.x; ok && unit < p.total_units; unit += gridDim.x) {
+        const Unit un(p, unit);
+        if (un.ntiles == 0) continue;
+        const int qb = n & 1;
+        if (!mbar_wait(&sh.qempty[qb], ((n >> 1) & 1) ^ 1, abortp, p.error_word, 110)) break;
+        mbar_arrive_expect_tx(&sh.qfull[qb], (uint32_t)(2 * R * 128));
+        const int qid = p.seq_idx[un.b];
+        unsigned char* qbuf = qbufs + qb * 2 * WT_QBLOCK_BYTES;
+        tma_load_5d(qbuf, &tmQ, &sh.qfull[qb], 0, un.h * G, 0, qid, un.l);
+        tma_load_5d(qbuf + WT_QBLOCK_BYTES, &tmQ, &sh.qfull[qb], 64, un.h * G, 0, qid, un.l);
+        TileCursor cur{un.table, p.NB, un.nvalid, 0, 0, 0};
+        cur.start();
+        for (int tt = 0; tt < un.ntiles; ++tt, ++gt) {
+          int entry;
+          cur.next(tt, un.ntiles, entry);
+          const int s = gt % WT_NS, k = gt / WT_NS;
+          if (!mbar_wait(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 111)) { ok = false; break; }
+          const int id = decode_page(entry).id;
+          mbar_arrive_expect_tx(&sh.full[s], WT_PAGE_BYTES);
+          tma_load_5d(bufs + s * WT_PAGE_BYTES, &tmK, &sh.full[s], 0, un.h, 0, id, un.l);
+          tma_load_5d(bufs + s * WT_PAGE_BYTES + WT_BLOCK_BYTES, &tmK, &sh.full[s], 64, un.h, 0, id, un.l);
+        }
+        ++n;
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t IDESC_QK = idesc_f16(UmmaFmt<T>::fmt, 128, 256);
       constexpr uint32_t IDESC_KQ = idesc_f16(UmmaFmt<T>::fmt, 128, 128);
-      bool ok = mbar_wait(&sh.qfull, 0, abortp, p.error_word, 211);
-      const uint32_t q_addr = smem_u32(qbuf);
-      for (int tt = 0; ok && tt < ntiles; ++tt) {
-        const int sweep = tt / nvalid;
-        const int s = tt % WT_NS, k = tt / WT_NS, buf = tt & 1, u = tt >> 1;
-        if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 212)) break;
-        if (!mbar_wait(&sh.tempty[buf], (u & 1) ^ 1, abortp, p.error_word, 213)) break;
-        fence_after_sync();
-        const uint32_t k_addr = smem_u32(bufs + s * WT_PAGE_BYTES);
-        const uint32_t d = tmem_base + buf * 256;
-        if (sweep < 2) {
-          umma_k128(d, q_addr, WT_QBLOCK_BYTES, k_addr, WT_BLOCK_BYTES, IDESC_QK);
-        } else {
-          umma_k128(d, k_addr, WT_BLOCK_BYTES, q_addr, WT_QBLOCK_BYTES, IDESC_KQ);
-          umma_k128(d + 128, k_addr + 16384, WT_BLOCK_BYTES, q_addr, WT_QBLOCK_BYTES, IDESC_KQ);
+      int gt = 0, n = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; ok && unit < p.total_units; unit += gridDim.x) {
+        const Unit un(p, unit);
+        if (un.ntiles == 0) continue;
+        const int qb = n & 1;
+        if (!mbar_wait(&sh.qfull[qb], (n >> 1) & 1, abortp, p.error_word, 211)) break;
+        const uint32_t q_addr = smem_u32(qbufs + qb * 2 * WT_QBLOCK_BYTES);
+        for (int tt = 0; tt < un.ntiles; ++tt, ++gt) {
+          const int sweep = tt / un.nvalid;
+          const int s = gt % WT_NS, k = gt / WT_NS, buf = gt & 1, u = gt >> 1;
+          if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 212)) { ok = false; break; }
+          if (!mbar_wait(&sh.tempty[buf], (u & 1) ^ 1, abortp, p.error_word, 213)) { ok = false; break; }
+          fence_after_sync();
+          const uint32_t k_addr = smem_u32(bufs + s * WT_PAGE_BYTES);
+          const uint32_t d = tmem_base + buf * 256;
+          if (sweep < 2) {
+            umma_k128(d, q_addr, WT_QBLOCK_BYTES, k_addr, WT_BLOCK_BYTES, IDESC_QK);
+          } else {
+            umma_k128(d, k_addr, WT_BLOCK_BYTES, q_addr, WT_QBLOCK_BYTES, IDESC_KQ);
+            umma_k128(d + 128, k_addr + 16384, WT_BLOCK_BYTES, q_addr, WT_QBLOCK_BYTES, IDESC_KQ);
+          }
+          umma_commit(&sh.tfull[buf]);
+          umma_commit(&sh.empty[s]);
         }
-        umma_commit(&sh.tfull[buf]);
-        umma_commit(&sh.empty[s]);
+        if (ok) umma_commit(&sh.qempty[qb]);  // the unit's queries are no longer read
+        ++n;
       }
     }
   } else {
@@ -200,15 +241,10 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const float LOG2E = 1.4426950408889634f;
     const int my_i = r / G;
     const bool use_max = p.reduce_mode != 0;
-    float row_max = -INFINITY, row_z = 0.f;
-    V m2 = Pair<T>::pack(0.f, 0.f);       // this row's maximum, twice
-    T* out = reinterpret_cast<T*>(p.scores_out) + (int64_t)unit * p.NB * 256;
-    if (grp < 2)
-      for (int pg = 0; pg < p.NB; ++pg)   // padded pages score exactly 0
-        if (table[pg] == -1) out[pg * 256 + grp * 128 + r] = Elem<T>::from_f32(0.f);
     uint32_t ph = 0;                      // phase of stats_bar (all 512 epilogue threads in lock step)
     auto sync_epilogue = [&](int where) -> bool {
-      mbar_arrive(&sh.stats_bar);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.stats_bar);
       const bool ok_ = mbar_wait(&sh.stats_bar, ph & 1, abortp, p.error_word, where);
       ++ph;
       return ok_;
@@ -217,30 +253,44 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const int hh = grp >> 1, cbase = (grp & 1) * 64;
     const int slot = hh * 128 + r;
 
-    TileCursor cur{table, p.NB, nvalid, 0};
-    for (int tt = 0; tt < ntiles; ++tt) {
-      const int pg = cur.next(tt);
+    int gt = 0;
+    bool ok = true;
+    for (int unit = blockIdx.x; ok && unit < p.total_units; unit += gridDim.x) {
+    const Unit un(p, unit);
+    const int32_t* table = un.table;
+    const int nvalid = un.nvalid, ntiles = un.ntiles;
+    float row_max = -INFINITY, row_z = 0.f;
+    V m2 = Pair<T>::pack(0.f, 0.f);       // this row's maximum, twice
+    T* out = reinterpret_cast<T*>(p.scores_out) + (int64_t)unit * p.NB * 256;
+    if (grp < 2)
+      for (int pg = 0; pg < p.NB; ++pg)   // padded pages score exactly 0
+        if (table[pg] == -1) out[pg * 256 + grp * 128 + r] = Elem<T>::from_f32(0.f);
+    TileCursor cur{table, p.NB, nvalid, 0, 0, 0};
+    if (ntiles > 0) cur.start();
+    for (int tt = 0; tt < ntiles; ++tt, ++gt) {
+      int entry;
+      const int pg = cur.next(tt, ntiles, entry);
       const int sweep = tt / nvalid;
-      const bool last = table[pg] < -1;
-      const int buf = tt & 1, u = tt >> 1;
+      const bool last = entry < -1;
+      const int buf = gt & 1, u = gt >> 1;
       if (tt == nvalid) {  // row maximum: combine the four column groups
         sh.part[grp][r] = row_max;
-        if (!sync_epilogue(311)) break;
+        if (!sync_epilogue(311)) { ok = false; break; }
         const float m = fmaxf(fmaxf(sh.part[0][r], sh.part[1][r]), fmaxf(sh.part[2][r], sh.part[3][r])) * p.scale;
         m2 = Pair<T>::pack(m, m);
-        if (!sync_epilogue(312)) break;  // everyone has read `part` before it is reused
+        if (!sync_epilogue(312)) { ok = false; break; }  // everyone has read `part` before it is reused
       }
       if (tt == 2 * nvalid) {  // row sum: combine, publish per-column statistics for sweep 2
         sh.part[grp][r] = row_z;
-        if (!sync_epilogue(313)) break;
+        if (!sync_epilogue(313)) { ok = false; break; }
         if (grp == 0) {
           const float z = (sh.part[0][r] + sh.part[1][r]) + (sh.part[2][r] + sh.part[3][r]);
           reinterpret_cast<T*>(sh.colm)[r] = reinterpret_cast<const T*>(&m2)[0];
           sh.colrz[r] = 1.f / z;
         }
-        if (!sync_epilogue(314)) break;
+        if (!sync_epilogue(314)) { ok = false; break; }
       }
-      if (!mbar_wait(&sh.tfull[buf], u & 1, abortp, p.error_word, 315)) break;
+      if (!mbar_wait(&sh.tfull[buf], u & 1, abortp, p.error_word, 315)) { ok = false; break; }
       fence_after_sync();
 
       if (sweep < 2) {
@@ -337,7 +387,7 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
           if (use_max) atomicMax(reinterpret_cast<int*>(&accbuf[slot]), __float_as_int(fmaxf(acc2, 0.f)));
           else atomicAdd(&accbuf[slot], acc2);
         }
-        if (!sync_epilogue(316)) break;
+        if (!sync_epilogue(316)) { ok = false; break; }
         if ((grp & 1) == 0) {
           const float a = accbuf[slot];
           accbuf[slot] = 0.f;
@@ -345,6 +395,7 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         }
       }
     }
+    }  // units
   }
   fence_before_sync();
   __syncthreads();
@@ -378,7 +429,7 @@ static int launch_window_tc(const void* k_cache, const void* q_cache, const WtPa
     int rc = make_tensor_map_5d(&tmQ, UmmaFmt<T>::tm, q_cache, dims, strides, box, sizeof(T));
     if (rc) return rc;
   }
-  const size_t smem = WT_NS * WT_PAGE_BYTES + 2 * WT_QBLOCK_BYTES + sizeof(WtShared) + 1024;
+  const size_t smem = WT_NS * WT_PAGE_BYTES + 4 * WT_QBLOCK_BYTES + sizeof(WtShared) + 1024;
   void (*kern)(const CUtensorMap, const CUtensorMap, const WtParams) = nullptr;
   switch (G) {
     case 1: kern = window_score_tc_kernel<T, 1>; break;
@@ -390,7 +441,11 @@ static int launch_window_tc(const void* k_cache, const void* q_cache, const WtPa
   }
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_error("zp_window_score(tcgen05): %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
-  kern<<<p.L * p.B * p.Hkv, WT_THREADS, smem, st>>>(tmK, tmQ, p);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = p.total_units < sms ? p.total_units : sms;
+  kern<<<grid, WT_THREADS, smem, st>>>(tmK, tmQ, p);
   return check_launch("zp_window_score(tcgen05)");
 }
 
@@ -412,6 +467,7 @@ int window_score_tc(const void* k_cache, const void* q_cache, const int32_t* seq
   p.error_word = device_error_word();
   p.L = L; p.B = B; p.NB = NB; p.Hq = Hq; p.Hkv = Hkv; p.QCL = QCL; p.scale = scale;
   p.reduce_mode = reduce_mode;
+  p.total_units = L * B * Hkv;
   if (!p.error_word) { set_error("zp_window_score(tcgen05): no device error word"); return ZP_ERR_CUDA; }
   if (dtype == ZP_DTYPE_BF16)
     return launch_window_tc<__nv_bfloat16>(k_cache, q_cache, p, k_stride_layer, k_stride_page,
