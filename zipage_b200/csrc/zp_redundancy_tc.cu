@@ -6,14 +6,14 @@
 // cosine normalisation is applied in the epilogue: S[m,n] = acc[m,n] / (|k_m| |k_n|), with the
 // norms computed from the same shared-memory tile and rounded to T as key_norm does.
 //
-// Roles (320 threads, 1 block per SM): warp 0 = TMA producer and TMEM owner, warp 1 = MMA issuer,
-// warps 2-9 = epilogue (thread <-> TMEM lane <-> similarity row; warps w and w+4 share a lane
-// quadrant and split the 256 columns of an item).  A work item is (column page, row half h): 128
-// rows x 256 columns = 256 TMEM columns; the two halves alternate between the two halves of TMEM,
-// so the MMA of one item overlaps the epilogue of the previous one; TMEM loads are software-
-// pipelined (the next 32-column chunk is in flight while one is processed).
-//   lightning: one block per unit; rows and columns are the same page (A = B tile).
-//   exact:     one block per (unit, row page); the row page stays resident, every page streams by.
+// Roles (576 threads, persistent blocks, one per SM): warp 0 = TMA producer and TMEM owner,
+// warp 1 = MMA issuer, warps 2-17 = epilogue (thread <-> TMEM lane <-> similarity row; the four
+// warps of a lane quadrant split the 256 columns of an item in groups of 64).  A work item is
+// (column page, row half h): 128 rows x 256 columns = 256 TMEM columns; the two halves alternate
+// between the two halves of TMEM, so the MMA of one item overlaps the epilogue of the previous one.
+//   lightning: a job is a unit; rows and columns are the same page (A = B tile).
+//   exact:     a job is (unit, row page); the row page stays resident, every page streams by.
+// Blocks walk over the jobs with a fixed stride, so the pipeline never drains between jobs.
 // The epilogue keeps row-wise state only (row sum, last column above the threshold and its value);
 // see zp_redundancy.cu for why that is enough.  The "subtract the exempted entries" step uses
 // 64-bit fixed-point atomics (2^-32 units), so the result does not depend on execution order.
@@ -23,7 +23,7 @@ namespace zp {
 
 using namespace tc;
 
-constexpr int RT_THREADS = 320;
+constexpr int RT_THREADS = 576;
 constexpr int RT_PAGE_BYTES = 65536;   // 256 keys x 128 dims x 2 bytes
 constexpr int RT_BLOCK_BYTES = 32768;  // one 64-column block of a page
 constexpr int RT_NBUF = 3;
@@ -36,14 +36,15 @@ struct RtParams {
   int* error_word;
   int L, B, NB, Hkv;
   float threshold, eps;
+  int total_jobs;
 };
 
 struct __align__(16) RtShared {
-  uint64_t full[RT_NBUF], empty[RT_NBUF], tfull[2], tempty[2], afull, sync_bar;
+  uint64_t full[RT_NBUF], empty[RT_NBUF], tfull[2], tempty[2], afull, aempty, sync_bar;
   alignas(16) float rn[2][256];     // 1 / |k| of the column page (double-buffered over pages)
   float s_sum[256];                 // combined row sums of a page (lightning)
-  float pb_sum[256], pb_val[256];   // partials of the upper column group, rows r and r + 128
-  int pb_col[256];
+  float pb_sum[4][256], pb_val[4][256];  // per column group partials of rows 0..255
+  int pb_col[4][256];
   unsigned long long s_sub[256];    // fixed-point sums of exempted entries (lightning)
   uint32_t tmem_base;
   int abort_flag;
@@ -52,19 +53,22 @@ struct __align__(16) RtShared {
 // sum of squares of one 128-element row of a swizzled [256][128] tile (two 64-column blocks)
 template <typename T>
 __device__ __forceinline__ float row_sumsq(const unsigned char* tile, int row) {
-  float ss = 0.f;
+  float s0 = 0.f, s1 = 0.f;
 #pragma unroll
   for (int blk = 0; blk < 2; ++blk) {
     const unsigned char* base = tile + blk * RT_BLOCK_BYTES + row * 128;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       const int4 raw = *reinterpret_cast<const int4*>(base + ((c ^ (row & 7)) << 4));
-      const T* e = reinterpret_cast<const T*>(&raw);
+      const typename Pair<T>::V* e = reinterpret_cast<const typename Pair<T>::V*>(&raw);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { const float x = Elem<T>::to_f32(e[j]); ss = fmaf(x, x, ss); }
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = Pair<T>::unpack(e[j]);
+        s0 = fmaf(f.x, f.x, s0); s1 = fmaf(f.y, f.y, s1);
+      }
     }
   }
-  return ss;
+  return s0 + s1;
 }
 
 template <typename T, bool EXACT>
@@ -76,23 +80,14 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
   constexpr int NS = EXACT ? 2 : 3;      // ring of streaming stages
   constexpr int RING0 = EXACT ? 1 : 0;   // buffer 0 holds the resident row page in the exact form
   auto stage_ptr = [&](int s) { return bufs + (RING0 + s) * RT_PAGE_BYTES; };
-
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int unit = EXACT ? blockIdx.x / p.NB : blockIdx.x;
-  const int mp = EXACT ? blockIdx.x % p.NB : 0;
-  const int h = unit % p.Hkv, b = (unit / p.Hkv) % p.B, l = unit / (p.Hkv * p.B);
-  const int32_t* table = p.block_table + (int64_t)b * p.NB;
-  PageRef rowpage{0, true, false};
-  if (EXACT) {
-    rowpage = decode_page(table[mp]);
-    if (!rowpage.valid) return;  // whole block; the finalize kernel writes -inf for padded pages
-  }
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < RT_NBUF; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 2); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 8); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 16); }
     mbar_init(&sh.afull, 1);
-    mbar_init(&sh.sync_bar, 256);
+    mbar_init(&sh.aempty, 1);
+    mbar_init(&sh.sync_bar, 16);  // one arrival per epilogue warp
     sh.abort_flag = 0;
     fence_mbar_init();
   }
@@ -107,71 +102,104 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
   volatile int* abortp = &sh.abort_flag;
   constexpr uint32_t IDESC = idesc_f16(UmmaFmt<T>::fmt, 128, 256);
 
+  // job -> (unit, row page).  All roles walk the same job sequence; `t` counts column pages since
+  // kernel start (stage and TMEM-buffer parity), `nj` counts the jobs that had work.
+  struct Job {
+    int unit, mp, h, b, l; const int32_t* table; bool valid;
+    __device__ __forceinline__ Job(const RtParams& p, int job) {
+      unit = EXACT ? job / p.NB : job;
+      mp = EXACT ? job % p.NB : 0;
+      h = unit % p.Hkv; b = (unit / p.Hkv) % p.B; l = unit / (p.Hkv * p.B);
+      table = p.block_table + (int64_t)b * p.NB;
+      valid = EXACT ? table[mp] != -1 : true;
+    }
+  };
+
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       prefetch_tensormap(&tmK);
-      if (EXACT) {
-        mbar_arrive_expect_tx(&sh.afull, RT_PAGE_BYTES);
-        tma_load_5d(bufs, &tmK, &sh.afull, 0, h, 0, rowpage.id, l);
-        tma_load_5d(bufs + RT_BLOCK_BYTES, &tmK, &sh.afull, 64, h, 0, rowpage.id, l);
-      }
-      int t = 0;
-      for (int pg = 0; pg < p.NB; ++pg) {
-        const PageRef cp = decode_page(table[pg]);
-        if (!cp.valid) continue;
-        const int s = t % NS, k = t / NS;
-        if (!mbar_wait(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 101)) break;
-        mbar_arrive_expect_tx(&sh.full[s], RT_PAGE_BYTES);
-        tma_load_5d(stage_ptr(s), &tmK, &sh.full[s], 0, h, 0, cp.id, l);
-        tma_load_5d(stage_ptr(s) + RT_BLOCK_BYTES, &tmK, &sh.full[s], 64, h, 0, cp.id, l);
-        ++t;
+      int t = 0, nj = 0;
+      bool ok = true;
+      for (int job = blockIdx.x; ok && job < p.total_jobs; job += gridDim.x) {
+        const Job jb(p, job);
+        if (!jb.valid) continue;
+        if (EXACT) {
+          if (!mbar_wait(&sh.aempty, (nj & 1) ^ 1, abortp, p.error_word, 100)) break;
+          const int id = decode_page(jb.table[jb.mp]).id;
+          mbar_arrive_expect_tx(&sh.afull, RT_PAGE_BYTES);
+          tma_load_5d(bufs, &tmK, &sh.afull, 0, jb.h, 0, id, jb.l);
+          tma_load_5d(bufs + RT_BLOCK_BYTES, &tmK, &sh.afull, 64, jb.h, 0, id, jb.l);
+        }
+        for (int pg = 0; pg < p.NB; ++pg) {
+          const PageRef cp = decode_page(jb.table[pg]);
+          if (!cp.valid) continue;
+          const int s = t % NS, k = t / NS;
+          if (!mbar_wait(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 101)) { ok = false; break; }
+          mbar_arrive_expect_tx(&sh.full[s], RT_PAGE_BYTES);
+          tma_load_5d(stage_ptr(s), &tmK, &sh.full[s], 0, jb.h, 0, cp.id, jb.l);
+          tma_load_5d(stage_ptr(s) + RT_BLOCK_BYTES, &tmK, &sh.full[s], 64, jb.h, 0, cp.id, jb.l);
+          ++t;
+        }
+        ++nj;
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
+      int t = 0, nj = 0;
       bool ok = true;
-      if (EXACT) ok = mbar_wait(&sh.afull, 0, abortp, p.error_word, 201);
-      int t = 0;
-      for (int pg = 0; ok && pg < p.NB; ++pg) {
-        if (table[pg] == -1) continue;
-        const int s = t % NS, k = t / NS;
-        if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 202)) break;
-        const uint32_t b_addr = smem_u32(stage_ptr(s));
-        const uint32_t a_base = EXACT ? smem_u32(bufs) : b_addr;
-        for (int hh = 0; hh < 2; ++hh) {
-          if (!mbar_wait(&sh.tempty[hh], (t & 1) ^ 1, abortp, p.error_word, 203)) { ok = false; break; }
-          fence_after_sync();
-          umma_k128(tmem_base + hh * 256, a_base + hh * 16384, RT_BLOCK_BYTES, b_addr, RT_BLOCK_BYTES, IDESC);
-          umma_commit(&sh.tfull[hh]);
+      for (int job = blockIdx.x; ok && job < p.total_jobs; job += gridDim.x) {
+        const Job jb(p, job);
+        if (!jb.valid) continue;
+        if (EXACT && !mbar_wait(&sh.afull, nj & 1, abortp, p.error_word, 201)) break;
+        for (int pg = 0; pg < p.NB; ++pg) {
+          if (jb.table[pg] == -1) continue;
+          const int s = t % NS, k = t / NS;
+          if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 202)) { ok = false; break; }
+          const uint32_t b_addr = smem_u32(stage_ptr(s));
+          const uint32_t a_base = EXACT ? smem_u32(bufs) : b_addr;
+          for (int hh = 0; hh < 2; ++hh) {
+            if (!mbar_wait(&sh.tempty[hh], (t & 1) ^ 1, abortp, p.error_word, 203)) { ok = false; break; }
+            fence_after_sync();
+            umma_k128(tmem_base + hh * 256, a_base + hh * 16384, RT_BLOCK_BYTES, b_addr, RT_BLOCK_BYTES, IDESC);
+            umma_commit(&sh.tfull[hh]);
+          }
+          if (!ok) break;
+          umma_commit(&sh.empty[s]);
+          ++t;
         }
-        umma_commit(&sh.empty[s]);
-        ++t;
+        if (EXACT && ok) umma_commit(&sh.aempty);  // the resident row page is no longer read
+        ++nj;
       }
     }
   } else {
     // ---------------- epilogue ----------------
-    // thread (grp, r): rows r (half 0) and r + 128 (half 1) of every item, columns grp*128 .. +127
+    // thread (grp, r): rows r (half 0) and r + 128 (half 1) of every item, columns grp*64 .. +63
     const int q = warp & 3;            // TMEM lane quadrant this warp may read
-    const int grp = (warp - 2) >> 2;   // column group
+    const int grp = (warp - 2) >> 2;   // column group 0..3
     const int r = q * 32 + lane;
-    const int myrow = grp * 128 + r;   // the row this thread normalises / writes
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + grp * 128;
+    const int myrow = (grp & 1) * 128 + r;   // row this thread normalises (groups 0,1) / writes
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + grp * 64;
     const float eps_t = round_to<T>(p.eps);
-    float rsum[2] = {0.f, 0.f}, bval[2] = {0.f, 0.f}, rn_m[2] = {0.f, 0.f}, thr_m[2] = {0.f, 0.f};
-    int bcol[2] = {-1, -1};
-    uint32_t ph = 0;                   // phase of sync_bar (all 256 epilogue threads in lock step)
+    uint32_t ph = 0;                   // phase of sync_bar (all epilogue warps in lock step)
     auto sync_epilogue = [&](int where) -> bool {
-      mbar_arrive(&sh.sync_bar);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.sync_bar);
       const bool ok_ = mbar_wait(&sh.sync_bar, ph & 1, abortp, p.error_word, where);
       ++ph;
       return ok_;
     };
+    int t = 0, nj = 0;
     bool ok = true;
-    if (EXACT) {
-      ok = mbar_wait(&sh.afull, 0, abortp, p.error_word, 301);
-      if (ok) {
+    for (int job = blockIdx.x; ok && job < p.total_jobs; job += gridDim.x) {
+      const Job jb(p, job);
+      if (!jb.valid) continue;
+      const int32_t* table = jb.table;
+      float rsum[2] = {0.f, 0.f}, bval[2] = {0.f, 0.f}, rn_m[2] = {0.f, 0.f}, thr_m[2] = {0.f, 0.f};
+      int bcol[2] = {-1, -1};
+      if (EXACT) {
+        if (!mbar_wait(&sh.afull, nj & 1, abortp, p.error_word, 301)) break;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           const float nrm = fmaxf(round_to<T>(sqrtf(row_sumsq<T>(bufs, r + 128 * hh))), eps_t);
@@ -179,131 +207,134 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
           thr_m[hh] = p.threshold * nrm;
         }
       }
-    }
-    int t = 0;
-    for (int pg = 0; ok && pg < p.NB; ++pg) {
-      if (table[pg] == -1) {
-        if (!EXACT)  // padded page: logits -inf
-          reinterpret_cast<T*>(p.logits_out)[((int64_t)unit * p.NB + pg) * 256 + myrow] = Elem<T>::from_f32(-INFINITY);
-        continue;
-      }
-      const int s = t % NS, k = t / NS;
-      if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 302)) break;
-      float* rn = sh.rn[t & 1];
-      rn[myrow] = 1.f / fmaxf(round_to<T>(sqrtf(row_sumsq<T>(stage_ptr(s), myrow))), eps_t);
-      if (!EXACT) sh.s_sub[myrow] = 0ull;
-      if (!sync_epilogue(303)) break;
-      if (myrow == 0) mbar_arrive(&sh.empty[s]);  // every epilogue thread is done reading the stage
-      if (!EXACT) {
+      for (int pg = 0; pg < p.NB; ++pg) {
+        if (table[pg] == -1) {
+          if (!EXACT && grp < 2)  // padded page: logits -inf
+            reinterpret_cast<T*>(p.logits_out)[((int64_t)jb.unit * p.NB + pg) * 256 + myrow] = Elem<T>::from_f32(-INFINITY);
+          continue;
+        }
+        const int s = t % NS, k = t / NS;
+        if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 302)) { ok = false; break; }
+        float* rn = sh.rn[t & 1];
+        if (grp < 2) {
+          rn[myrow] = 1.f / fmaxf(round_to<T>(sqrtf(row_sumsq<T>(stage_ptr(s), myrow))), eps_t);
+          if (!EXACT) sh.s_sub[myrow] = 0ull;
+        }
+        if (!sync_epilogue(303)) { ok = false; break; }
+        if (warp == 2 && lane == 0) mbar_arrive(&sh.empty[s]);  // the epilogue is done reading the stage
+        if (!EXACT) {
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            rn_m[hh] = rn[r + 128 * hh]; thr_m[hh] = p.threshold / rn_m[hh];
+            rsum[hh] = 0.f; bcol[hh] = -1; bval[hh] = 0.f;
+          }
+        }
+        const bool diag_page = EXACT ? (pg == jb.mp) : true;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          rn_m[hh] = rn[r + 128 * hh]; thr_m[hh] = p.threshold / rn_m[hh];
-          rsum[hh] = 0.f; bcol[hh] = -1; bval[hh] = 0.f;
+          if (!mbar_wait(&sh.tfull[hh], t & 1, abortp, p.error_word, 304)) { ok = false; break; }
+          fence_after_sync();
+          const uint32_t tbase = lane_base + hh * 256;
+          float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t raw[32];
+            tmem_ld32_issue(tbase + c * 32, raw);
+            tmem_ld32_wait(raw);
+            if (c == 1) {  // every TMEM read of this item has landed in registers
+              fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&sh.tempty[hh]);
+            }
+            const int cg = grp * 2 + c;  // chunk index within the 256 columns
+            const float4* rn4 = reinterpret_cast<const float4*>(rn + cg * 32);
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 f = rn4[j];
+              v[4 * j] = __uint_as_float(raw[4 * j]) * f.x; v[4 * j + 1] = __uint_as_float(raw[4 * j + 1]) * f.y;
+              v[4 * j + 2] = __uint_as_float(raw[4 * j + 2]) * f.z; v[4 * j + 3] = __uint_as_float(raw[4 * j + 3]) * f.w;
+            }
+            if (diag_page && cg == hh * 4 + q) {  // warp-uniform: the chunk that holds this warp's diagonal
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = (j == lane) ? 0.f : v[j];
+            }
+            float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              s0 += v[j]; s1 += v[j + 1]; s2 += v[j + 2]; s3 += v[j + 3];
+              m0 = fmaxf(m0, v[j]); m1 = fmaxf(m1, v[j + 1]); m2 = fmaxf(m2, v[j + 2]); m3 = fmaxf(m3, v[j + 3]);
+            }
+            if (fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) > thr_m[hh]) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (v[j] > thr_m[hh]) { bcol[hh] = pg * 256 + cg * 32 + j; bval[hh] = v[j]; }
+            }
+          }
+          rsum[hh] += (s0 + s1) + (s2 + s3);
         }
-      }
-      const bool diag_page = EXACT ? (pg == mp) : true;
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        if (!mbar_wait(&sh.tfull[hh], t & 1, abortp, p.error_word, 304)) { ok = false; break; }
-        fence_after_sync();
-        const uint32_t tbase = lane_base + hh * 256;
-        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-        auto process = [&](const uint32_t (&raw)[32], int c) {
-          const int cg = grp * 4 + c;  // chunk index within the 256 columns
-          const float4* rn4 = reinterpret_cast<const float4*>(rn + cg * 32);
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float4 f = rn4[j];
-            v[4 * j] = __uint_as_float(raw[4 * j]) * f.x; v[4 * j + 1] = __uint_as_float(raw[4 * j + 1]) * f.y;
-            v[4 * j + 2] = __uint_as_float(raw[4 * j + 2]) * f.z; v[4 * j + 3] = __uint_as_float(raw[4 * j + 3]) * f.w;
-          }
-          if (diag_page && cg == hh * 4 + q) {  // warp-uniform: the chunk that holds this warp's diagonal
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = (j == lane) ? 0.f : v[j];
-          }
-          float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            s0 += v[j]; s1 += v[j + 1]; s2 += v[j + 2]; s3 += v[j + 3];
-            m0 = fmaxf(m0, v[j]); m1 = fmaxf(m1, v[j + 1]); m2 = fmaxf(m2, v[j + 2]); m3 = fmaxf(m3, v[j + 3]);
-          }
-          if (fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) > thr_m[hh]) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (v[j] > thr_m[hh]) { bcol[hh] = pg * 256 + cg * 32 + j; bval[hh] = v[j]; }
-          }
-        };
-        uint32_t ra[32], rb[32];
-        tmem_ld32_issue(tbase, ra);
-        tmem_ld32_wait(ra);
-        tmem_ld32_issue(tbase + 32, rb);
-        process(ra, 0);
-        tmem_ld32_wait(rb);
-        tmem_ld32_issue(tbase + 64, ra);
-        process(rb, 1);
-        tmem_ld32_wait(ra);
-        tmem_ld32_issue(tbase + 96, rb);
-        process(ra, 2);
-        tmem_ld32_wait(rb);
-        fence_before_sync();   // every TMEM read of this item has landed in registers
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh.tempty[hh]);
-        process(rb, 3);
-        rsum[hh] += (s0 + s1) + (s2 + s3);
-      }
-      if (!ok) break;
-      if (!EXACT) {
-        // page done: merge the two column groups, subtract the exempted entries, write the logits
-        if (grp == 1) {
+        if (!ok) break;
+        if (!EXACT) {
+          // page done: merge the four column groups, subtract the exempted entries, write the logits
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
-            sh.pb_sum[r + 128 * hh] = rsum[hh]; sh.pb_col[r + 128 * hh] = bcol[hh]; sh.pb_val[r + 128 * hh] = bval[hh];
+            sh.pb_sum[grp][r + 128 * hh] = rsum[hh]; sh.pb_col[grp][r + 128 * hh] = bcol[hh];
+            sh.pb_val[grp][r + 128 * hh] = bval[hh];
           }
-        }
-        if (!sync_epilogue(305)) break;
-        if (grp == 0) {
+          if (!sync_epilogue(305)) { ok = false; break; }
+          if (grp < 2) {
+            const int row = myrow;
+            float total = 0.f, bv = 0.f;
+            int bc = -1;
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            const int row = r + 128 * hh;
-            const float total = rsum[hh] + sh.pb_sum[row];
-            const int bc = sh.pb_col[row] >= 0 ? sh.pb_col[row] : bcol[hh];   // upper columns win
-            const float bv = sh.pb_col[row] >= 0 ? sh.pb_val[row] : bval[hh];
-            sh.s_sum[row] = total * rn_m[hh];
+            for (int g = 0; g < 4; ++g) {   // fixed order; higher column groups win
+              total += sh.pb_sum[g][row];
+              if (sh.pb_col[g][row] >= 0) { bc = sh.pb_col[g][row]; bv = sh.pb_val[g][row]; }
+            }
+            const float rnm = rn[row];
+            sh.s_sum[row] = total * rnm;
             if (bc >= 0) {
-              const long long fx = __float2ll_rn(bv * rn_m[hh] * 4294967296.f);
+              const long long fx = __float2ll_rn(bv * rnm * 4294967296.f);
               atomicAdd(&sh.s_sub[bc - pg * 256], (unsigned long long)fx);
             }
           }
+          if (!sync_epilogue(306)) { ok = false; break; }
+          if (grp < 2) {
+            const float sub = (float)((double)(long long)sh.s_sub[myrow] * (1.0 / 4294967296.0));
+            reinterpret_cast<T*>(p.logits_out)[((int64_t)jb.unit * p.NB + pg) * 256 + myrow] =
+                Elem<T>::from_f32(sh.s_sum[myrow] - sub);
+          }
         }
-        if (!sync_epilogue(306)) break;
-        const float sub = (float)((double)(long long)sh.s_sub[myrow] * (1.0 / 4294967296.0));
-        reinterpret_cast<T*>(p.logits_out)[((int64_t)unit * p.NB + pg) * 256 + myrow] =
-            Elem<T>::from_f32(sh.s_sum[myrow] - sub);
+        ++t;
       }
-      ++t;
-    }
-    if (EXACT && ok && !*abortp) {
-      if (grp == 1) {
+      if (!ok) break;
+      if (EXACT) {
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          sh.pb_sum[r + 128 * hh] = rsum[hh]; sh.pb_col[r + 128 * hh] = bcol[hh]; sh.pb_val[r + 128 * hh] = bval[hh];
+          sh.pb_sum[grp][r + 128 * hh] = rsum[hh]; sh.pb_col[grp][r + 128 * hh] = bcol[hh];
+          sh.pb_val[grp][r + 128 * hh] = bval[hh];
         }
-      }
-      if (sync_epilogue(307) && grp == 0) {
-        const int64_t base = (int64_t)unit * p.NB * 256;
+        if (!sync_epilogue(307)) break;
+        if (grp < 2) {
+          const int row = myrow;
+          const int64_t base = (int64_t)jb.unit * p.NB * 256;
+          float total = 0.f, bv = 0.f;
+          int bc = -1;
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          const int row = r + 128 * hh;
-          const int bc = sh.pb_col[row] >= 0 ? sh.pb_col[row] : bcol[hh];
-          const float bv = sh.pb_col[row] >= 0 ? sh.pb_val[row] : bval[hh];
-          p.rowsum[base + mp * 256 + row] = (rsum[hh] + sh.pb_sum[row]) * rn_m[hh];
+          for (int g = 0; g < 4; ++g) {
+            total += sh.pb_sum[g][row];
+            if (sh.pb_col[g][row] >= 0) { bc = sh.pb_col[g][row]; bv = sh.pb_val[g][row]; }
+          }
+          const float rnm = grp == 0 ? rn_m[0] : rn_m[1];
+          p.rowsum[base + jb.mp * 256 + row] = total * rnm;
           if (bc >= 0) {
-            const long long fx = __float2ll_rn(bv * rn_m[hh] * 4294967296.f);
+            const long long fx = __float2ll_rn(bv * rnm * 4294967296.f);
             atomicAdd(reinterpret_cast<unsigned long long*>(p.sub + base + bc), (unsigned long long)fx);
           }
         }
+        if (!sync_epilogue(308)) break;  // pb_* are free again
       }
+      ++nj;
     }
   }
   fence_before_sync();
@@ -327,15 +358,21 @@ static int launch_redundancy_tc(const void* k_cache, const RtParams& p, int64_t 
   if (rc) return rc;
   const size_t smem = RT_NBUF * RT_PAGE_BYTES + sizeof(RtShared) + 1024;
   const int units = p.L * p.B * p.Hkv;
+  RtParams pp = p;
+  pp.total_jobs = exact ? units * p.NB : units;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = pp.total_jobs < sms ? pp.total_jobs : sms;
   cudaError_t e;
   if (exact) {
     auto kern = redundancy_tc_kernel<T, true>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) kern<<<units * p.NB, RT_THREADS, smem, st>>>(tm, p);
+    if (e == cudaSuccess) kern<<<grid, RT_THREADS, smem, st>>>(tm, pp);
   } else {
     auto kern = redundancy_tc_kernel<T, false>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) kern<<<units, RT_THREADS, smem, st>>>(tm, p);
+    if (e == cudaSuccess) kern<<<grid, RT_THREADS, smem, st>>>(tm, pp);
   }
   if (e != cudaSuccess) { set_error("zp_redundancy(tcgen05): %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
   return check_launch("zp_redundancy(tcgen05)");
