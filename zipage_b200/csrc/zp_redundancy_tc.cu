@@ -42,6 +42,7 @@ struct RtParams {
 struct __align__(16) RtShared {
   uint64_t full[RT_NBUF], empty[RT_NBUF], tfull[2], tempty[2], afull, aempty, sync_bar;
   alignas(16) float rn[2][256];     // 1 / |k| of the column page (double-buffered over pages)
+  float nmin[2][8];                 // smallest |k| of each 32-column chunk of that page
   float s_sum[256];                 // combined row sums of a page (lightning)
   float pb_sum[4][256], pb_val[4][256];  // per column group partials of rows 0..255
   int pb_col[4][256];
@@ -53,7 +54,7 @@ struct __align__(16) RtShared {
 // sum of squares of one 128-element row of a swizzled [256][128] tile (two 64-column blocks)
 template <typename T>
 __device__ __forceinline__ float row_sumsq(const unsigned char* tile, int row) {
-  float s0 = 0.f, s1 = 0.f;
+  float2 a0 = make_float2(0.f, 0.f), a1 = a0, a2 = a0, a3 = a0;
 #pragma unroll
   for (int blk = 0; blk < 2; ++blk) {
     const unsigned char* base = tile + blk * RT_BLOCK_BYTES + row * 128;
@@ -61,14 +62,12 @@ __device__ __forceinline__ float row_sumsq(const unsigned char* tile, int row) {
     for (int c = 0; c < 8; ++c) {
       const int4 raw = *reinterpret_cast<const int4*>(base + ((c ^ (row & 7)) << 4));
       const typename Pair<T>::V* e = reinterpret_cast<const typename Pair<T>::V*>(&raw);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = Pair<T>::unpack(e[j]);
-        s0 = fmaf(f.x, f.x, s0); s1 = fmaf(f.y, f.y, s1);
-      }
+      const float2 f0 = Pair<T>::unpack(e[0]), f1 = Pair<T>::unpack(e[1]);
+      const float2 f2 = Pair<T>::unpack(e[2]), f3 = Pair<T>::unpack(e[3]);
+      ffma2(a0, f0, f0); ffma2(a1, f1, f1); ffma2(a2, f2, f2); ffma2(a3, f3, f3);
     }
   }
-  return s0 + s1;
+  return ((a0.x + a0.y) + (a1.x + a1.y)) + ((a2.x + a2.y) + (a3.x + a3.y));
 }
 
 template <typename T, bool EXACT>
@@ -125,7 +124,7 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
         const Job jb(p, job);
         if (!jb.valid) continue;
         if (EXACT) {
-          if (!mbar_wait(&sh.aempty, (nj & 1) ^ 1, abortp, p.error_word, 100)) break;
+          if (!mbar_wait<true>(&sh.aempty, (nj & 1) ^ 1, abortp, p.error_word, 100)) break;
           const int id = decode_page(jb.table[jb.mp]).id;
           mbar_arrive_expect_tx(&sh.afull, RT_PAGE_BYTES);
           tma_load_5d(bufs, &tmK, &sh.afull, 0, jb.h, 0, id, jb.l);
@@ -135,7 +134,7 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
           const PageRef cp = decode_page(jb.table[pg]);
           if (!cp.valid) continue;
           const int s = t % NS, k = t / NS;
-          if (!mbar_wait(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 101)) { ok = false; break; }
+          if (!mbar_wait<true>(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 101)) { ok = false; break; }
           mbar_arrive_expect_tx(&sh.full[s], RT_PAGE_BYTES);
           tma_load_5d(stage_ptr(s), &tmK, &sh.full[s], 0, jb.h, 0, cp.id, jb.l);
           tma_load_5d(stage_ptr(s) + RT_BLOCK_BYTES, &tmK, &sh.full[s], 64, jb.h, 0, cp.id, jb.l);
@@ -152,15 +151,15 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
       for (int job = blockIdx.x; ok && job < p.total_jobs; job += gridDim.x) {
         const Job jb(p, job);
         if (!jb.valid) continue;
-        if (EXACT && !mbar_wait(&sh.afull, nj & 1, abortp, p.error_word, 201)) break;
+        if (EXACT && !mbar_wait<true>(&sh.afull, nj & 1, abortp, p.error_word, 201)) break;
         for (int pg = 0; pg < p.NB; ++pg) {
           if (jb.table[pg] == -1) continue;
           const int s = t % NS, k = t / NS;
-          if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 202)) { ok = false; break; }
+          if (!mbar_wait<true>(&sh.full[s], k & 1, abortp, p.error_word, 202)) { ok = false; break; }
           const uint32_t b_addr = smem_u32(stage_ptr(s));
           const uint32_t a_base = EXACT ? smem_u32(bufs) : b_addr;
           for (int hh = 0; hh < 2; ++hh) {
-            if (!mbar_wait(&sh.tempty[hh], (t & 1) ^ 1, abortp, p.error_word, 203)) { ok = false; break; }
+            if (!mbar_wait<true>(&sh.tempty[hh], (t & 1) ^ 1, abortp, p.error_word, 203)) { ok = false; break; }
             fence_after_sync();
             umma_k128(tmem_base + hh * 256, a_base + hh * 16384, RT_BLOCK_BYTES, b_addr, RT_BLOCK_BYTES, IDESC);
             umma_commit(&sh.tfull[hh]);
@@ -216,8 +215,13 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
         const int s = t % NS, k = t / NS;
         if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 302)) { ok = false; break; }
         float* rn = sh.rn[t & 1];
-        if (grp < 2) {
-          rn[myrow] = 1.f / fmaxf(round_to<T>(sqrtf(row_sumsq<T>(stage_ptr(s), myrow))), eps_t);
+        if (grp < 2) {   // a warp covers exactly one 32-column chunk of the page
+          const float nrm = fmaxf(round_to<T>(sqrtf(row_sumsq<T>(stage_ptr(s), myrow))), eps_t);
+          rn[myrow] = 1.f / nrm;
+          float mn = nrm;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+          if (lane == 0) sh.nmin[t & 1][(grp & 1) * 4 + q] = mn;
           if (!EXACT) sh.s_sub[myrow] = 0ull;
         }
         if (!sync_epilogue(303)) { ok = false; break; }
@@ -235,7 +239,7 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
           if (!mbar_wait(&sh.tfull[hh], t & 1, abortp, p.error_word, 304)) { ok = false; break; }
           fence_after_sync();
           const uint32_t tbase = lane_base + hh * 256;
-          float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+          float2 sa = make_float2(0.f, 0.f), sb = sa;
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             uint32_t raw[32];
@@ -247,30 +251,34 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
               if (lane == 0) mbar_arrive(&sh.tempty[hh]);
             }
             const int cg = grp * 2 + c;  // chunk index within the 256 columns
+            if (diag_page && cg == hh * 4 + q) {  // warp-uniform: the chunk that holds this warp's diagonal
+#pragma unroll
+              for (int j = 0; j < 32; ++j) raw[j] = (j == lane) ? 0u : raw[j];
+            }
+            // row sum: acc * (1/|k_n|) accumulated two columns at a time; threshold filter on the raw
+            // accumulators: S > thr needs acc > thr * |k_m| * |k_n| >= thr * |k_m| * min|k_n|
             const float4* rn4 = reinterpret_cast<const float4*>(rn + cg * 32);
-            float v[32];
+            float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const float4 f = rn4[j];
-              v[4 * j] = __uint_as_float(raw[4 * j]) * f.x; v[4 * j + 1] = __uint_as_float(raw[4 * j + 1]) * f.y;
-              v[4 * j + 2] = __uint_as_float(raw[4 * j + 2]) * f.z; v[4 * j + 3] = __uint_as_float(raw[4 * j + 3]) * f.w;
+              const float a0 = __uint_as_float(raw[4 * j]), a1 = __uint_as_float(raw[4 * j + 1]);
+              const float a2 = __uint_as_float(raw[4 * j + 2]), a3 = __uint_as_float(raw[4 * j + 3]);
+              ffma2(sa, make_float2(a0, a1), make_float2(f.x, f.y));
+              ffma2(sb, make_float2(a2, a3), make_float2(f.z, f.w));
+              m0 = fmax3(m0, a0, a1);
+              m1 = fmax3(m1, a2, a3);
             }
-            if (diag_page && cg == hh * 4 + q) {  // warp-uniform: the chunk that holds this warp's diagonal
+            if (fmaxf(m0, m1) > thr_m[hh] * sh.nmin[t & 1][cg]) {  // rare: look at the normalised values
+              const float* rnc = rn + cg * 32;
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = (j == lane) ? 0.f : v[j];
-            }
-            float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              s0 += v[j]; s1 += v[j + 1]; s2 += v[j + 2]; s3 += v[j + 3];
-              m0 = fmaxf(m0, v[j]); m1 = fmaxf(m1, v[j + 1]); m2 = fmaxf(m2, v[j + 2]); m3 = fmaxf(m3, v[j + 3]);
-            }
-            if (fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) > thr_m[hh]) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (v[j] > thr_m[hh]) { bcol[hh] = pg * 256 + cg * 32 + j; bval[hh] = v[j]; }
+              for (int j = 0; j < 32; ++j) {
+                const float v = __uint_as_float(raw[j]) * rnc[j];
+                if (v > thr_m[hh]) { bcol[hh] = pg * 256 + cg * 32 + j; bval[hh] = v; }
+              }
             }
           }
+          const float s0 = sa.x, s1 = sa.y, s2 = sb.x, s3 = sb.y;
           rsum[hh] += (s0 + s1) + (s2 + s3);
         }
         if (!ok) break;

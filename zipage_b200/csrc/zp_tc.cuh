@@ -48,11 +48,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when the block is aborting (this wait ran out, or another role's did).
+// BACKOFF: sleep between polls — for the single-thread producer / MMA roles, whose polling would
+// otherwise take issue slots from the epilogue warps that share their scheduler.
+template <bool BACKOFF = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* error_word, int where) {
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
+    if (BACKOFF) __nanosleep(64);
   }
   *abort_flag = 1;
   atomicCAS(error_word, 0, where);
@@ -139,6 +143,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   tmem_ld32_wait(r);
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// ---- packed fp32 pairs and 3-input max (sm_100) ----
+__device__ __forceinline__ void ffma2(float2& d, float2 a, float2 b) {  // d += a * b, both lanes
+  asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mov.b64 rc, {%0, %1};\n\tfma.rn.f32x2 rc, ra, rb, rc;\n\tmov.b64 {%0, %1}, rc;\n\t}"
+      : "+f"(d.x), "+f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 
 // ---- packed 16-bit pairs (two values per 32-bit register, element 0 in the low half) ----

@@ -178,7 +178,7 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         const Unit un(p, unit);
         if (un.ntiles == 0) continue;
         const int qb = n & 1;
-        if (!mbar_wait(&sh.qempty[qb], ((n >> 1) & 1) ^ 1, abortp, p.error_word, 110)) break;
+        if (!mbar_wait<true>(&sh.qempty[qb], ((n >> 1) & 1) ^ 1, abortp, p.error_word, 110)) break;
         mbar_arrive_expect_tx(&sh.qfull[qb], (uint32_t)(2 * R * 128));
         const int qid = p.seq_idx[un.b];
         unsigned char* qbuf = qbufs + qb * 2 * WT_QBLOCK_BYTES;
@@ -190,7 +190,7 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
           int entry;
           cur.next(tt, un.ntiles, entry);
           const int s = gt % WT_NS, k = gt / WT_NS;
-          if (!mbar_wait(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 111)) { ok = false; break; }
+          if (!mbar_wait<true>(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 111)) { ok = false; break; }
           const int id = decode_page(entry).id;
           mbar_arrive_expect_tx(&sh.full[s], WT_PAGE_BYTES);
           tma_load_5d(bufs + s * WT_PAGE_BYTES, &tmK, &sh.full[s], 0, un.h, 0, id, un.l);
@@ -209,13 +209,13 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         const Unit un(p, unit);
         if (un.ntiles == 0) continue;
         const int qb = n & 1;
-        if (!mbar_wait(&sh.qfull[qb], (n >> 1) & 1, abortp, p.error_word, 211)) break;
+        if (!mbar_wait<true>(&sh.qfull[qb], (n >> 1) & 1, abortp, p.error_word, 211)) break;
         const uint32_t q_addr = smem_u32(qbufs + qb * 2 * WT_QBLOCK_BYTES);
         for (int tt = 0; tt < un.ntiles; ++tt, ++gt) {
           const int sweep = tt / un.nvalid;
           const int s = gt % WT_NS, k = gt / WT_NS, buf = gt & 1, u = gt >> 1;
-          if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 212)) { ok = false; break; }
-          if (!mbar_wait(&sh.tempty[buf], (u & 1) ^ 1, abortp, p.error_word, 213)) { ok = false; break; }
+          if (!mbar_wait<true>(&sh.full[s], k & 1, abortp, p.error_word, 212)) { ok = false; break; }
+          if (!mbar_wait<true>(&sh.tempty[buf], (u & 1) ^ 1, abortp, p.error_word, 213)) { ok = false; break; }
           fence_after_sync();
           const uint32_t k_addr = smem_u32(bufs + s * WT_PAGE_BYTES);
           const uint32_t d = tmem_base + buf * 256;
