@@ -291,7 +291,28 @@ def main():
                      "global_score_sum": "window_score"}.get(top, "window_score")
         nlaunch = (L + chunk - 1) // chunk
         top_ms = stage_ms.get(top, ms_step) / nlaunch
-        achieved = stages[stage_key] * units / nlaunch / (top_ms * 1e-3) / 1e9
+        # DRAM bytes per unit of each kernel from the committed ncu capture of a 1024-unit case
+        # (profiles/compress_op_tcgen05_kernels_b32_l4.md); traffic grows in proportion to the units
+        ncu_bytes_per_unit = {"window_score": 760.809e6 / 1024, "redundancy": 614.333e6 / 1024,
+                              "compact": 2072.943e6 / 1024, "select": 9.48e6 / 1024}
+        if stage_key == "redundancy" and args.variant == "exact":
+            n_tok = (BUDGET + 1) * BS
+            flops = 2.0 * n_tok * n_tok * D * units / nlaunch
+            peak = peaks.get("bf16_tflops_sustained", 1400.0)
+            achieved = flops / (top_ms * 1e-3) / 1e12
+            roofline = {"bound": "tensor", "kernel": "redundancy_tc (exact)", "achieved": achieved,
+                        "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                        "peak_source": "measured sustained cuBLAS bf16 (MEASURED_PEAKS.json)" if peaks
+                        else "fallback", "traffic": None}
+        else:
+            achieved = stages[stage_key] * units / nlaunch / (top_ms * 1e-3) / 1e9
+            traffic = None
+            if args.variant == "lightning" and args.kernel_impl != "simt":
+                traffic = ncu_bytes_per_unit[stage_key] * units / nlaunch
+            roofline = {"bound": "hbm", "kernel": stage_key, "achieved": achieved, "peak": hbm_peak,
+                        "unit": "GB/s", "frac": achieved / hbm_peak,
+                        "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
+                        "traffic": traffic}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -313,10 +334,7 @@ def main():
                     "ms_per_step": e2e_ms},
             "gpu_launches": launches,
             "clocks": clocks.summary(),
-            "roofline": {"bound": "hbm", "kernel": stage_key, "achieved": achieved, "peak": hbm_peak,
-                         "unit": "GB/s", "frac": achieved / hbm_peak,
-                         "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
-                         "traffic": None},
+            "roofline": roofline,
         }
         if not args.no_cpu_baseline and world == 1:
             threads = os.cpu_count() or 1
