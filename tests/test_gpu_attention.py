@@ -103,3 +103,48 @@ def test_attention_layer_contract():
     ref = O.paged_decode_attention(q.unsqueeze(1), kc, vc, lens, table)
     assert torch.equal(kc_d.cpu(), kc) and torch.equal(layer.q_cache.cpu(), qcache)
     assert (out.float() - ref.float()).abs().max() <= 2e-2 * ref.float().abs().max()
+
+
+def test_compress_then_decode_over_compacted_tables():
+    """The path end to end on device: compress a batch, update the tables on the GPU, append one
+    token with store_kvcache at the slot the table update names, and decode over the compacted
+    pages.  The result must equal fp32 attention over exactly the kept tokens plus the new one."""
+    from oracle import zipage_oracle as O
+    from zipage_b200 import kernel as K
+    from zipage_b200.compress import CompressConfig, compress_chunk
+    from zipage_b200.layers.attention import paged_decode_attention
+    from zipage_b200.synthetic import make_compress_workload
+    dev = torch.device("cuda:0")
+    Hkv, Hq, D, budget = 2, 8, 128, 2
+    w = make_compress_workload(B=3, L=1, Hkv=Hkv, Hq=Hq, QCL=16, budget=budget, pages_per_seq=[3, 4, 3],
+                               dtype=torch.bfloat16, device=dev, seed=77, spare_pages=1,
+                               compressed_prob=0.5, fresh_target_prob=1.0)
+    k0, v0 = w.kv_cache[0, 0].clone().cpu(), w.kv_cache[1, 0].clone().cpu()
+    cfg = CompressConfig(budget_blocks=budget, query_cache_len=16, use_redudancy=True,
+                         lightning_redudancy=True, enable_pooling=True)
+    dbg = compress_chunk(w.kv_cache[0], w.kv_cache[1], w.query_cache, None, w.query_ids,
+                         w.block_tables, w.target_tables, w.compressed, cfg, return_debug=True)
+    new_tables, ctx, nxt = K.update_tables(w.target_tables)
+    # one new token per sequence goes to the first slot of the page after the budget
+    g = torch.Generator().manual_seed(1)
+    kn = torch.randn(3, Hkv, D, generator=g).to(torch.bfloat16)
+    vn = torch.randn(3, Hkv, D, generator=g).to(torch.bfloat16)
+    q = torch.randn(3, 1, Hq, D, generator=g).to(torch.bfloat16)
+    K.store_kvcache(kn.to(dev), vn.to(dev), w.kv_cache[0, 0], w.kv_cache[1, 0], nxt)
+    out = paged_decode_attention(q.to(dev), w.kv_cache[0, 0], w.kv_cache[1, 0], ctx, new_tables).cpu()
+    torch.cuda.synchronize()
+    assert ctx.cpu().tolist() == [budget * BS + 1] * 3
+    keep = dbg["keep"].cpu()[0]                      # [B,Hkv,NB,BS]
+    plain = w.tables_plain.cpu()
+    for b in range(3):
+        for h in range(Hkv):
+            idx = keep[b, h].flatten().nonzero().flatten()
+            pages = plain[b][idx // BS].long()
+            kk = torch.cat([k0[pages, idx % BS, h], kn[b, h][None]]).float()
+            vv = torch.cat([v0[pages, idx % BS, h], vn[b, h][None]]).float()
+            G = Hq // Hkv
+            qq = q[b, 0, h * G:(h + 1) * G].float()
+            p = torch.softmax(qq @ kk.t() * D ** -0.5, dim=-1)
+            ref = p @ vv
+            got = out[b, 0, h * G:(h + 1) * G].float()
+            assert (got - ref).abs().max() <= 2e-2 * ref.abs().max()

@@ -209,7 +209,13 @@ static int dispatch_decode(const DecArgs& a, int D, int G, cudaStream_t st) {
   return ZP_ERR_UNSUPPORTED;
 }
 
-static int gp_of(int G) { return G == 1 ? 1 : G == 2 ? 2 : G <= 4 ? 4 : 8; }
+static int gp_of(int G) { return G == 1 ? 1 : G == 2 ? 2 : G <= 4 ? 4 : G <= 8 ? 8 : 16; }
+
+// tensor-core path for 16-bit caches (zp_decode_mma.cu)
+int paged_decode_mma(const void* q, const void* k, const void* v, const int32_t* seqlens,
+                     const int32_t* table, void* out, float* part, int B, int NBmax, int Hq, int Hkv,
+                     int BS, int nsplit, int gp, int64_t kv_stride_page, float scale_log2e, int dtype,
+                     cudaStream_t st);
 
 }  // namespace zp
 
@@ -243,6 +249,11 @@ extern "C" int zp_paged_decode(const void* q, const void* k_cache, const void* v
     else a.part = reinterpret_cast<float*>(workspace);
   }
   cudaStream_t st = (cudaStream_t)stream;
+  const bool mma = (dtype == ZP_DTYPE_BF16 || dtype == ZP_DTYPE_F16) && D == 128 && BS % 64 == 0 && G <= 16;
+  if (mma)
+    return zp::paged_decode_mma(q, k_cache, v_cache, cache_seqlens, block_table, out, a.part, B, NBmax,
+                                Hq, Hkv, BS, a.nsplit, zp::gp_of(G), kv_stride_page, a.scale_log2e, dtype,
+                                st);
   ZP_DISPATCH_DTYPE(dtype, T, { return zp::dispatch_decode<T>(a, D, G, st); });
   return ZP_OK;
 }
