@@ -148,3 +148,23 @@ def test_compress_then_decode_over_compacted_tables():
             ref = p @ vv
             got = out[b, 0, h * G:(h + 1) * G].float()
             assert (got - ref).abs().max() <= 2e-2 * ref.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_varlen_prefill_long_ragged(dtype):
+    """Several 64-key tiles, ragged lengths around tile and page boundaries, GQA group of 4."""
+    from oracle import zipage_oracle as O
+    from zipage_b200.layers.attention import varlen_prefill_attention
+    dev = torch.device("cuda:0")
+    Hq, Hkv, D = 8, 2, 128
+    g = torch.Generator().manual_seed(11)
+    lens = [1000, 63, 64, 65, 257, 1, 512]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    tot = int(cu[-1])
+    q = torch.randn(tot, Hq, D, generator=g).to(dtype)
+    k = torch.randn(tot, Hkv, D, generator=g).to(dtype)
+    v = torch.randn(tot, Hkv, D, generator=g).to(dtype)
+    ref = O.varlen_prefill_attention(q, k, v, cu, cu)
+    out = varlen_prefill_attention(q.to(dev), k.to(dev), v.to(dev), max(lens), cu.to(dev), max(lens),
+                                   cu.to(dev)).cpu()
+    assert (out.float() - ref.float()).abs().max() <= 2e-2 * ref.float().abs().max()

@@ -173,6 +173,12 @@ static int launch_prefill(const PfArgs& a, int max_seqlen_q, cudaStream_t st) {
   return check_launch("zp_varlen_prefill");
 }
 
+// tensor-core path for 16-bit tensors (zp_prefill_mma.cu)
+int varlen_prefill_mma(const void* q, const void* k, const void* v, const int32_t* cu_q, const int32_t* cu_k,
+                       const int32_t* table, void* out, int B, int max_seqlen_q, int NBmax, int Hq,
+                       int Hkv, int BS, int64_t kv_stride_page, float scale_log2e, int dtype,
+                       cudaStream_t st);
+
 }  // namespace zp
 
 extern "C" int zp_varlen_prefill(const void* q, const void* k, const void* v,
@@ -191,6 +197,10 @@ extern "C" int zp_varlen_prefill(const void* q, const void* k, const void* v,
   a.kv_stride_page = kv_stride_page;
   a.scale_log2e = softmax_scale * 1.4426950408889634f;
   cudaStream_t st = (cudaStream_t)stream;
+  if ((dtype == ZP_DTYPE_BF16 || dtype == ZP_DTYPE_F16) && D == 128 &&
+      ((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) % 16 == 0)
+    return zp::varlen_prefill_mma(q, k, v, cu_seqlens_q, cu_seqlens_k, block_table, out, B, max_seqlen_q,
+                                  NBmax, Hq, Hkv, BS, kv_stride_page, a.scale_log2e, dtype, st);
   ZP_DISPATCH_DTYPE(dtype, T, {
     if (D == 128) return zp::launch_prefill<T, 128>(a, max_seqlen_q, st);
     return zp::launch_prefill<T, 64>(a, max_seqlen_q, st);
