@@ -1,0 +1,92 @@
+"""Edge cases of the compression path on the GPU: empty batches, long ragged tables with fresh
+target pages (first compression of a long prompt), group sizes the tensor-core kernel does not
+cover, tables shorter than the budget, oversized rows."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+BS = 256
+
+
+def _run_both(w, cfg_kwargs, dtype, impl="auto"):
+    from oracle import zipage_oracle as O
+    from zipage_b200.compress import CompressConfig, compress_chunk
+    ko, vo = w.kv_cache[0].cpu().clone(), w.kv_cache[1].cpu().clone()
+    sco = None if w.score_cache is None else w.score_cache.cpu().clone()
+    final_o, keep_o = O.compress(ko, vo, w.query_cache.cpu(), sco, w.query_ids.cpu(), w.block_tables.cpu(),
+                                 w.target_tables.cpu(), w.compressed.cpu(), O.CompressConfig(**cfg_kwargs))
+    dbg = compress_chunk(w.kv_cache[0], w.kv_cache[1], w.query_cache, w.score_cache, w.query_ids,
+                         w.block_tables, w.target_tables, w.compressed, CompressConfig(**cfg_kwargs),
+                         impl=impl, return_debug=True)
+    torch.cuda.synchronize()
+    return (final_o, keep_o, ko, vo), dbg
+
+
+def test_empty_batch_is_a_noop():
+    from zipage_b200 import kernel as K
+    dev = torch.device("cuda:0")
+    k = torch.zeros(2, 4, BS, 2, 128, device=dev, dtype=torch.bfloat16)
+    q = torch.zeros(2, 3, 16, 4, 128, device=dev, dtype=torch.bfloat16)
+    bt = torch.zeros(0, 3, dtype=torch.int32, device=dev)
+    s = K.attention_score(k, q, torch.zeros(0, dtype=torch.int32, device=dev), bt)
+    assert s.shape == (2, 0, 2, 3, BS)
+    K.compress_kv(k, k.clone(), torch.zeros(2, 0, 2, 3, BS, dtype=torch.bool, device=dev), bt,
+                  torch.zeros(0, 3, dtype=torch.int32, device=dev))
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_long_prompt_first_compression(dtype):
+    """Tables of 9..40 pages compressed to 8 (+1), some targets starting with fresh pages."""
+    from zipage_b200.synthetic import make_compress_workload
+    dev = torch.device("cuda:0")
+    w = make_compress_workload(B=4, L=1, Hkv=2, Hq=8, QCL=16, budget=8, pages_per_seq=[40, 9, 17, 12],
+                               dtype=dtype, device=dev, seed=5, with_score_cache=True, compressed_prob=0.5,
+                               fresh_target_prob=0.7, similar_keys=True)
+    cfg = dict(budget_blocks=8, query_cache_len=16, use_global_score=True, use_redudancy=True,
+               lightning_redudancy=True, enable_pooling=True)
+    (final_o, keep_o, ko, vo), dbg = _run_both(w, cfg, dtype)
+    keep = dbg["keep"].cpu()
+    assert (keep.flatten(3).sum(-1) == 8 * BS).all()
+    if dtype == torch.float32:
+        assert torch.equal(keep, keep_o)
+        assert torch.equal(w.kv_cache[0].cpu(), ko) and torch.equal(w.kv_cache[1].cpu(), vo)
+    else:
+        assert (keep ^ keep_o).float().mean() < 1e-2
+
+
+def test_group_of_eight_with_window_32_uses_the_portable_kernel():
+    """G*QCL = 256 window rows exceed the tensor-core kernel's 128: auto falls back, results agree."""
+    from zipage_b200.synthetic import make_compress_workload
+    dev = torch.device("cuda:0")
+    w = make_compress_workload(B=2, L=2, Hkv=1, Hq=8, QCL=32, budget=2, pages_per_seq=[3, 4],
+                               dtype=torch.bfloat16, device=dev, seed=8)
+    cfg = dict(budget_blocks=2, query_cache_len=32, use_redudancy=True, lightning_redudancy=False,
+               enable_pooling=True)
+    (final_o, keep_o, _, _), dbg = _run_both(w, cfg, torch.bfloat16)
+    fo, fg = final_o.float(), dbg["final"].float().cpu()
+    fin = torch.isfinite(fo)
+    assert torch.equal(fg[~fin], fo[~fin])
+    assert (fg[fin] - fo[fin]).abs().max() <= 2e-2 * fo[fin].abs().max()
+    assert (dbg["keep"].cpu() ^ keep_o).float().mean() < 1e-2
+    from zipage_b200 import kernel as K, _lib
+    with pytest.raises(_lib.ZipageError):
+        K.attention_score(w.kv_cache[0], w.query_cache, w.query_ids, w.block_tables, impl="tcgen05")
+
+
+def test_table_not_longer_than_budget_keeps_everything():
+    from zipage_b200 import kernel as K
+    dev = torch.device("cuda:0")
+    scores = torch.rand(1, 2, 2, 2 * BS, device=dev)
+    keep = K.topk_mask(scores, 4 * BS)
+    assert keep.all()
+    keep = K.topk_mask(scores, 2 * BS)
+    assert keep.all()
+
+
+def test_oversized_row_is_rejected_cleanly():
+    from zipage_b200 import kernel as K, _lib
+    dev = torch.device("cuda:0")
+    scores = torch.zeros(1, 1, 1, 300 * BS, device=dev)  # 76 800 fp32 scores > shared memory
+    with pytest.raises(_lib.ZipageError, match="shared memory"):
+        K.topk_mask(scores, 8 * BS)
