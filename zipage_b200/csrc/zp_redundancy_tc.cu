@@ -7,10 +7,12 @@
 // norms computed from the same shared-memory tile and rounded to T as key_norm does.
 //
 // Roles (576 threads, persistent blocks, one per SM): warp 0 = TMA producer and TMEM owner,
-// warp 1 = MMA issuer, warps 2-17 = epilogue (thread <-> TMEM lane <-> similarity row; the four
-// warps of a lane quadrant split the 256 columns of an item in groups of 64).  A work item is
-// (column page, row half h): 128 rows x 256 columns = 256 TMEM columns; the two halves alternate
-// between the two halves of TMEM, so the MMA of one item overlaps the epilogue of the previous one.
+// warp 1 = MMA issuer, warps 2-17 = two epilogue TEAMS of 8 warps.  Column pages alternate between
+// the teams; a team owns one half of TMEM (256 columns).  A work item is (column page, row half h):
+// 128 rows x 256 columns; thread <-> TMEM lane <-> similarity row, the two warps of a lane quadrant
+// split the 256 columns.  While one team normalises / merges / writes a page, the other is in the
+// middle of its items, so the phases of consecutive pages overlap and the tensor pipe is fed by
+// whichever team has a free accumulator.
 //   lightning: a job is a unit; rows and columns are the same page (A = B tile).
 //   exact:     a job is (unit, row page); the row page stays resident, every page streams by.
 // Blocks walk over the jobs with a fixed stride, so the pipeline never drains between jobs.
@@ -39,14 +41,18 @@ struct RtParams {
   int total_jobs;
 };
 
+struct __align__(16) RtTeam {        // per epilogue team
+  alignas(16) float rn[256];         // 1 / |k| of the team's current column page
+  float nmin[8];                     // smallest |k| of each 32-column chunk of that page
+  float s_sum[256];                  // combined row sums of the page (lightning)
+  float pb_sum[2][256], pb_val[2][256];  // per column group partials of rows 0..255
+  int pb_col[2][256];
+  unsigned long long s_sub[256];     // fixed-point sums of exempted entries (lightning)
+};
+
 struct __align__(16) RtShared {
-  uint64_t full[RT_NBUF], empty[RT_NBUF], tfull[2], tempty[2], afull, aempty, sync_bar;
-  alignas(16) float rn[2][256];     // 1 / |k| of the column page (double-buffered over pages)
-  float nmin[2][8];                 // smallest |k| of each 32-column chunk of that page
-  float s_sum[256];                 // combined row sums of a page (lightning)
-  float pb_sum[4][256], pb_val[4][256];  // per column group partials of rows 0..255
-  int pb_col[4][256];
-  unsigned long long s_sub[256];    // fixed-point sums of exempted entries (lightning)
+  uint64_t full[RT_NBUF], empty[RT_NBUF], tfull[2], tempty[2], afull, aempty, team_bar[2], all_bar;
+  RtTeam team[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -83,10 +89,13 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < RT_NBUF; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 2); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 16); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 8);
+      mbar_init(&sh.team_bar[i], 8);   // one arrival per warp of the team
+    }
     mbar_init(&sh.afull, 1);
     mbar_init(&sh.aempty, 1);
-    mbar_init(&sh.sync_bar, 16);  // one arrival per epilogue warp
+    mbar_init(&sh.all_bar, 16);
     sh.abort_flag = 0;
     fence_mbar_init();
   }
@@ -102,7 +111,7 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
   constexpr uint32_t IDESC = idesc_f16(UmmaFmt<T>::fmt, 128, 256);
 
   // job -> (unit, row page).  All roles walk the same job sequence; `t` counts column pages since
-  // kernel start (stage and TMEM-buffer parity), `nj` counts the jobs that had work.
+  // kernel start (stage ring position; page t belongs to team t & 1), `nj` counts jobs with work.
   struct Job {
     int unit, mp, h, b, l; const int32_t* table; bool valid;
     __device__ __forceinline__ Job(const RtParams& p, int job) {
@@ -145,48 +154,69 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
+    // Pages of a job are issued in pairs (one per team): both first halves, then both second
+    // halves, so that each team's accumulator is refilled while the other team's is being read.
     if (lane == 0) {
       int t = 0, nj = 0;
       bool ok = true;
+      auto issue = [&](int tt, int hh) -> bool {   // item (page tt, row half hh) into team tt & 1
+        const int team = tt & 1, s = tt % NS;
+        const int use = (tt >> 1) * 2 + hh;         // how often this team's accumulator was used before
+        if (!mbar_wait<true>(&sh.tempty[team], (use & 1) ^ 1, abortp, p.error_word, 203)) return false;
+        fence_after_sync();
+        const uint32_t b_addr = smem_u32(stage_ptr(s));
+        const uint32_t a_base = EXACT ? smem_u32(bufs) : b_addr;
+        umma_k128(tmem_base + team * 256, a_base + hh * 16384, RT_BLOCK_BYTES, b_addr, RT_BLOCK_BYTES, IDESC);
+        umma_commit(&sh.tfull[team]);
+        return true;
+      };
       for (int job = blockIdx.x; ok && job < p.total_jobs; job += gridDim.x) {
         const Job jb(p, job);
         if (!jb.valid) continue;
         if (EXACT && !mbar_wait<true>(&sh.afull, nj & 1, abortp, p.error_word, 201)) break;
-        for (int pg = 0; pg < p.NB; ++pg) {
-          if (jb.table[pg] == -1) continue;
-          const int s = t % NS, k = t / NS;
-          if (!mbar_wait<true>(&sh.full[s], k & 1, abortp, p.error_word, 202)) { ok = false; break; }
-          const uint32_t b_addr = smem_u32(stage_ptr(s));
-          const uint32_t a_base = EXACT ? smem_u32(bufs) : b_addr;
-          for (int hh = 0; hh < 2; ++hh) {
-            if (!mbar_wait<true>(&sh.tempty[hh], (t & 1) ^ 1, abortp, p.error_word, 203)) { ok = false; break; }
-            fence_after_sync();
-            umma_k128(tmem_base + hh * 256, a_base + hh * 16384, RT_BLOCK_BYTES, b_addr, RT_BLOCK_BYTES, IDESC);
-            umma_commit(&sh.tfull[hh]);
+        int nvalid = 0;
+        for (int pg = 0; pg < p.NB; ++pg) nvalid += jb.table[pg] != -1;
+        for (int i = 0; ok && i < nvalid; i += 2) {
+          const int npair = min(2, nvalid - i);
+          for (int j = 0; ok && j < npair; ++j) {
+            const int tt = t + i + j, s = tt % NS, k = tt / NS;
+            ok = mbar_wait<true>(&sh.full[s], k & 1, abortp, p.error_word, 202);
           }
-          if (!ok) break;
-          umma_commit(&sh.empty[s]);
-          ++t;
+          for (int hh = 0; ok && hh < 2; ++hh)
+            for (int j = 0; ok && j < npair; ++j) ok = issue(t + i + j, hh);
+          for (int j = 0; ok && j < npair; ++j) umma_commit(&sh.empty[(t + i + j) % NS]);
         }
+        t += nvalid;
         if (EXACT && ok) umma_commit(&sh.aempty);  // the resident row page is no longer read
         ++nj;
       }
     }
   } else {
-    // ---------------- epilogue ----------------
-    // thread (grp, r): rows r (half 0) and r + 128 (half 1) of every item, columns grp*64 .. +63
+    // ---------------- epilogue teams ----------------
+    // thread (team, grp, r): rows r (half 0) and r + 128 (half 1) of the team's items, columns
+    // grp*128 .. +127; during the norm / merge phases it owns row `myrow` of the page
+    const int ew = warp - 2;
+    const int team = ew >> 3;
     const int q = warp & 3;            // TMEM lane quadrant this warp may read
-    const int grp = (warp - 2) >> 2;   // column group 0..3
+    const int grp = (ew >> 2) & 1;     // column group 0..1
     const int r = q * 32 + lane;
-    const int myrow = (grp & 1) * 128 + r;   // row this thread normalises (groups 0,1) / writes
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + grp * 64;
+    const int myrow = grp * 128 + r;
+    RtTeam& tm = sh.team[team];
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + team * 256 + grp * 128;
     const float eps_t = round_to<T>(p.eps);
-    uint32_t ph = 0;                   // phase of sync_bar (all epilogue warps in lock step)
-    auto sync_epilogue = [&](int where) -> bool {
+    uint32_t ph_team = 0, ph_all = 0;
+    auto sync_team = [&](int where) -> bool {
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh.sync_bar);
-      const bool ok_ = mbar_wait(&sh.sync_bar, ph & 1, abortp, p.error_word, where);
-      ++ph;
+      if (lane == 0) mbar_arrive(&sh.team_bar[team]);
+      const bool ok_ = mbar_wait(&sh.team_bar[team], ph_team & 1, abortp, p.error_word, where);
+      ++ph_team;
+      return ok_;
+    };
+    auto sync_all = [&](int where) -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.all_bar);
+      const bool ok_ = mbar_wait(&sh.all_bar, ph_all & 1, abortp, p.error_word, where);
+      ++ph_all;
       return ok_;
     };
     int t = 0, nj = 0;
@@ -208,56 +238,57 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
       }
       for (int pg = 0; pg < p.NB; ++pg) {
         if (table[pg] == -1) {
-          if (!EXACT && grp < 2)  // padded page: logits -inf
+          if (!EXACT && team == 0)  // padded page: logits -inf
             reinterpret_cast<T*>(p.logits_out)[((int64_t)jb.unit * p.NB + pg) * 256 + myrow] = Elem<T>::from_f32(-INFINITY);
           continue;
         }
-        const int s = t % NS, k = t / NS;
+        const int tt = t++;
+        if ((tt & 1) != team) continue;   // the other team's page
+        const int s = tt % NS, k = tt / NS;
         if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 302)) { ok = false; break; }
-        float* rn = sh.rn[t & 1];
-        if (grp < 2) {   // a warp covers exactly one 32-column chunk of the page
+        {   // a warp covers exactly one 32-column chunk of the page
           const float nrm = fmaxf(round_to<T>(sqrtf(row_sumsq<T>(stage_ptr(s), myrow))), eps_t);
-          rn[myrow] = 1.f / nrm;
+          tm.rn[myrow] = 1.f / nrm;
           float mn = nrm;
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-          if (lane == 0) sh.nmin[t & 1][(grp & 1) * 4 + q] = mn;
-          if (!EXACT) sh.s_sub[myrow] = 0ull;
+          if (lane == 0) tm.nmin[grp * 4 + q] = mn;
+          if (!EXACT) tm.s_sub[myrow] = 0ull;
         }
-        if (!sync_epilogue(303)) { ok = false; break; }
-        if (warp == 2 && lane == 0) mbar_arrive(&sh.empty[s]);  // the epilogue is done reading the stage
+        if (!sync_team(303)) { ok = false; break; }
+        if ((ew & 7) == 0 && lane == 0) mbar_arrive(&sh.empty[s]);  // the team is done reading the stage
         if (!EXACT) {
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
-            rn_m[hh] = rn[r + 128 * hh]; thr_m[hh] = p.threshold / rn_m[hh];
+            rn_m[hh] = tm.rn[r + 128 * hh]; thr_m[hh] = p.threshold / rn_m[hh];
             rsum[hh] = 0.f; bcol[hh] = -1; bval[hh] = 0.f;
           }
         }
         const bool diag_page = EXACT ? (pg == jb.mp) : true;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          if (!mbar_wait(&sh.tfull[hh], t & 1, abortp, p.error_word, 304)) { ok = false; break; }
+          const int use = (tt >> 1) * 2 + hh;
+          if (!mbar_wait(&sh.tfull[team], use & 1, abortp, p.error_word, 304)) { ok = false; break; }
           fence_after_sync();
-          const uint32_t tbase = lane_base + hh * 256;
           float2 sa = make_float2(0.f, 0.f), sb = sa;
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
             uint32_t raw[32];
-            tmem_ld32_issue(tbase + c * 32, raw);
+            tmem_ld32_issue(lane_base + c * 32, raw);
             tmem_ld32_wait(raw);
-            if (c == 1) {  // every TMEM read of this item has landed in registers
+            if (c == 3) {  // every TMEM read of this item has landed in registers
               fence_before_sync();
               __syncwarp();
-              if (lane == 0) mbar_arrive(&sh.tempty[hh]);
+              if (lane == 0) mbar_arrive(&sh.tempty[team]);
             }
-            const int cg = grp * 2 + c;  // chunk index within the 256 columns
+            const int cg = grp * 4 + c;  // chunk index within the 256 columns
             if (diag_page && cg == hh * 4 + q) {  // warp-uniform: the chunk that holds this warp's diagonal
 #pragma unroll
               for (int j = 0; j < 32; ++j) raw[j] = (j == lane) ? 0u : raw[j];
             }
             // row sum: acc * (1/|k_n|) accumulated two columns at a time; threshold filter on the raw
             // accumulators: S > thr needs acc > thr * |k_m| * |k_n| >= thr * |k_m| * min|k_n|
-            const float4* rn4 = reinterpret_cast<const float4*>(rn + cg * 32);
+            const float4* rn4 = reinterpret_cast<const float4*>(tm.rn + cg * 32);
             float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -269,8 +300,8 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
               m0 = fmax3(m0, a0, a1);
               m1 = fmax3(m1, a2, a3);
             }
-            if (fmaxf(m0, m1) > thr_m[hh] * sh.nmin[t & 1][cg]) {  // rare: look at the normalised values
-              const float* rnc = rn + cg * 32;
+            if (fmaxf(m0, m1) > thr_m[hh] * tm.nmin[cg]) {  // rare: look at the normalised values
+              const float* rnc = tm.rn + cg * 32;
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
                 const float v = __uint_as_float(raw[j]) * rnc[j];
@@ -278,61 +309,57 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
               }
             }
           }
-          const float s0 = sa.x, s1 = sa.y, s2 = sb.x, s3 = sb.y;
-          rsum[hh] += (s0 + s1) + (s2 + s3);
+          rsum[hh] += (sa.x + sa.y) + (sb.x + sb.y);
         }
         if (!ok) break;
         if (!EXACT) {
-          // page done: merge the four column groups, subtract the exempted entries, write the logits
+          // page done: merge the two column groups, subtract the exempted entries, write the logits
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
-            sh.pb_sum[grp][r + 128 * hh] = rsum[hh]; sh.pb_col[grp][r + 128 * hh] = bcol[hh];
-            sh.pb_val[grp][r + 128 * hh] = bval[hh];
+            tm.pb_sum[grp][r + 128 * hh] = rsum[hh]; tm.pb_col[grp][r + 128 * hh] = bcol[hh];
+            tm.pb_val[grp][r + 128 * hh] = bval[hh];
           }
-          if (!sync_epilogue(305)) { ok = false; break; }
-          if (grp < 2) {
+          if (!sync_team(305)) { ok = false; break; }
+          {
             const int row = myrow;
-            float total = 0.f, bv = 0.f;
-            int bc = -1;
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {   // fixed order; higher column groups win
-              total += sh.pb_sum[g][row];
-              if (sh.pb_col[g][row] >= 0) { bc = sh.pb_col[g][row]; bv = sh.pb_val[g][row]; }
-            }
-            const float rnm = rn[row];
-            sh.s_sum[row] = total * rnm;
+            const float total = tm.pb_sum[0][row] + tm.pb_sum[1][row];
+            const int bc = tm.pb_col[1][row] >= 0 ? tm.pb_col[1][row] : tm.pb_col[0][row];  // upper columns win
+            const float bv = tm.pb_col[1][row] >= 0 ? tm.pb_val[1][row] : tm.pb_val[0][row];
+            const float rnm = tm.rn[row];
+            tm.s_sum[row] = total * rnm;
             if (bc >= 0) {
               const long long fx = __float2ll_rn(bv * rnm * 4294967296.f);
-              atomicAdd(&sh.s_sub[bc - pg * 256], (unsigned long long)fx);
+              atomicAdd(&tm.s_sub[bc - pg * 256], (unsigned long long)fx);
             }
           }
-          if (!sync_epilogue(306)) { ok = false; break; }
-          if (grp < 2) {
-            const float sub = (float)((double)(long long)sh.s_sub[myrow] * (1.0 / 4294967296.0));
-            reinterpret_cast<T*>(p.logits_out)[((int64_t)jb.unit * p.NB + pg) * 256 + myrow] =
-                Elem<T>::from_f32(sh.s_sum[myrow] - sub);
-          }
+          if (!sync_team(306)) { ok = false; break; }
+          const float sub = (float)((double)(long long)tm.s_sub[myrow] * (1.0 / 4294967296.0));
+          reinterpret_cast<T*>(p.logits_out)[((int64_t)jb.unit * p.NB + pg) * 256 + myrow] =
+              Elem<T>::from_f32(tm.s_sum[myrow] - sub);
         }
-        ++t;
       }
       if (!ok) break;
       if (EXACT) {
+        // job done: merge the two teams (even / odd column pages) and their column groups
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          sh.pb_sum[grp][r + 128 * hh] = rsum[hh]; sh.pb_col[grp][r + 128 * hh] = bcol[hh];
-          sh.pb_val[grp][r + 128 * hh] = bval[hh];
+          tm.pb_sum[grp][r + 128 * hh] = rsum[hh]; tm.pb_col[grp][r + 128 * hh] = bcol[hh];
+          tm.pb_val[grp][r + 128 * hh] = bval[hh];
         }
-        if (!sync_epilogue(307)) break;
-        if (grp < 2) {
+        if (!sync_all(307)) break;
+        if (team == 0) {
           const int row = myrow;
           const int64_t base = (int64_t)jb.unit * p.NB * 256;
           float total = 0.f, bv = 0.f;
           int bc = -1;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            total += sh.pb_sum[g][row];
-            if (sh.pb_col[g][row] >= 0) { bc = sh.pb_col[g][row]; bv = sh.pb_val[g][row]; }
-          }
+          for (int tmi = 0; tmi < 2; ++tmi)
+#pragma unroll
+            for (int g2 = 0; g2 < 2; ++g2) {   // fixed order; the largest column index wins
+              total += sh.team[tmi].pb_sum[g2][row];
+              const int c2 = sh.team[tmi].pb_col[g2][row];
+              if (c2 > bc) { bc = c2; bv = sh.team[tmi].pb_val[g2][row]; }
+            }
           const float rnm = grp == 0 ? rn_m[0] : rn_m[1];
           p.rowsum[base + jb.mp * 256 + row] = total * rnm;
           if (bc >= 0) {
@@ -340,7 +367,7 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
             atomicAdd(reinterpret_cast<unsigned long long*>(p.sub + base + bc), (unsigned long long)fx);
           }
         }
-        if (!sync_epilogue(308)) break;  // pb_* are free again
+        if (!sync_all(308)) break;  // pb_* are free again
       }
       ++nj;
     }
