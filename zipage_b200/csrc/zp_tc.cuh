@@ -152,6 +152,14 @@ __device__ __forceinline__ void ffma2(float2& d, float2 a, float2 b) {  // d += 
       : "+f"(d.x), "+f"(d.y)
       : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
 }
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {  // a * b, both lanes
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rc, ra, rb;\n\tmov.b64 {%0, %1}, rc;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));

@@ -238,7 +238,8 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const int grp = (warp - 2) >> 2;      // column group 0..3 (64 columns each)
     const int r = q * 32 + lane;          // TMEM lane: window row (sweeps 0/1) or key (sweep 2)
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + grp * 64;
-    const float LOG2E = 1.4426950408889634f;
+    const float2 log2e2 = make_float2(1.4426950408889634f, 1.4426950408889634f);
+    const float2 scale2 = make_float2(p.scale, p.scale);
     const int my_i = r / G;
     const bool use_max = p.reduce_mode != 0;
     uint32_t ph = 0;                      // phase of stats_bar (all 512 epilogue threads in lock step)
@@ -324,11 +325,13 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-              const V la = Pair<T>::pack(__uint_as_float(raw[j]) * p.scale, __uint_as_float(raw[j + 1]) * p.scale);
-              const V lb = Pair<T>::pack(__uint_as_float(raw[j + 2]) * p.scale, __uint_as_float(raw[j + 3]) * p.scale);
-              const float2 da = Pair<T>::unpack(__hsub2(la, m2)), db = Pair<T>::unpack(__hsub2(lb, m2));
-              z0 += ex2_approx(da.x * LOG2E); z1 += ex2_approx(da.y * LOG2E);
-              z2 += ex2_approx(db.x * LOG2E); z3 += ex2_approx(db.y * LOG2E);
+              const float2 xa = fmul2(make_float2(__uint_as_float(raw[j]), __uint_as_float(raw[j + 1])), scale2);
+              const float2 xb = fmul2(make_float2(__uint_as_float(raw[j + 2]), __uint_as_float(raw[j + 3])), scale2);
+              const V la = Pair<T>::pack(xa.x, xa.y), lb = Pair<T>::pack(xb.x, xb.y);
+              const float2 da = fmul2(Pair<T>::unpack(__hsub2(la, m2)), log2e2);
+              const float2 db = fmul2(Pair<T>::unpack(__hsub2(lb, m2)), log2e2);
+              z0 += ex2_approx(da.x); z1 += ex2_approx(da.y);
+              z2 += ex2_approx(db.x); z3 += ex2_approx(db.y);
             }
             row_z += (z0 + z1) + (z2 + z3);
           }
@@ -365,10 +368,12 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               const int jp = 4 * j4 + k;
-              const V lg = Pair<T>::pack(__uint_as_float(raw[2 * jp]) * p.scale,
-                                         __uint_as_float(raw[2 * jp + 1]) * p.scale);
-              const float2 d = Pair<T>::unpack(__hsub2(lg, *reinterpret_cast<const V*>(&cmv[k])));
-              pp[jp] = Pair<T>::pack(ex2_approx(d.x * LOG2E) * rzv[2 * k], ex2_approx(d.y * LOG2E) * rzv[2 * k + 1]);
+              const float2 x = fmul2(make_float2(__uint_as_float(raw[2 * jp]), __uint_as_float(raw[2 * jp + 1])), scale2);
+              const V lg = Pair<T>::pack(x.x, x.y);
+              const float2 d = fmul2(Pair<T>::unpack(__hsub2(lg, *reinterpret_cast<const V*>(&cmv[k]))), log2e2);
+              const float2 e = fmul2(make_float2(ex2_approx(d.x), ex2_approx(d.y)),
+                                     make_float2(rzv[2 * k], rzv[2 * k + 1]));
+              pp[jp] = Pair<T>::pack(e.x, e.y);
             }
           }
           if (jmask > col0) {  // some of this chunk's window rows cannot see this key (last page only)
