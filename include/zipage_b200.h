@@ -154,6 +154,40 @@ int zp_compact(void* k_cache, void* v_cache, void* score_cache, const uint8_t* k
                int NT, int Hkv, int D, int BS, int64_t kv_stride_layer, int64_t kv_stride_page,
                int64_t sc_stride_layer, int64_t sc_stride_page, int dtype, void* stream);
 
+/* Parameters of zp_compress_batch: the switches ModelRunner.compress reads
+ * (zipage/config.py:22-46, zipage/engine/model_runner.py:51-71). */
+typedef struct zp_compress_params {
+  int32_t budget_blocks;       /* pages kept per sequence; top_k = BS * budget_blocks          */
+  int32_t query_cache_len;
+  int32_t use_global_score;    /* merge with / persist to score_cache                          */
+  int32_t max_norm;            /* divide scores (and redundancy) by their row maximum           */
+  int32_t redundancy;          /* 0 none, 1 lightning, 2 exact                                  */
+  int32_t pooling_size;        /* 0 = off, else odd max-pool kernel (reference: 5)              */
+  int32_t continues_pooling;
+  int32_t sink_len;            /* 0 = off                                                       */
+  float decay_factor;
+  float redundancy_lambda;
+  float redundancy_one_minus_lambda;
+  float redundancy_temperature;
+  float redundancy_threshold;  /* reference default 0.5                                         */
+  float softmax_scale;         /* <= 0: head_dim^-0.5                                           */
+} zp_compress_params;
+
+/* Replaces one layer-chunk iteration of ModelRunner.compress, zipage/engine/model_runner.py:466-622,
+ * as ONE call: window scoring -> [global score] -> [redundancy] -> pooling/combine/masks/top-k ->
+ * in-place compaction of K, V (and the score cache) -> optional device-side table update
+ * (new_table [B, NT], context_len [B], next_slot [B]; pass NULL to skip).  Scratch comes from the
+ * caller: zp_compress_batch_workspace_bytes(L, B, NB, Hkv, BS, dtype, redundancy). */
+size_t zp_compress_batch_workspace_bytes(int L, int B, int NB, int Hkv, int BS, int dtype, int redundancy);
+int zp_compress_batch(void* k_cache, void* v_cache, const void* query_cache, void* score_cache,
+                      const int32_t* query_ids, const int32_t* block_table,
+                      const int32_t* target_table, const uint8_t* compressed, int32_t* new_table,
+                      int32_t* context_len, int32_t* next_slot, int L, int B, int NB, int NT, int Hq,
+                      int Hkv, int D, int QCL, int BS, int64_t kv_stride_layer, int64_t kv_stride_page,
+                      int64_t q_stride_layer, int64_t q_stride_seq, int64_t sc_stride_layer,
+                      int64_t sc_stride_page, const zp_compress_params* params, int dtype, int impl,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
 /* Device-side table update after a compaction (no reference kernel: the reference does this on
  * the host in zipage/engine/scheduler.py:150-156 and model_runner.py:633-675).  For each sequence:
  * new_table[b, :] = target_table[b, :]; context_len[b] = BS*(NT-1) + 1;

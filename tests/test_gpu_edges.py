@@ -90,3 +90,27 @@ def test_oversized_row_is_rejected_cleanly():
     scores = torch.zeros(1, 1, 1, 300 * BS, device=dev)  # 76 800 fp32 scores > shared memory
     with pytest.raises(_lib.ZipageError, match="shared memory"):
         K.topk_mask(scores, 8 * BS)
+
+
+@pytest.mark.parametrize("variant", ["lightning", "exact", "none"])
+def test_single_entry_point_equals_stage_by_stage(variant):
+    """zp_compress_batch (one C call) leaves the caches exactly as the stage-by-stage path does."""
+    from zipage_b200.compress import CompressConfig, compress_batch, compress_chunk
+    from zipage_b200.synthetic import make_compress_workload
+    dev = torch.device("cuda:0")
+    mk = lambda: make_compress_workload(B=3, L=2, Hkv=2, Hq=8, QCL=16, budget=2, pages_per_seq=[3, 5, 3],
+                                        dtype=torch.bfloat16, device=dev, seed=12, with_score_cache=True,
+                                        compressed_prob=0.5, fresh_target_prob=0.5, similar_keys=True)
+    cfg = CompressConfig(budget_blocks=2, query_cache_len=16, use_global_score=True, decay_factor=0.8,
+                         use_redudancy=variant != "none", lightning_redudancy=variant == "lightning",
+                         enable_pooling=True, use_attention_sink=True, sink_len=4)
+    a, b = mk(), mk()
+    compress_chunk(a.kv_cache[0], a.kv_cache[1], a.query_cache, a.score_cache, a.query_ids, a.block_tables,
+                   a.target_tables, a.compressed, cfg)
+    new_table, ctx, nxt = compress_batch(b.kv_cache[0], b.kv_cache[1], b.query_cache, b.score_cache,
+                                         b.query_ids, b.block_tables, b.target_tables, b.compressed, cfg,
+                                         update_tables=True)
+    torch.cuda.synchronize()
+    assert torch.equal(a.kv_cache, b.kv_cache) and torch.equal(a.score_cache, b.score_cache)
+    assert torch.equal(new_table, b.target_tables) and ctx.tolist() == [2 * BS + 1] * 3
+    assert nxt.tolist() == (b.target_tables[:, -1] * BS).tolist()

@@ -31,6 +31,17 @@ class SelectParams(C.Structure):
     ]
 
 
+class CompressParams(C.Structure):
+    _fields_ = [
+        ("budget_blocks", C.c_int32), ("query_cache_len", C.c_int32), ("use_global_score", C.c_int32),
+        ("max_norm", C.c_int32), ("redundancy", C.c_int32), ("pooling_size", C.c_int32),
+        ("continues_pooling", C.c_int32), ("sink_len", C.c_int32), ("decay_factor", C.c_float),
+        ("redundancy_lambda", C.c_float), ("redundancy_one_minus_lambda", C.c_float),
+        ("redundancy_temperature", C.c_float), ("redundancy_threshold", C.c_float),
+        ("softmax_scale", C.c_float),
+    ]
+
+
 _P, _I, _L, _F, _Z = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
 # name -> (restype, argtypes); mirrors include/zipage_b200.h one to one
@@ -49,6 +60,8 @@ SIGNATURES = {
     "zp_redundancy_softmax": (_I, [_P, _P] + [_I] * 5 + [_F, _I, _I, _P]),
     "zp_select": (_I, [_P, _P, _P, _P, _P, _P] + [_I] * 5 + [C.POINTER(SelectParams), _I, _P]),
     "zp_compact": (_I, [_P, _P, _P, _P, _P, _P] + [_I] * 7 + [_L] * 4 + [_I, _P]),
+    "zp_compress_batch_workspace_bytes": (_Z, [_I] * 7),
+    "zp_compress_batch": (_I, [_P] * 11 + [_I] * 9 + [_L] * 6 + [C.POINTER(CompressParams), _I, _I, _P, _Z, _P]),
     "zp_update_tables": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "zp_paged_decode_workspace_bytes": (_Z, [_I] * 4),
     "zp_paged_decode": (_I, [_P] * 6 + [_I] * 6 + [_L, _F, _I, _P, _Z, _P]),

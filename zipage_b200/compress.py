@@ -81,6 +81,55 @@ def compress_chunk(k_cache, v_cache, query_cache, score_cache, query_ids, block_
     return None
 
 
+def compress_batch(k_cache, v_cache, query_cache, score_cache, query_ids, block_tables,
+                   target_block_tables, compressed, cfg: CompressConfig, impl="auto", workspace=None,
+                   update_tables=False):
+    """The same op as `compress_chunk` through the single C entry point `zp_compress_batch`
+    (one host call, scratch from one workspace tensor).  Returns (new_table, context_len, next_slot)
+    device tensors when update_tables is set, else None."""
+    import ctypes
+
+    from . import _lib as L
+    Ln, _, BS, Hkv, D = k_cache.shape
+    _, _, QCL, Hq, _ = query_cache.shape
+    B, NB = block_tables.shape
+    NT = target_block_tables.shape[1]
+    lib = L.load()
+    pr = L.CompressParams()
+    pr.budget_blocks, pr.query_cache_len = cfg.budget_blocks, cfg.query_cache_len
+    pr.use_global_score, pr.max_norm = int(cfg.use_global_score), int(cfg.max_norm)
+    pr.redundancy = 0 if not cfg.use_redudancy else (1 if cfg.lightning_redudancy else 2)
+    pr.pooling_size = cfg.pooling_size if cfg.enable_pooling else 0
+    pr.continues_pooling = int(cfg.continues_pooling)
+    pr.sink_len = cfg.sink_len if cfg.use_attention_sink else 0
+    pr.decay_factor = cfg.decay_factor
+    pr.redundancy_lambda = cfg.redudancy_lambda
+    pr.redundancy_one_minus_lambda = 1 - cfg.redudancy_lambda
+    pr.redundancy_temperature = cfg.redudancy_temperature
+    pr.redundancy_threshold = cfg.redudancy_threshold
+    pr.softmax_scale = 0.0
+    code = L.dtype_code(k_cache)
+    need = lib.zp_compress_batch_workspace_bytes(Ln, B, NB, Hkv, BS, code, pr.redundancy)
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=k_cache.device)
+    outs = (None, None, None)
+    if update_tables:
+        dev = k_cache.device
+        outs = (torch.empty((B, NT), dtype=torch.int32, device=dev),
+                torch.empty(B, dtype=torch.int32, device=dev), torch.empty(B, dtype=torch.int32, device=dev))
+    comp = compressed.to(torch.uint8) if compressed.dtype != torch.uint8 else compressed
+    sc = score_cache if cfg.use_global_score else None
+    L.check(lib.zp_compress_batch(
+        L.ptr(k_cache), L.ptr(v_cache), L.ptr(query_cache), L.ptr(sc), L.ptr(query_ids),
+        L.ptr(block_tables), L.ptr(target_block_tables), L.ptr(comp), L.ptr(outs[0]), L.ptr(outs[1]),
+        L.ptr(outs[2]), Ln, B, NB, NT, Hq, Hkv, D, QCL, BS, k_cache.stride(0), k_cache.stride(1),
+        query_cache.stride(0), query_cache.stride(1), sc.stride(0) if sc is not None else 0,
+        sc.stride(1) if sc is not None else 0, ctypes.byref(pr), code, L.IMPL[impl], L.ptr(workspace),
+        workspace.numel() * workspace.element_size(), L.stream_ptr()), "compress_batch")
+    K._count(4 + int(cfg.use_global_score) + int(update_tables))
+    return outs if update_tables else None
+
+
 class _Null:
     def __enter__(self):
         return self
