@@ -81,6 +81,18 @@ int zp_window_score(const void* k_cache, const void* query_cache, const int32_t*
                     int64_t k_stride_page, int64_t q_stride_layer, int64_t q_stride_seq,
                     float softmax_scale, int reduce_mode, int dtype, int impl, void* stream);
 
+/* Same as zp_window_score with scratch.  The tcgen05 kernel handles 128 window rows (G*QCL) per
+ * pass; larger windows (e.g. 8 query heads per KV head with a 32-token window) take several passes
+ * whose per-key sums meet in this workspace (zp_window_score_workspace_bytes + 256; 0 bytes when
+ * one pass suffices).  Without a sufficient workspace such shapes run on the portable SIMT kernel. */
+size_t zp_window_score_workspace_bytes(int L, int B, int NB, int Hq, int Hkv, int QCL);
+int zp_window_score_ws(const void* k_cache, const void* query_cache, const int32_t* seq_idx,
+                       const int32_t* block_table, void* scores_out, void* logits_out, int L, int B,
+                       int NB, int Hq, int Hkv, int D, int QCL, int BS, int64_t k_stride_layer,
+                       int64_t k_stride_page, int64_t q_stride_layer, int64_t q_stride_seq,
+                       float softmax_scale, int reduce_mode, int dtype, int impl, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
 /* Replaces global_score, zipage/kernel/global_score.py:8-120 (activate 0 = max, 1 = sum), plus the
  * optional max-normalisation that precedes it, zipage/engine/model_runner.py:482-487
  * (max_norm != 0: scores are first divided by their per-(layer, seq, head) maximum).

@@ -52,6 +52,8 @@ SIGNATURES = {
     "zp_store_kv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _L, _L, _I, _P]),
     "zp_store_query": (_I, [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P]),
     "zp_window_score": (_I, [_P, _P, _P, _P, _P, _P] + [_I] * 8 + [_L] * 4 + [_F, _I, _I, _I, _P]),
+    "zp_window_score_workspace_bytes": (_Z, [_I] * 6),
+    "zp_window_score_ws": (_I, [_P, _P, _P, _P, _P, _P] + [_I] * 8 + [_L] * 4 + [_F, _I, _I, _I, _P, _Z, _P]),
     "zp_global_score": (_I, [_P, _P, _P, _P] + [_I] * 5 + [_L, _L, _F, _I, _I, _I, _P]),
     "zp_key_norm": (_I, [_P, _P, _P] + [_I] * 6 + [_L, _L, _F, _I, _P]),
     "zp_redundancy_lightning": (_I, [_P, _P, _P] + [_I] * 6 + [_L, _L, _F, _I, _I, _P]),

@@ -10,7 +10,9 @@ extern "C" size_t zp_compress_batch_workspace_bytes(int L, int B, int NB, int Hk
                                                     int redundancy) {
   const size_t n = (size_t)L * B * Hkv * NB * BS;
   const size_t es = zp::dtype_size(dtype);
+  // scores + keep flags + room for up to two passes of window-score partial sums (fp32)
   size_t total = align256(n * es) /* scores */ + align256(n) /* keep flags */ + 256;
+  if (dtype != ZP_DTYPE_F32) total += align256(2 * n * sizeof(float) + 256);
   if (redundancy) total += align256(n * es);  /* redundancy logits */
   if (redundancy == 2) total += align256(zp_redundancy_exact_workspace_bytes(L, B, NB, Hkv, BS));
   return total;
@@ -42,11 +44,18 @@ extern "C" int zp_compress_batch(void* k_cache, void* v_cache, const void* query
   void* red = nullptr;
   if (pr->redundancy) { red = w; w += align256(n * es); }
   void* red_ws = w;
+  void* win_ws = nullptr;
+  size_t win_ws_bytes = 0;
+  if (dtype != ZP_DTYPE_F32) {  // placed last: the exact-redundancy scratch (if any) comes first
+    char* e = reinterpret_cast<char*>(red_ws);
+    if (pr->redundancy == 2) e += align256(zp_redundancy_exact_workspace_bytes(L, B, NB, Hkv, BS));
+    win_ws = e; win_ws_bytes = 2 * n * sizeof(float) + 256;
+  }
   const float scale = pr->softmax_scale > 0.f ? pr->softmax_scale : 1.0f / sqrtf((float)D);
 
-  int rc = zp_window_score(k_cache, query_cache, query_ids, block_table, scores, nullptr, L, B, NB, Hq, Hkv,
-                           D, QCL, BS, kv_stride_layer, kv_stride_page, q_stride_layer, q_stride_seq, scale,
-                           0, dtype, impl, stream);
+  int rc = zp_window_score_ws(k_cache, query_cache, query_ids, block_table, scores, nullptr, L, B, NB, Hq,
+                              Hkv, D, QCL, BS, kv_stride_layer, kv_stride_page, q_stride_layer, q_stride_seq,
+                              scale, 0, dtype, impl, win_ws, win_ws_bytes, stream);
   if (rc) return rc;
   if (pr->use_global_score) {
     rc = zp_global_score(scores, score_cache, block_table, compressed, L, B, NB, Hkv, BS, sc_stride_layer,

@@ -296,9 +296,15 @@ bool window_score_tc_supported(int dtype, int D, int BS, int Hq, int Hkv, int QC
 int window_score_tc(const void* k_cache, const void* q_cache, const int32_t* seq_idx,
                     const int32_t* block_table, void* scores_out, int L, int B, int NB, int Hq, int Hkv,
                     int QCL, int64_t k_stride_layer, int64_t k_stride_page, int64_t q_stride_layer,
-                    int64_t q_stride_seq, float scale, int reduce_mode, int dtype, cudaStream_t st);
+                    int64_t q_stride_seq, float scale, int reduce_mode, int dtype, float* partial,
+                    cudaStream_t st);
+size_t window_score_tc_workspace_bytes(int L, int B, int NB, int Hq, int Hkv, int QCL);
 
 }  // namespace zp
+
+extern "C" size_t zp_window_score_workspace_bytes(int L, int B, int NB, int Hq, int Hkv, int QCL) {
+  return Hkv > 0 && Hq % Hkv == 0 ? zp::window_score_tc_workspace_bytes(L, B, NB, Hq, Hkv, QCL) : 0;
+}
 
 extern "C" int zp_window_score(const void* k_cache, const void* query_cache, const int32_t* seq_idx,
                                const int32_t* block_table, void* scores_out, void* logits_out,
@@ -306,6 +312,18 @@ extern "C" int zp_window_score(const void* k_cache, const void* query_cache, con
                                int64_t k_stride_layer, int64_t k_stride_page,
                                int64_t q_stride_layer, int64_t q_stride_seq, float softmax_scale,
                                int reduce_mode, int dtype, int impl, void* stream) {
+  return zp_window_score_ws(k_cache, query_cache, seq_idx, block_table, scores_out, logits_out, L, B, NB,
+                            Hq, Hkv, D, QCL, BS, k_stride_layer, k_stride_page, q_stride_layer,
+                            q_stride_seq, softmax_scale, reduce_mode, dtype, impl, nullptr, 0, stream);
+}
+
+extern "C" int zp_window_score_ws(const void* k_cache, const void* query_cache, const int32_t* seq_idx,
+                                  const int32_t* block_table, void* scores_out, void* logits_out,
+                                  int L, int B, int NB, int Hq, int Hkv, int D, int QCL, int BS,
+                                  int64_t k_stride_layer, int64_t k_stride_page,
+                                  int64_t q_stride_layer, int64_t q_stride_seq, float softmax_scale,
+                                  int reduce_mode, int dtype, int impl, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
   if (L * B == 0) return ZP_OK;
   ZP_REQUIRE(k_cache && query_cache && seq_idx && block_table && scores_out,
              "zp_window_score: null pointer");
@@ -324,18 +342,23 @@ extern "C" int zp_window_score(const void* k_cache, const void* query_cache, con
   p.q_stride_layer = q_stride_layer; p.q_stride_seq = q_stride_seq;
   p.scale = softmax_scale; p.reduce_mode = reduce_mode;
   ZP_REQUIRE(softmax_scale > 0.f, "zp_window_score: softmax_scale must be positive");
-  const bool can_tc = zp::window_score_tc_supported(dtype, D, BS, Hq, Hkv, QCL, logits_out != nullptr) &&
+  const size_t ws_need = zp::window_score_tc_workspace_bytes(L, B, NB, Hq, Hkv, QCL);
+  const bool ws_ok = ws_need == 0 || (workspace && workspace_bytes >= ws_need + 256);
+  const bool can_tc = ws_ok && zp::window_score_tc_supported(dtype, D, BS, Hq, Hkv, QCL, logits_out != nullptr) &&
                       ((uintptr_t)query_cache % 16 == 0) &&
                       (q_stride_layer * zp::dtype_size(dtype)) % 16 == 0 &&
                       (q_stride_seq * zp::dtype_size(dtype)) % 16 == 0;
   if (impl == ZP_IMPL_TCGEN05 && !can_tc) {
     zp::set_error("zp_window_score: the tcgen05 kernel needs a 16-bit cache, head_dim 128, page size "
-                  "256, a power-of-two group size with G*QCL <= 128, and no logits output");
+                  "256, a power-of-two group size, no logits output and, for more than 128 window rows, "
+                  "a workspace of zp_window_score_workspace_bytes()");
     return ZP_ERR_UNSUPPORTED;
   }
   if (impl != ZP_IMPL_SIMT && can_tc)
     return zp::window_score_tc(k_cache, query_cache, seq_idx, block_table, scores_out, L, B, NB, Hq,
                                Hkv, QCL, k_stride_layer, k_stride_page, q_stride_layer, q_stride_seq,
-                               softmax_scale, reduce_mode, dtype, (cudaStream_t)stream);
+                               softmax_scale, reduce_mode, dtype,
+                               ws_need ? reinterpret_cast<float*>(((uintptr_t)workspace + 255) & ~(uintptr_t)255) : nullptr,
+                               (cudaStream_t)stream);
   return zp::window_score_simt(p, D, dtype, (cudaStream_t)stream);
 }

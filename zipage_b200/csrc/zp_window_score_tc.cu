@@ -40,6 +40,11 @@ struct WtParams {
   float scale;
   int reduce_mode;
   int total_units;
+  // Window rows are processed in passes of at most 128 rows (G * qcl_pass): this launch covers
+  // window indices [i0, i0 + qcl_pass).  With more than one pass the per-key sums go to `partial`
+  // ([pass][unit][NB*256] fp32) and a small kernel adds the passes and rounds.
+  int i0, qcl_pass, pass;
+  float* partial;
 };
 
 struct __align__(16) WtShared {
@@ -105,7 +110,7 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   WtShared& sh = *reinterpret_cast<WtShared*>(qbufs + 4 * WT_QBLOCK_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int R = G * p.QCL;
+  const int R = G * p.qcl_pass;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < WT_NS; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
@@ -182,8 +187,8 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         mbar_arrive_expect_tx(&sh.qfull[qb], (uint32_t)(2 * R * 128));
         const int qid = p.seq_idx[un.b];
         unsigned char* qbuf = qbufs + qb * 2 * WT_QBLOCK_BYTES;
-        tma_load_5d(qbuf, &tmQ, &sh.qfull[qb], 0, un.h * G, 0, qid, un.l);
-        tma_load_5d(qbuf + WT_QBLOCK_BYTES, &tmQ, &sh.qfull[qb], 64, un.h * G, 0, qid, un.l);
+        tma_load_5d(qbuf, &tmQ, &sh.qfull[qb], 0, un.h * G, p.i0, qid, un.l);
+        tma_load_5d(qbuf + WT_QBLOCK_BYTES, &tmQ, &sh.qfull[qb], 64, un.h * G, p.i0, qid, un.l);
         TileCursor cur{un.table, p.NB, un.nvalid, 0, 0, 0};
         cur.start();
         for (int tt = 0; tt < un.ntiles; ++tt, ++gt) {
@@ -265,7 +270,10 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     T* out = reinterpret_cast<T*>(p.scores_out) + (int64_t)unit * p.NB * 256;
     if (grp < 2)
       for (int pg = 0; pg < p.NB; ++pg)   // padded pages score exactly 0
-        if (table[pg] == -1) out[pg * 256 + grp * 128 + r] = Elem<T>::from_f32(0.f);
+        if (table[pg] == -1) {
+          if (p.partial) p.partial[((int64_t)p.pass * p.total_units + unit) * p.NB * 256 + pg * 256 + grp * 128 + r] = 0.f;
+          else out[pg * 256 + grp * 128 + r] = Elem<T>::from_f32(0.f);
+        }
     TileCursor cur{table, p.NB, nvalid, 0, 0, 0};
     if (ntiles > 0) cur.start();
     for (int tt = 0; tt < ntiles; ++tt, ++gt) {
@@ -297,7 +305,7 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       if (sweep < 2) {
         // columns = key slots grp*64 ..; row r sees slot <= smax inside the last page
         const uint32_t tbase = lane_base + buf * 256;
-        const int smax = last ? 256 - p.QCL + my_i : 256;
+        const int smax = last ? 256 - p.QCL + p.i0 + my_i : 256;
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
           uint32_t raw[32];
@@ -339,7 +347,7 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       } else {
         // rows of D = keys; columns = window rows j = i*G + g; key `slot` is hidden from columns < jmask
         const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * 256 + hh * 128 + cbase;
-        const int jmask = last ? max(0, slot - (256 - p.QCL)) * G : 0;
+        const int jmask = last ? max(0, slot - (256 - p.QCL) - p.i0) * G : 0;
         float acc2 = use_max ? -INFINITY : 0.f;
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
@@ -396,7 +404,10 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         if ((grp & 1) == 0) {
           const float a = accbuf[slot];
           accbuf[slot] = 0.f;
-          out[pg * 256 + slot] = Elem<T>::from_f32(use_max ? a : a / (float)p.QCL);
+          if (p.partial)
+            p.partial[((int64_t)p.pass * p.total_units + unit) * p.NB * 256 + pg * 256 + slot] = a;
+          else
+            out[pg * 256 + slot] = Elem<T>::from_f32(use_max ? a : a / (float)p.QCL);
         }
       }
     }
@@ -430,7 +441,7 @@ static int launch_window_tc(const void* k_cache, const void* q_cache, const WtPa
     const uint64_t dims[5] = {128, (uint64_t)p.Hq, (uint64_t)p.QCL, seqs, (uint64_t)p.L};
     const uint64_t strides[4] = {128, (uint64_t)p.Hq * 128, (uint64_t)q_stride_seq,
                                  (uint64_t)(p.L > 1 ? q_stride_layer : q_stride_seq)};
-    const uint32_t box[5] = {64, (uint32_t)G, (uint32_t)p.QCL, 1, 1};
+    const uint32_t box[5] = {64, (uint32_t)G, (uint32_t)p.qcl_pass, 1, 1};
     int rc = make_tensor_map_5d(&tmQ, UmmaFmt<T>::tm, q_cache, dims, strides, box, sizeof(T));
     if (rc) return rc;
   }
@@ -454,31 +465,74 @@ static int launch_window_tc(const void* k_cache, const void* q_cache, const WtPa
   return check_launch("zp_window_score(tcgen05)");
 }
 
+// adds the passes' per-key sums (or takes their max) and rounds: out = T(sum / QCL)
+template <typename T>
+__global__ void window_score_combine_kernel(const float* __restrict__ partial, T* __restrict__ out,
+                                            int64_t n, int npass, float qcl, int use_max) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float a = partial[i];
+  for (int ps = 1; ps < npass; ++ps) a = use_max ? fmaxf(a, partial[ps * n + i]) : a + partial[ps * n + i];
+  out[i] = Elem<T>::from_f32(use_max ? a : a / qcl);
+}
+
+// number of passes over the window rows (0 = shapes not covered)
+int window_score_tc_passes(int Hq, int Hkv, int QCL) {
+  const int G = Hq / Hkv;
+  if (G < 1 || G > 32 || (G & (G - 1))) return 0;
+  for (int np = 1; np <= 8; np *= 2) {
+    if (QCL % np) return 0;
+    const int R = G * (QCL / np);
+    if (R <= 128) return (R % 8 == 0) ? np : 0;
+  }
+  return 0;
+}
+size_t window_score_tc_workspace_bytes(int L, int B, int NB, int Hq, int Hkv, int QCL) {
+  const int np = window_score_tc_passes(Hq, Hkv, QCL);
+  return np > 1 ? (size_t)np * L * B * Hkv * NB * 256 * sizeof(float) : 0;
+}
+
 // true when the tensor-core kernel covers these shapes
 bool window_score_tc_supported(int dtype, int D, int BS, int Hq, int Hkv, int QCL, bool want_logits) {
   if (want_logits || !(dtype == ZP_DTYPE_BF16 || dtype == ZP_DTYPE_F16) || D != 128 || BS != 256) return false;
-  const int G = Hq / Hkv;
-  if (G < 1 || G > 32 || (G & (G - 1))) return false;
-  const int R = G * QCL;
-  return R <= 128 && R % 8 == 0 && QCL <= 256;
+  return QCL <= 256 && window_score_tc_passes(Hq, Hkv, QCL) > 0;
 }
 
 int window_score_tc(const void* k_cache, const void* q_cache, const int32_t* seq_idx,
                     const int32_t* block_table, void* scores_out, int L, int B, int NB, int Hq, int Hkv,
                     int QCL, int64_t k_stride_layer, int64_t k_stride_page, int64_t q_stride_layer,
-                    int64_t q_stride_seq, float scale, int reduce_mode, int dtype, cudaStream_t st) {
+                    int64_t q_stride_seq, float scale, int reduce_mode, int dtype, float* partial,
+                    cudaStream_t st) {
+  const int npass = window_score_tc_passes(Hq, Hkv, QCL);
+  if (npass > 1 && !partial) {
+    set_error("zp_window_score(tcgen05): %d window rows need %d passes and a workspace", (Hq / Hkv) * QCL, npass);
+    return ZP_ERR_WORKSPACE;
+  }
   WtParams p;
+  p.qcl_pass = QCL / npass; p.partial = npass > 1 ? partial : nullptr;
   p.seq_idx = seq_idx; p.block_table = block_table; p.scores_out = scores_out;
   p.error_word = device_error_word();
   p.L = L; p.B = B; p.NB = NB; p.Hq = Hq; p.Hkv = Hkv; p.QCL = QCL; p.scale = scale;
   p.reduce_mode = reduce_mode;
   p.total_units = L * B * Hkv;
   if (!p.error_word) { set_error("zp_window_score(tcgen05): no device error word"); return ZP_ERR_CUDA; }
-  if (dtype == ZP_DTYPE_BF16)
-    return launch_window_tc<__nv_bfloat16>(k_cache, q_cache, p, k_stride_layer, k_stride_page,
-                                           q_stride_layer, q_stride_seq, st);
-  return launch_window_tc<__half>(k_cache, q_cache, p, k_stride_layer, k_stride_page, q_stride_layer,
-                                  q_stride_seq, st);
+  for (int ps = 0; ps < npass; ++ps) {
+    p.pass = ps; p.i0 = ps * p.qcl_pass;
+    const int rc = dtype == ZP_DTYPE_BF16
+        ? launch_window_tc<__nv_bfloat16>(k_cache, q_cache, p, k_stride_layer, k_stride_page, q_stride_layer, q_stride_seq, st)
+        : launch_window_tc<__half>(k_cache, q_cache, p, k_stride_layer, k_stride_page, q_stride_layer, q_stride_seq, st);
+    if (rc) return rc;
+  }
+  if (npass > 1) {
+    const int64_t n = (int64_t)L * B * Hkv * NB * 256;
+    const int blocks = (int)((n + 255) / 256);
+    if (dtype == ZP_DTYPE_BF16)
+      window_score_combine_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(partial, (__nv_bfloat16*)scores_out, n, npass, (float)QCL, reduce_mode);
+    else
+      window_score_combine_kernel<__half><<<blocks, 256, 0, st>>>(partial, (__half*)scores_out, n, npass, (float)QCL, reduce_mode);
+    return check_launch("zp_window_score(tcgen05) combine");
+  }
+  return ZP_OK;
 }
 
 }  // namespace zp

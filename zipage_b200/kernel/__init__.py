@@ -88,12 +88,17 @@ def attention_score(k_cache, query_cache, seq_idx, block_table, softmax_scale=No
     logits = None
     if return_logits:
         logits = torch.empty((Ln, B, Hq, QCL, NB, BS), dtype=k_cache.dtype, device=k_cache.device)
-    L.check(L.load().zp_window_score(
+    lib = L.load()
+    need = lib.zp_window_score_workspace_bytes(Ln, B, NB, Hq, Hkv, QCL)
+    ws = None
+    if need and impl != "simt" and k_cache.dtype != torch.float32 and not return_logits:
+        ws = torch.empty(need + 256, dtype=torch.uint8, device=k_cache.device)
+    L.check(lib.zp_window_score_ws(
         L.ptr(k_cache), L.ptr(query_cache), L.ptr(_i32(seq_idx)), L.ptr(_i32(block_table)),
         L.ptr(scores), L.ptr(logits), Ln, B, NB, Hq, Hkv, D, QCL, BS, k_cache.stride(0),
         k_cache.stride(1), query_cache.stride(0), query_cache.stride(1), float(softmax_scale),
-        0 if reduced == "mean" else 1, L.dtype_code(k_cache), L.IMPL[impl], L.stream_ptr()),
-        "attention_score")
+        0 if reduced == "mean" else 1, L.dtype_code(k_cache), L.IMPL[impl], L.ptr(ws),
+        0 if ws is None else ws.numel(), L.stream_ptr()), "attention_score")
     _count()
     if return_logits:
         return scores, logits
