@@ -168,3 +168,56 @@ def test_varlen_prefill_long_ragged(dtype):
     out = varlen_prefill_attention(q.to(dev), k.to(dev), v.to(dev), max(lens), cu.to(dev), max(lens),
                                    cu.to(dev)).cpu()
     assert (out.float() - ref.float()).abs().max() <= 2e-2 * ref.float().abs().max()
+
+
+def test_async_compress_overlaps_decode_on_another_stream():
+    """The overlap contract of async_step: compression of some sequences runs on the compress
+    stream from a worker thread while the main thread decodes OTHER sequences on its own stream.
+    Both results must equal the sequential ones (the library keeps no global state)."""
+    import threading
+    from zipage_b200.compress import CompressConfig
+    from zipage_b200.engine.compressor import Compressor
+    from zipage_b200.layers.attention import paged_decode_attention
+    from zipage_b200.synthetic import make_compress_workload
+    dev = torch.device("cuda:0")
+    Hkv, Hq, budget = 2, 8, 2
+    cfg = CompressConfig(budget_blocks=budget, query_cache_len=16, use_redudancy=True,
+                         lightning_redudancy=True, enable_pooling=True)
+
+    def make():
+        return make_compress_workload(B=6, L=4, Hkv=Hkv, Hq=Hq, QCL=16, budget=budget, pages_per_seq=3,
+                                      dtype=torch.bfloat16, device=dev, seed=3, spare_pages=0)
+    w_seq, w_par = make(), make()
+    tables = w_seq.tables_plain.cpu().tolist()
+    # sequences 0-2 are compressed, sequences 3-5 are decoded meanwhile (disjoint pages)
+    comp_tables, comp_targets = tables[:3], w_seq.target_tables.cpu().tolist()[:3]
+    qids, flags = w_seq.query_ids.cpu().tolist()[:3], [True] * 3
+    dec_table = w_seq.tables_plain[3:].contiguous()
+    lens = torch.tensor([3 * BS, 2 * BS + 5, 700], dtype=torch.int32, device=dev)
+    q = torch.randn(3, 1, Hq, 128, device=dev, dtype=torch.bfloat16)
+
+    c1 = Compressor(w_seq.kv_cache, w_seq.query_cache, None, cfg, layer_stride=2)
+    c1.compress_tables(comp_tables, comp_targets, qids, flags)
+    ref = [paged_decode_attention(q, w_seq.kv_cache[0, l], w_seq.kv_cache[1, l], lens, dec_table) for l in range(4)]
+    torch.cuda.synchronize()
+
+    c2 = Compressor(w_par.kv_cache, w_par.query_cache, None, cfg, layer_stride=2)
+    err = []
+
+    def worker():
+        try:
+            c2.compress_tables(comp_tables, comp_targets, qids, flags)
+        except Exception as e:  # noqa: BLE001
+            err.append(e)
+    th = threading.Thread(target=worker)
+    run_stream = torch.cuda.Stream()
+    th.start()
+    with torch.cuda.stream(run_stream):
+        got = [paged_decode_attention(q, w_par.kv_cache[0, l], w_par.kv_cache[1, l], lens, dec_table)
+               for l in range(4) for _ in range(3)][::3]
+    th.join()
+    torch.cuda.synchronize()
+    assert not err, err
+    assert torch.equal(w_par.kv_cache, w_seq.kv_cache)
+    for a, b in zip(got, ref):
+        assert torch.equal(a, b)

@@ -306,3 +306,30 @@ def test_window_score_tcgen05_matches_simt_and_oracle(dtype, Hq, Hkv, QCL, reduc
     assert (a - o).abs().max() <= 2e-2 * scale
     # the bulk agrees to the last bit of T; only isolated roundings differ
     assert (a != o).float().mean() < 0.02
+
+
+@pytest.mark.parametrize("variant", ["exact", "lightning"])
+def test_config1_shapes_fp32_bit_exact_against_oracle(variant):
+    """The single-layer CPU config (4 ragged sequences of 9, 9, 10, 10 full pages, 32 query / 8 KV
+    heads, window 32, pool 7, lambda 0.5, budget 8 pages) in fp32: identical kept sets and
+    identical compacted caches."""
+    from oracle import zipage_oracle as O
+    from zipage_b200.compress import CompressConfig, compress_chunk
+    from zipage_b200.synthetic import make_compress_workload
+    dev = _gpu()
+    kw = dict(budget_blocks=8, query_cache_len=32, use_redudancy=True,
+              lightning_redudancy=variant == "lightning", redudancy_lambda=0.5, redudancy_temperature=0.4,
+              enable_pooling=True, continues_pooling=True, pooling_size=7)
+    w = make_compress_workload(B=4, L=1, Hkv=8, Hq=32, QCL=32, budget=8, pages_per_seq=[9, 9, 10, 10],
+                               dtype=torch.float32, device="cpu", seed=0, compressed_prob=0.0)
+    ko, vo = w.kv_cache[0].clone(), w.kv_cache[1].clone()
+    _, keep_o = O.compress(ko, vo, w.query_cache, None, w.query_ids, w.block_tables, w.target_tables,
+                           w.compressed, O.CompressConfig(**kw))
+    kg = w.kv_cache.to(dev)
+    dbg = compress_chunk(kg[0], kg[1], w.query_cache.to(dev), None, w.query_ids.to(dev),
+                         w.block_tables.to(dev), w.target_tables.to(dev), w.compressed.to(dev),
+                         CompressConfig(**kw), return_debug=True)
+    torch.cuda.synchronize()
+    assert torch.equal(dbg["keep"].cpu(), keep_o)
+    assert torch.equal(kg[0].cpu(), ko) and torch.equal(kg[1].cpu(), vo)
+    assert (keep_o.flatten(3).sum(-1) == 8 * BS).all()
