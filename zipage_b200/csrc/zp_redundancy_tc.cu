@@ -183,8 +183,11 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
             ok = mbar_wait<true>(&sh.full[s], k & 1, abortp, p.error_word, 202);
           }
           for (int hh = 0; ok && hh < 2; ++hh)
-            for (int j = 0; ok && j < npair; ++j) ok = issue(t + i + j, hh);
-          for (int j = 0; ok && j < npair; ++j) umma_commit(&sh.empty[(t + i + j) % NS]);
+            for (int j = 0; ok && j < npair; ++j) {
+              ok = issue(t + i + j, hh);
+              // a stage is free as soon as the MMAs of its second half are done
+              if (ok && hh == 1) umma_commit(&sh.empty[(t + i + j) % NS]);
+            }
         }
         t += nvalid;
         if (EXACT && ok) umma_commit(&sh.aempty);  // the resident row page is no longer read
