@@ -269,7 +269,7 @@ static int redundancy_simt(const RdParams& p, int D, int dtype, cudaStream_t st)
 
 // tcgen05 path (zp_redundancy_tc.cu)
 int redundancy_tc(const void* k_cache, const int32_t* block_table, void* logits_out, float* rowsum,
-                  long long* sub, int L, int B, int NB, int Hkv, int64_t k_stride_layer,
+                  long long* sub, float* stats, int L, int B, int NB, int Hkv, int64_t k_stride_layer,
                   int64_t k_stride_page, float threshold, float eps, int dtype, bool exact,
                   cudaStream_t st);
 
@@ -322,15 +322,18 @@ extern "C" int zp_redundancy_lightning(const void* k_cache, const int32_t* block
   const int tc = zp::pick_tc(impl, dtype, D, BS, "zp_redundancy_lightning");
   if (tc < 0) return tc;
   if (tc)
-    return zp::redundancy_tc(k_cache, block_table, logits_out, nullptr, nullptr, L, B, NB, Hkv,
+    return zp::redundancy_tc(k_cache, block_table, logits_out, nullptr, nullptr, nullptr, L, B, NB, Hkv,
                              k_stride_layer, k_stride_page, threshold, 1e-6f, dtype, false,
                              (cudaStream_t)stream);
   return zp::redundancy_simt(p, D, dtype, (cudaStream_t)stream);
 }
 
 extern "C" size_t zp_redundancy_exact_workspace_bytes(int L, int B, int NB, int Hkv, int BS) {
-  const size_t n = (size_t)L * B * Hkv * NB * BS;
-  return n * (sizeof(float) + sizeof(long long)) + 256;
+  // fixed-point subtrahends + row sums; for the tcgen05 kernel also the latest-similar-key records
+  // (64 bits per key, zeroed with the subtrahends) and the key statistics:
+  // 1/|k| and self-similarity per key, the smallest norm per 32-key chunk, one 128-vector per unit
+  const size_t units = (size_t)L * B * Hkv, n = units * NB * BS;
+  return n * (sizeof(float) + 2 * sizeof(long long)) + (2 * n + units * ((size_t)NB * 8 + 128)) * sizeof(float) + 256;
 }
 
 extern "C" int zp_redundancy_exact(const void* k_cache, const int32_t* block_table, void* logits_out,
@@ -350,8 +353,11 @@ extern "C" int zp_redundancy_exact(const void* k_cache, const int32_t* block_tab
   const size_t n = (size_t)L * B * Hkv * NB * BS;
   uintptr_t w = ((uintptr_t)workspace + 255) & ~(uintptr_t)255;
   long long* sub = reinterpret_cast<long long*>(w);
-  float* rowsum = reinterpret_cast<float*>(w + n * sizeof(long long));
-  cudaError_t e = cudaMemsetAsync(sub, 0, n * sizeof(long long), st);
+  float* rowsum = reinterpret_cast<float*>(w + 2 * n * sizeof(long long));
+  float* stats = rowsum + n;
+  const int tc = zp::pick_tc(impl, dtype, D, BS, "zp_redundancy_exact");
+  if (tc < 0) return tc;
+  cudaError_t e = cudaMemsetAsync(sub, 0, (tc ? 2 : 1) * n * sizeof(long long), st);
   if (e != cudaSuccess) { zp::set_error("zp_redundancy_exact: %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
   zp::RdParams p{};
   p.k_cache = k_cache; p.block_table = block_table; p.logits_out = logits_out;
@@ -359,9 +365,7 @@ extern "C" int zp_redundancy_exact(const void* k_cache, const int32_t* block_tab
   p.L = L; p.B = B; p.NB = NB; p.Hkv = Hkv; p.BS = BS;
   p.k_stride_layer = k_stride_layer; p.k_stride_page = k_stride_page;
   p.threshold = threshold; p.eps = 1e-6f; p.exact = 1;
-  const int tc = zp::pick_tc(impl, dtype, D, BS, "zp_redundancy_exact");
-  if (tc < 0) return tc;
-  int rc = tc ? zp::redundancy_tc(k_cache, block_table, logits_out, rowsum, sub, L, B, NB, Hkv,
+  int rc = tc ? zp::redundancy_tc(k_cache, block_table, logits_out, rowsum, sub, stats, L, B, NB, Hkv,
                                   k_stride_layer, k_stride_page, threshold, 1e-6f, dtype, true, st)
               : zp::redundancy_simt(p, D, dtype, st);
   if (rc) return rc;

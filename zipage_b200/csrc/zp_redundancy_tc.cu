@@ -14,11 +14,23 @@
 // middle of its items, so the phases of consecutive pages overlap and the tensor pipe is fed by
 // whichever team has a free accumulator.
 //   lightning: a job is a unit; rows and columns are the same page (A = B tile).
-//   exact:     a job is (unit, row page); the row page stays resident, every page streams by.
+//   exact:     a job is (unit, row page I); the row page stays resident and the column pages
+//              J >= I stream by.  S is symmetric, so the tiles below the diagonal are never
+//              computed: an entry (m, n) above the threshold found in tile (I, J) is recorded for
+//              key m and, when J > I, for key n as well.
 // Blocks walk over the jobs with a fixed stride, so the pipeline never drains between jobs.
-// The epilogue keeps row-wise state only (row sum, last column above the threshold and its value);
-// see zp_redundancy.cu for why that is enough.  The "subtract the exempted entries" step uses
-// 64-bit fixed-point atomics (2^-32 units), so the result does not depend on execution order.
+// Exact form, row sums without touching every element: sum_n S[m,n] = (k_m / |k_m|) . w with
+// w = sum_n k_n / |k_n|, a vector a small pre-pass (key_stats_kernel) computes once per unit together
+// with the norms.  The epilogue then only has to FIND entries above the threshold: a 3-input max
+// over the raw accumulators against the bound thr * |k_m| * min|k_n| of the 32-column chunk, and a
+// look at the normalised values only where that bound is exceeded.  That leaves the kernel bound
+// by the tensor pipe instead of by epilogue instruction issue.
+// Per key the op needs the row sum and the LAST other key above the threshold with its similarity
+// (see zp_redundancy.cu for why that is enough).  The lightning form keeps both as per-thread row
+// state; the exact form records the latter with a 64-bit atomicMax on (index + 1) << 32 | value
+// bits, which a small kernel afterwards turns into the "subtract the exempted entries" sums.  Those
+// sums use 64-bit fixed-point atomics (2^-32 units), so the result does not depend on execution
+// order.
 #include "zp_tc.cuh"
 
 namespace zp {
@@ -39,6 +51,12 @@ struct RtParams {
   int L, B, NB, Hkv;
   float threshold, eps;
   int total_jobs;
+  // exact form: per-key statistics from key_stats_kernel
+  const float* rn;     // [units][NB*256]  1 / |k|
+  const float* dself;  // [units][NB*256]  the key's similarity with itself (the zeroed diagonal)
+  const float* nmin;   // [units][NB*8]    smallest |k| of each 32-key chunk
+  const float* wvec;   // [units][128]     sum over the sequence of k / |k|
+  unsigned long long* best;  // [units][NB*256] exact form: latest similar key, packed; zeroed
 };
 
 struct __align__(16) RtTeam {        // per epilogue team
@@ -51,8 +69,9 @@ struct __align__(16) RtTeam {        // per epilogue team
 };
 
 struct __align__(16) RtShared {
-  uint64_t full[RT_NBUF], empty[RT_NBUF], tfull[2], tempty[2], afull, aempty, team_bar[2], all_bar;
+  uint64_t full[RT_NBUF], empty[RT_NBUF], tfull[2], tempty[2], afull, aempty, team_bar[2];
   RtTeam team[2];
+  alignas(16) float wv[128];         // exact form: the unit's sum of normalised keys
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -88,14 +107,14 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < RT_NBUF; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 2); }
+    // a stage is released by the MMA commit and, in the lightning form, by the team that read it
+    for (int i = 0; i < RT_NBUF; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], EXACT ? 1 : 2); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 8);
       mbar_init(&sh.team_bar[i], 8);   // one arrival per warp of the team
     }
     mbar_init(&sh.afull, 1);
-    mbar_init(&sh.aempty, 1);
-    mbar_init(&sh.all_bar, 16);
+    mbar_init(&sh.aempty, 2);  // MMA commit + the epilogue's row-sum pass over the resident page
     sh.abort_flag = 0;
     fence_mbar_init();
   }
@@ -139,7 +158,7 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
           tma_load_5d(bufs, &tmK, &sh.afull, 0, jb.h, 0, id, jb.l);
           tma_load_5d(bufs + RT_BLOCK_BYTES, &tmK, &sh.afull, 64, jb.h, 0, id, jb.l);
         }
-        for (int pg = 0; pg < p.NB; ++pg) {
+        for (int pg = EXACT ? jb.mp : 0; pg < p.NB; ++pg) {
           const PageRef cp = decode_page(jb.table[pg]);
           if (!cp.valid) continue;
           const int s = t % NS, k = t / NS;
@@ -175,7 +194,7 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
         if (!jb.valid) continue;
         if (EXACT && !mbar_wait<true>(&sh.afull, nj & 1, abortp, p.error_word, 201)) break;
         int nvalid = 0;
-        for (int pg = 0; pg < p.NB; ++pg) nvalid += jb.table[pg] != -1;
+        for (int pg = EXACT ? jb.mp : 0; pg < p.NB; ++pg) nvalid += jb.table[pg] != -1;
         for (int i = 0; ok && i < nvalid; i += 2) {
           const int npair = min(2, nvalid - i);
           for (int j = 0; ok && j < npair; ++j) {
@@ -207,19 +226,12 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
     RtTeam& tm = sh.team[team];
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + team * 256 + grp * 128;
     const float eps_t = round_to<T>(p.eps);
-    uint32_t ph_team = 0, ph_all = 0;
+    uint32_t ph_team = 0;
     auto sync_team = [&](int where) -> bool {
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh.team_bar[team]);
       const bool ok_ = mbar_wait(&sh.team_bar[team], ph_team & 1, abortp, p.error_word, where);
       ++ph_team;
-      return ok_;
-    };
-    auto sync_all = [&](int where) -> bool {
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh.all_bar);
-      const bool ok_ = mbar_wait(&sh.all_bar, ph_all & 1, abortp, p.error_word, where);
-      ++ph_all;
       return ok_;
     };
     int t = 0, nj = 0;
@@ -230,16 +242,15 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
       const int32_t* table = jb.table;
       float rsum[2] = {0.f, 0.f}, bval[2] = {0.f, 0.f}, rn_m[2] = {0.f, 0.f}, thr_m[2] = {0.f, 0.f};
       int bcol[2] = {-1, -1};
+      const int64_t ubase = (int64_t)jb.unit * p.NB * 256;
       if (EXACT) {
-        if (!mbar_wait(&sh.afull, nj & 1, abortp, p.error_word, 301)) break;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          const float nrm = fmaxf(round_to<T>(sqrtf(row_sumsq<T>(bufs, r + 128 * hh))), eps_t);
-          rn_m[hh] = 1.f / nrm;
-          thr_m[hh] = p.threshold * nrm;
+          rn_m[hh] = p.rn[ubase + jb.mp * 256 + r + 128 * hh];
+          thr_m[hh] = p.threshold / rn_m[hh];
         }
       }
-      for (int pg = 0; pg < p.NB; ++pg) {
+      for (int pg = EXACT ? jb.mp : 0; pg < p.NB; ++pg) {
         if (table[pg] == -1) {
           if (!EXACT && team == 0)  // padded page: logits -inf
             reinterpret_cast<T*>(p.logits_out)[((int64_t)jb.unit * p.NB + pg) * 256 + myrow] = Elem<T>::from_f32(-INFINITY);
@@ -248,19 +259,23 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
         const int tt = t++;
         if ((tt & 1) != team) continue;   // the other team's page
         const int s = tt % NS, k = tt / NS;
-        if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 302)) { ok = false; break; }
-        {   // a warp covers exactly one 32-column chunk of the page
-          const float nrm = fmaxf(round_to<T>(sqrtf(row_sumsq<T>(stage_ptr(s), myrow))), eps_t);
-          tm.rn[myrow] = 1.f / nrm;
-          float mn = nrm;
+        float nm[4] = {0.f, 0.f, 0.f, 0.f};   // exact form: smallest |k| of this thread's four chunks
+        if (EXACT) {
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-          if (lane == 0) tm.nmin[grp * 4 + q] = mn;
-          if (!EXACT) tm.s_sub[myrow] = 0ull;
-        }
-        if (!sync_team(303)) { ok = false; break; }
-        if ((ew & 7) == 0 && lane == 0) mbar_arrive(&sh.empty[s]);  // the team is done reading the stage
-        if (!EXACT) {
+          for (int c = 0; c < 4; ++c) nm[c] = p.nmin[(int64_t)jb.unit * p.NB * 8 + pg * 8 + grp * 4 + c];
+        } else {
+          if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 302)) { ok = false; break; }
+          {   // a warp covers exactly one 32-column chunk of the page
+            const float nrm = fmaxf(round_to<T>(sqrtf(row_sumsq<T>(stage_ptr(s), myrow))), eps_t);
+            tm.rn[myrow] = 1.f / nrm;
+            float mn = nrm;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+            if (lane == 0) tm.nmin[grp * 4 + q] = mn;
+            tm.s_sub[myrow] = 0ull;
+          }
+          if (!sync_team(303)) { ok = false; break; }
+          if ((ew & 7) == 0 && lane == 0) mbar_arrive(&sh.empty[s]);  // the team is done reading the stage
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
             rn_m[hh] = tm.rn[r + 128 * hh]; thr_m[hh] = p.threshold / rn_m[hh];
@@ -273,7 +288,7 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
           const int use = (tt >> 1) * 2 + hh;
           if (!mbar_wait(&sh.tfull[team], use & 1, abortp, p.error_word, 304)) { ok = false; break; }
           fence_after_sync();
-          float2 sa = make_float2(0.f, 0.f), sb = sa;
+          float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t raw[32];
@@ -289,30 +304,53 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
 #pragma unroll
               for (int j = 0; j < 32; ++j) raw[j] = (j == lane) ? 0u : raw[j];
             }
-            // row sum: acc * (1/|k_n|) accumulated two columns at a time; threshold filter on the raw
-            // accumulators: S > thr needs acc > thr * |k_m| * |k_n| >= thr * |k_m| * min|k_n|
-            const float4* rn4 = reinterpret_cast<const float4*>(tm.rn + cg * 32);
+            // threshold filter on the raw accumulators: S > thr needs
+            // acc > thr * |k_m| * |k_n| >= thr * |k_m| * min|k_n|
             float m0 = -INFINITY, m1 = -INFINITY;
+            if (EXACT) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 f = rn4[j];
-              const float a0 = __uint_as_float(raw[4 * j]), a1 = __uint_as_float(raw[4 * j + 1]);
-              const float a2 = __uint_as_float(raw[4 * j + 2]), a3 = __uint_as_float(raw[4 * j + 3]);
-              ffma2(sa, make_float2(a0, a1), make_float2(f.x, f.y));
-              ffma2(sb, make_float2(a2, a3), make_float2(f.z, f.w));
-              m0 = fmax3(m0, a0, a1);
-              m1 = fmax3(m1, a2, a3);
-            }
-            if (fmaxf(m0, m1) > thr_m[hh] * tm.nmin[cg]) {  // rare: look at the normalised values
-              const float* rnc = tm.rn + cg * 32;
+              for (int j = 0; j < 8; ++j) {
+                m0 = fmax3(m0, __uint_as_float(raw[4 * j]), __uint_as_float(raw[4 * j + 1]));
+                m1 = fmax3(m1, __uint_as_float(raw[4 * j + 2]), __uint_as_float(raw[4 * j + 3]));
+              }
+              if (fmaxf(m0, m1) > thr_m[hh] * nm[c]) {  // look at the normalised values
+                const float* rnc = p.rn + ubase + pg * 256 + cg * 32;
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const float v = __uint_as_float(raw[j]) * rnc[j];
-                if (v > thr_m[hh]) { bcol[hh] = pg * 256 + cg * 32 + j; bval[hh] = v; }
+                for (int j = 0; j < 32; ++j) {
+                  const float v = __uint_as_float(raw[j]) * rnc[j];
+                  if (v > thr_m[hh]) {
+                    const unsigned m_key = jb.mp * 256 + r + 128 * hh, n_key = pg * 256 + cg * 32 + j;
+                    const unsigned long long bits = __float_as_uint(v * rn_m[hh]);
+                    atomicMax(p.best + ubase + m_key, ((unsigned long long)(n_key + 1) << 32) | bits);
+                    if (!diag_page)  // the mirrored entry of the tile that is not computed
+                      atomicMax(p.best + ubase + n_key, ((unsigned long long)(m_key + 1) << 32) | bits);
+                  }
+                }
+              }
+            } else {
+              // row sum: acc * (1/|k_n|) accumulated in four chains
+              const float4* rn4 = reinterpret_cast<const float4*>(tm.rn + cg * 32);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 f = rn4[j];
+                const float a0 = __uint_as_float(raw[4 * j]), a1 = __uint_as_float(raw[4 * j + 1]);
+                const float a2 = __uint_as_float(raw[4 * j + 2]), a3 = __uint_as_float(raw[4 * j + 3]);
+                s0 = fmaf(a0, f.x, s0); s1 = fmaf(a1, f.y, s1);
+                s2 = fmaf(a2, f.z, s2); s3 = fmaf(a3, f.w, s3);
+                m0 = fmax3(m0, a0, a1);
+                m1 = fmax3(m1, a2, a3);
+              }
+              if (fmaxf(m0, m1) > thr_m[hh] * tm.nmin[cg]) {  // rare: look at the normalised values
+                const float* rnc = tm.rn + cg * 32;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const float v = __uint_as_float(raw[j]) * rnc[j];
+                  if (v > thr_m[hh]) { bcol[hh] = pg * 256 + cg * 32 + j; bval[hh] = v; }
+                }
               }
             }
           }
-          rsum[hh] += (sa.x + sa.y) + (sb.x + sb.y);
+          rsum[hh] += (s0 + s1) + (s2 + s3);
         }
         if (!ok) break;
         if (!EXACT) {
@@ -342,35 +380,36 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
         }
       }
       if (!ok) break;
-      if (EXACT) {
-        // job done: merge the two teams (even / odd column pages) and their column groups
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          tm.pb_sum[grp][r + 128 * hh] = rsum[hh]; tm.pb_col[grp][r + 128 * hh] = bcol[hh];
-          tm.pb_val[grp][r + 128 * hh] = bval[hh];
-        }
-        if (!sync_all(307)) break;
-        if (team == 0) {
+      if (EXACT && team == 0) {
+        // job done: the row sums from the linear form  sum_n S[m,n] = rn_m * (k_m . w) - S[m,m]
+        if (myrow < 128) sh.wv[myrow] = p.wvec[(int64_t)jb.unit * 128 + myrow];
+        if (!mbar_wait(&sh.afull, nj & 1, abortp, p.error_word, 301)) break;  // (long since complete)
+        if (!sync_team(307)) break;
+        {
           const int row = myrow;
-          const int64_t base = (int64_t)jb.unit * p.NB * 256;
-          float total = 0.f, bv = 0.f;
-          int bc = -1;
+          float d0 = 0.f, d1 = 0.f;   // k_m . w over the resident (swizzled) row page
 #pragma unroll
-          for (int tmi = 0; tmi < 2; ++tmi)
+          for (int blk = 0; blk < 2; ++blk) {
+            const unsigned char* base = bufs + blk * RT_BLOCK_BYTES + row * 128;
 #pragma unroll
-            for (int g2 = 0; g2 < 2; ++g2) {   // fixed order; the largest column index wins
-              total += sh.team[tmi].pb_sum[g2][row];
-              const int c2 = sh.team[tmi].pb_col[g2][row];
-              if (c2 > bc) { bc = c2; bv = sh.team[tmi].pb_val[g2][row]; }
+            for (int c = 0; c < 8; ++c) {
+              const int4 rawk = *reinterpret_cast<const int4*>(base + ((c ^ (row & 7)) << 4));
+              const typename Pair<T>::V* e = reinterpret_cast<const typename Pair<T>::V*>(&rawk);
+              const float4 wa = *reinterpret_cast<const float4*>(&sh.wv[blk * 64 + c * 8]);
+              const float4 wb = *reinterpret_cast<const float4*>(&sh.wv[blk * 64 + c * 8 + 4]);
+              const float2 f0 = Pair<T>::unpack(e[0]), f1 = Pair<T>::unpack(e[1]);
+              const float2 f2 = Pair<T>::unpack(e[2]), f3 = Pair<T>::unpack(e[3]);
+              d0 = fmaf(f0.x, wa.x, d0); d1 = fmaf(f0.y, wa.y, d1);
+              d0 = fmaf(f1.x, wa.z, d0); d1 = fmaf(f1.y, wa.w, d1);
+              d0 = fmaf(f2.x, wb.x, d0); d1 = fmaf(f2.y, wb.y, d1);
+              d0 = fmaf(f3.x, wb.z, d0); d1 = fmaf(f3.y, wb.w, d1);
             }
-          const float rnm = grp == 0 ? rn_m[0] : rn_m[1];
-          p.rowsum[base + jb.mp * 256 + row] = total * rnm;
-          if (bc >= 0) {
-            const long long fx = __float2ll_rn(bv * rnm * 4294967296.f);
-            atomicAdd(reinterpret_cast<unsigned long long*>(p.sub + base + bc), (unsigned long long)fx);
           }
+          const float rnm = grp == 0 ? rn_m[0] : rn_m[1];
+          p.rowsum[ubase + jb.mp * 256 + row] = rnm * (d0 + d1) - p.dself[ubase + jb.mp * 256 + row];
         }
-        if (!sync_all(308)) break;  // pb_* are free again
+        if (!sync_team(308)) break;  // wv and the resident page are free again
+        if (ew == 0 && lane == 0) mbar_arrive(&sh.aempty);
       }
       ++nj;
     }
@@ -381,6 +420,74 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
     fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+// Pre-pass of the exact form: per key 1/|k| (the norm rounded to T as key_norm does) and the key's
+// similarity with itself, per 32-key chunk the smallest norm, per unit w = sum_n k_n / |k_n| in
+// fp32.  One block per unit walks the unit's pages in order (a fixed summation order); a warp owns
+// one 32-key chunk of each page, a lane four of the 128 dims.
+template <typename T>
+__global__ void __launch_bounds__(256)
+key_stats_kernel(const T* __restrict__ k_cache, const int32_t* __restrict__ block_table,
+                 float* __restrict__ rn, float* __restrict__ dself, float* __restrict__ nmin,
+                 float* __restrict__ wvec, int B, int NB, int Hkv, int64_t k_stride_layer,
+                 int64_t k_stride_page, float eps) {
+  __shared__ float part[8][128];
+  const int unit = blockIdx.x;
+  const int h = unit % Hkv, b = (unit / Hkv) % B, l = unit / (Hkv * B);
+  const int lane = threadIdx.x & 31, wv = threadIdx.x >> 5;
+  const float eps_t = round_to<T>(eps);
+  float w0 = 0.f, w1 = 0.f, w2 = 0.f, w3 = 0.f;
+  for (int pg = 0; pg < NB; ++pg) {
+    const PageRef pr = decode_page(block_table[(int64_t)b * NB + pg]);
+    if (!pr.valid) continue;
+    const T* kp = k_cache + (int64_t)l * k_stride_layer + (int64_t)pr.id * k_stride_page +
+                  ((int64_t)(wv * 32) * Hkv + h) * 128 + lane * 4;
+    float my_rn = 0.f, my_ds = 0.f, mn = INFINITY;
+#pragma unroll 1
+    for (int r0 = 0; r0 < 32; r0 += 8) {
+      uint2 raw[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        raw[j] = *reinterpret_cast<const uint2*>(kp + (int64_t)(r0 + j) * Hkv * 128);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float2 a = Pair<T>::unpack(*reinterpret_cast<const typename Pair<T>::V*>(&raw[j].x));
+        const float2 c = Pair<T>::unpack(*reinterpret_cast<const typename Pair<T>::V*>(&raw[j].y));
+        const float ss = warp_sum(fmaf(a.x, a.x, a.y * a.y) + fmaf(c.x, c.x, c.y * c.y));
+        const float nrm = fmaxf(round_to<T>(sqrtf(ss)), eps_t);
+        const float rnv = 1.f / nrm;
+        w0 = fmaf(rnv, a.x, w0); w1 = fmaf(rnv, a.y, w1);
+        w2 = fmaf(rnv, c.x, w2); w3 = fmaf(rnv, c.y, w3);
+        if (lane == r0 + j) { my_rn = rnv; my_ds = rnv * rnv * ss; }
+        mn = fminf(mn, nrm);
+      }
+    }
+    const int64_t idx = ((int64_t)unit * NB + pg) * 256 + wv * 32 + lane;
+    rn[idx] = my_rn;
+    dself[idx] = my_ds;
+    if (lane == 0) nmin[((int64_t)unit * NB + pg) * 8 + wv] = mn;
+  }
+  *reinterpret_cast<float4*>(&part[wv][lane * 4]) = make_float4(w0, w1, w2, w3);
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += part[i][threadIdx.x];
+    wvec[(int64_t)unit * 128 + threadIdx.x] = acc;
+  }
+}
+
+// exact form: key i's latest similar key y = c(i) loses S[i, y] from its row sum
+__global__ void exempt_scatter_kernel(const unsigned long long* __restrict__ best,
+                                      long long* __restrict__ sub, int N, int64_t total) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const unsigned long long bq = best[i];
+  if (!bq) return;
+  const int64_t y = (int64_t)(bq >> 32) - 1;
+  const long long fx = __float2ll_rn(__uint_as_float((unsigned)bq) * 4294967296.f);
+  atomicAdd(reinterpret_cast<unsigned long long*>(sub + (i / N) * N + y), (unsigned long long)fx);
 }
 
 template <typename T>
@@ -404,9 +511,17 @@ static int launch_redundancy_tc(const void* k_cache, const RtParams& p, int64_t 
   const int grid = pp.total_jobs < sms ? pp.total_jobs : sms;
   cudaError_t e;
   if (exact) {
+    key_stats_kernel<T><<<units, 256, 0, st>>>(
+        reinterpret_cast<const T*>(k_cache), p.block_table, const_cast<float*>(p.rn),
+        const_cast<float*>(p.dself), const_cast<float*>(p.nmin), const_cast<float*>(p.wvec), p.B, p.NB,
+        p.Hkv, k_stride_layer, k_stride_page, p.eps);
     auto kern = redundancy_tc_kernel<T, true>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) kern<<<grid, RT_THREADS, smem, st>>>(tm, pp);
+    if (e == cudaSuccess) {
+      kern<<<grid, RT_THREADS, smem, st>>>(tm, pp);
+      const int64_t total = (int64_t)units * p.NB * 256;
+      exempt_scatter_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p.best, p.sub, p.NB * 256, total);
+    }
   } else {
     auto kern = redundancy_tc_kernel<T, false>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -417,11 +532,17 @@ static int launch_redundancy_tc(const void* k_cache, const RtParams& p, int64_t 
 }
 
 // Called by the C entry points in zp_redundancy.cu.
+// Exact form: `sub` holds 2*n zeroed 64-bit words (the subtrahends, then the latest-similar-key
+// records), `stats` 2*n + units*(NB*8 + 128) floats of scratch, n = units*NB*256.
 int redundancy_tc(const void* k_cache, const int32_t* block_table, void* logits_out, float* rowsum,
-                  long long* sub, int L, int B, int NB, int Hkv, int64_t k_stride_layer,
+                  long long* sub, float* stats, int L, int B, int NB, int Hkv, int64_t k_stride_layer,
                   int64_t k_stride_page, float threshold, float eps, int dtype, bool exact,
                   cudaStream_t st) {
   RtParams p;
+  const size_t units_ = (size_t)L * B * Hkv, n_ = units_ * NB * 256;
+  p.best = reinterpret_cast<unsigned long long*>(sub) + n_;  // zeroed together with `sub`
+  p.rn = stats; p.dself = stats + n_; p.nmin = stats + 2 * n_; p.wvec = stats + 2 * n_ + units_ * NB * 8;
+  if (exact && !stats) { set_error("zp_redundancy(tcgen05): no scratch for the key statistics"); return ZP_ERR_WORKSPACE; }
   p.block_table = block_table; p.logits_out = logits_out; p.rowsum = rowsum; p.sub = sub;
   p.error_word = device_error_word();
   p.L = L; p.B = B; p.NB = NB; p.Hkv = Hkv; p.threshold = threshold; p.eps = eps;
