@@ -268,10 +268,14 @@ static int redundancy_simt(const RdParams& p, int D, int dtype, cudaStream_t st)
 }
 
 // tcgen05 path (zp_redundancy_tc.cu)
-int redundancy_tc(const void* k_cache, const int32_t* block_table, void* logits_out, float* rowsum,
-                  long long* sub, float* stats, int L, int B, int NB, int Hkv, int64_t k_stride_layer,
-                  int64_t k_stride_page, float threshold, float eps, int dtype, bool exact,
-                  cudaStream_t st);
+int redundancy_tc(const void* k_cache, const int32_t* block_table, void* logits_out, int L, int B,
+                  int NB, int Hkv, int64_t k_stride_layer, int64_t k_stride_page, float threshold,
+                  float eps, int dtype, cudaStream_t st);
+
+// tcgen05 path of the exact form (zp_redundancy_exact_tc.cu)
+int redundancy_exact_tc(const void* k_cache, const int32_t* block_table, float* rowsum, long long* sub,
+                        float* stats, int L, int B, int NB, int Hkv, int64_t k_stride_layer,
+                        int64_t k_stride_page, float threshold, float eps, int dtype, cudaStream_t st);
 
 // which kernel family a call uses: 1 = tcgen05, 0 = SIMT, <0 = error already set
 static int pick_tc(int impl, int dtype, int D, int BS, const char* who) {
@@ -322,9 +326,8 @@ extern "C" int zp_redundancy_lightning(const void* k_cache, const int32_t* block
   const int tc = zp::pick_tc(impl, dtype, D, BS, "zp_redundancy_lightning");
   if (tc < 0) return tc;
   if (tc)
-    return zp::redundancy_tc(k_cache, block_table, logits_out, nullptr, nullptr, nullptr, L, B, NB, Hkv,
-                             k_stride_layer, k_stride_page, threshold, 1e-6f, dtype, false,
-                             (cudaStream_t)stream);
+    return zp::redundancy_tc(k_cache, block_table, logits_out, L, B, NB, Hkv, k_stride_layer,
+                             k_stride_page, threshold, 1e-6f, dtype, (cudaStream_t)stream);
   return zp::redundancy_simt(p, D, dtype, (cudaStream_t)stream);
 }
 
@@ -365,8 +368,8 @@ extern "C" int zp_redundancy_exact(const void* k_cache, const int32_t* block_tab
   p.L = L; p.B = B; p.NB = NB; p.Hkv = Hkv; p.BS = BS;
   p.k_stride_layer = k_stride_layer; p.k_stride_page = k_stride_page;
   p.threshold = threshold; p.eps = 1e-6f; p.exact = 1;
-  int rc = tc ? zp::redundancy_tc(k_cache, block_table, logits_out, rowsum, sub, stats, L, B, NB, Hkv,
-                                  k_stride_layer, k_stride_page, threshold, 1e-6f, dtype, true, st)
+  int rc = tc ? zp::redundancy_exact_tc(k_cache, block_table, rowsum, sub, stats, L, B, NB, Hkv,
+                                        k_stride_layer, k_stride_page, threshold, 1e-6f, dtype, st)
               : zp::redundancy_simt(p, D, dtype, st);
   if (rc) return rc;
   const int64_t total = (int64_t)n;

@@ -1,0 +1,446 @@
+// Exact (whole-sequence) key-similarity redundancy on tcgen05 tensor cores
+// (16-bit caches, head_dim 128, page size 256).
+//
+// S = K K^T over the N = NB*256 keys of a unit is symmetric, so only the page tiles (I, J) with
+// J >= I are computed.  What the op needs per key m is
+//   * the row sum  sum_n S[m,n]  (diagonal excluded), and
+//   * the LAST other key n with S[m,n] above the threshold, with that similarity.
+// The row sum is linear in the normalised keys:  sum_n S[m,n] = (k_m / |k_m|) . w - S[m,m]  with
+// w = sum_n k_n / |k_n|; a pre-pass (key_stats_kernel) computes the norms (rounded to T as key_norm
+// does), w and S[m,m] once per unit.  The tensor-core pass then only has to FIND entries above the
+// threshold: a 3-input max over the raw fp32 accumulators against the bound
+// thr * |k_m| * min|k_n| of a 32-column chunk, and a look at the normalised values only where that
+// bound is exceeded.  A hit (m, n) is recorded for key m and, off the diagonal page, for key n
+// (the mirrored entry that is never computed) with a 64-bit atomicMax on (index + 1) << 32 | value
+// bits; a small kernel afterwards turns the records into the "subtract the exempted entries" sums
+// (64-bit fixed point, 2^-32 units, so the result does not depend on execution order).
+//
+// Tiling: a job is (unit, pair of row pages).  Both row pages (512 keys, 128 KB) stay resident in
+// shared memory as the A operands of four row groups of 128; the column pages J >= I stream by
+// in half pages of 128 keys (32 KB stages, 3-deep ring), each multiplied with every row group
+// that needs it (M = 128, N = 128, K = 128 per item).  Two resident row pages halve the bytes a
+// block pulls from L2 per flop compared with one, which is what bounds this kernel.
+// Roles (576 threads, persistent blocks, one per SM): warp 0 = TMA producer and TMEM owner,
+// warp 1 = MMA issuer, warps 2-17 = four epilogue groups of four warps; group g owns row group g
+// and its 128-column accumulator in TMEM, thread <-> TMEM lane <-> similarity row.
+#include "zp_tc.cuh"
+
+namespace zp {
+
+using namespace tc;
+
+constexpr int XT_THREADS = 576;
+constexpr int XT_PAGE_BYTES = 65536;    // 256 keys x 128 dims x 2 bytes
+constexpr int XT_ABLOCK_BYTES = 32768;  // one 64-dim block of a resident page
+constexpr int XT_STAGE_BYTES = 32768;   // half a page: 128 keys
+constexpr int XT_SBLOCK_BYTES = 16384;  // one 64-dim block of a stage
+constexpr int XT_NS = 3;
+
+struct XtParams {
+  const int32_t* block_table;
+  float* rowsum;               // [units][NB*256]
+  unsigned long long* best;    // [units][NB*256] latest similar key, packed; zeroed before the launch
+  int* error_word;
+  int L, B, NB, Hkv;
+  float threshold;
+  int total_jobs, pairs;       // pairs = ceil(NB / 2) row-page pairs per unit
+  const float* rn;             // [units][NB*256]  1 / |k|
+  const float* dself;          // [units][NB*256]  the key's similarity with itself
+  const float* nmin;           // [units][NB*8]    smallest |k| of each 32-key chunk
+  const float* wvec;           // [units][128]     sum over the sequence of k / |k|
+};
+
+struct __align__(16) XtShared {
+  uint64_t full[XT_NS], empty[XT_NS], tfull[4], tempty[4], afull, aempty, all_bar;
+  alignas(16) float wv[2][128];  // the unit's sum of normalised keys, by job parity
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// Pre-pass: per key 1/|k| and the key's similarity with itself, per 32-key chunk the smallest norm,
+// per unit w = sum_n k_n / |k_n| in fp32.  One block per unit walks the unit's pages in order (a
+// fixed summation order); a warp owns one 32-key chunk of each page, a lane four of the 128 dims.
+template <typename T>
+__global__ void __launch_bounds__(256)
+key_stats_kernel(const T* __restrict__ k_cache, const int32_t* __restrict__ block_table,
+                 float* __restrict__ rn, float* __restrict__ dself, float* __restrict__ nmin,
+                 float* __restrict__ wvec, int B, int NB, int Hkv, int64_t k_stride_layer,
+                 int64_t k_stride_page, float eps) {
+  __shared__ float part[8][128];
+  const int unit = blockIdx.x;
+  const int h = unit % Hkv, b = (unit / Hkv) % B, l = unit / (Hkv * B);
+  const int lane = threadIdx.x & 31, wv = threadIdx.x >> 5;
+  const float eps_t = round_to<T>(eps);
+  // after the folding below a lane holds the sum of squares of row `myr` of each group of 8 rows
+  const int myr = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+  const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+  float w0 = 0.f, w1 = 0.f, w2 = 0.f, w3 = 0.f;
+  for (int pg = 0; pg < NB; ++pg) {
+    const PageRef pr = decode_page(block_table[(int64_t)b * NB + pg]);
+    if (!pr.valid) continue;
+    const T* kp = k_cache + (int64_t)l * k_stride_layer + (int64_t)pr.id * k_stride_page +
+                  ((int64_t)(wv * 32) * Hkv + h) * 128 + lane * 4;
+    float mn = INFINITY;
+    const int64_t kbase = ((int64_t)unit * NB + pg) * 256 + wv * 32;
+#pragma unroll 1
+    for (int r0 = 0; r0 < 32; r0 += 8) {
+      uint2 raw[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        raw[j] = *reinterpret_cast<const uint2*>(kp + (int64_t)(r0 + j) * Hkv * 128);
+      float2 a[8], c[8];
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        a[j] = Pair<T>::unpack(*reinterpret_cast<const typename Pair<T>::V*>(&raw[j].x));
+        c[j] = Pair<T>::unpack(*reinterpret_cast<const typename Pair<T>::V*>(&raw[j].y));
+        v[j] = fmaf(a[j].x, a[j].x, a[j].y * a[j].y) + fmaf(c[j].x, c[j].x, c[j].y * c[j].y);
+      }
+      // transposed reduction: 8 values x 32 lanes -> one row total per lane (9 shuffles)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float send = b4 ? v[i] : v[i + 4], keep = b4 ? v[i + 4] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const float send = b3 ? v[i] : v[i + 2], keep = b3 ? v[i + 2] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+      }
+      {
+        const float send = b2 ? v[0] : v[1], keep = b2 ? v[1] : v[0];
+        v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+      }
+      float ss = v[0];
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      const float nrm = fmaxf(round_to<T>(sqrtf(ss)), eps_t);
+      const float rnv = 1.f / nrm;
+      mn = fminf(mn, nrm);
+      if ((lane & 3) == 0) {
+        rn[kbase + r0 + myr] = rnv;
+        dself[kbase + r0 + myr] = rnv * rnv * ss;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float rj = __shfl_sync(0xffffffffu, rnv, ((j >> 2) & 1) * 16 + ((j >> 1) & 1) * 8 + (j & 1) * 4);
+        w0 = fmaf(rj, a[j].x, w0); w1 = fmaf(rj, a[j].y, w1);
+        w2 = fmaf(rj, c[j].x, w2); w3 = fmaf(rj, c[j].y, w3);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    if (lane == 0) nmin[((int64_t)unit * NB + pg) * 8 + wv] = mn;
+  }
+  *reinterpret_cast<float4*>(&part[wv][lane * 4]) = make_float4(w0, w1, w2, w3);
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += part[i][threadIdx.x];
+    wvec[(int64_t)unit * 128 + threadIdx.x] = acc;
+  }
+}
+
+// key i's latest similar key y = c(i) loses S[i, y] from its row sum
+__global__ void exempt_scatter_kernel(const unsigned long long* __restrict__ best,
+                                      long long* __restrict__ sub, int N, int64_t total) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const unsigned long long bq = best[i];
+  if (!bq) return;
+  const int64_t y = (int64_t)(bq >> 32) - 1;
+  const long long fx = __float2ll_rn(__uint_as_float((unsigned)bq) * 4294967296.f);
+  atomicAdd(reinterpret_cast<unsigned long long*>(sub + (i / N) * N + y), (unsigned long long)fx);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(XT_THREADS, 1)
+redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                           const XtParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* bufs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* ring = bufs + 2 * XT_PAGE_BYTES;
+  XtShared& sh = *reinterpret_cast<XtShared*>(ring + XT_NS * XT_STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < XT_NS; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
+    for (int i = 0; i < 4; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 4); }
+    mbar_init(&sh.afull, 1);
+    mbar_init(&sh.aempty, 1);
+    mbar_init(&sh.all_bar, 16);
+    sh.abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&sh.tmem_base, 512);
+    tmem_relinquish();
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = sh.tmem_base;
+  volatile int* abortp = &sh.abort_flag;
+  constexpr uint32_t IDESC = idesc_f16(UmmaFmt<T>::fmt, 128, 128);
+
+  // job -> (unit, row pages i0 and i0 + 1).  All roles walk the same job and item sequences:
+  // column pages pg >= first row page, two halves each; row group g (page i0 + g/2, rows
+  // (g%2)*128..) takes part in column page pg iff its page is valid and pg >= that page.
+  struct Job {
+    int unit, i0, h, l; const int32_t* table; bool rv0, rv1, valid; int pg_begin;
+    __device__ __forceinline__ Job(const XtParams& p, int job) {
+      unit = job / p.pairs;
+      i0 = (job % p.pairs) * 2;
+      h = unit % p.Hkv;
+      const int b = (unit / p.Hkv) % p.B;
+      l = unit / (p.Hkv * p.B);
+      table = p.block_table + (int64_t)b * p.NB;
+      rv0 = table[i0] != -1;
+      rv1 = i0 + 1 < p.NB && table[i0 + 1] != -1;
+      valid = rv0 || rv1;
+      pg_begin = rv0 ? i0 : i0 + 1;
+    }
+    __device__ __forceinline__ bool takes_part(int g, int pg) const {
+      return (g < 2) ? rv0 : (rv1 && pg >= i0 + 1);
+    }
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      prefetch_tensormap(&tmA);
+      prefetch_tensormap(&tmB);
+      int t = 0, nj = 0;
+      bool ok = true;
+      for (int job = blockIdx.x; ok && job < p.total_jobs; job += gridDim.x) {
+        const Job jb(p, job);
+        if (!jb.valid) continue;
+        if (!mbar_wait<true>(&sh.aempty, (nj & 1) ^ 1, abortp, p.error_word, 100)) break;
+        mbar_arrive_expect_tx(&sh.afull, XT_PAGE_BYTES * ((int)jb.rv0 + (int)jb.rv1));
+        for (int a = 0; a < 2; ++a) {
+          if (!(a ? jb.rv1 : jb.rv0)) continue;
+          const int id = decode_page(jb.table[jb.i0 + a]).id;
+          tma_load_5d(bufs + a * XT_PAGE_BYTES, &tmA, &sh.afull, 0, jb.h, 0, id, jb.l);
+          tma_load_5d(bufs + a * XT_PAGE_BYTES + XT_ABLOCK_BYTES, &tmA, &sh.afull, 64, jb.h, 0, id, jb.l);
+        }
+        for (int pg = jb.pg_begin; ok && pg < p.NB; ++pg) {
+          const PageRef cp = decode_page(jb.table[pg]);
+          if (!cp.valid) continue;
+          for (int hf = 0; hf < 2; ++hf, ++t) {
+            const int s = t % XT_NS, k = t / XT_NS;
+            if (!mbar_wait<true>(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 101)) { ok = false; break; }
+            unsigned char* dst = ring + s * XT_STAGE_BYTES;
+            mbar_arrive_expect_tx(&sh.full[s], XT_STAGE_BYTES);
+            tma_load_5d(dst, &tmB, &sh.full[s], 0, jb.h, hf * 128, cp.id, jb.l);
+            tma_load_5d(dst + XT_SBLOCK_BYTES, &tmB, &sh.full[s], 64, jb.h, hf * 128, cp.id, jb.l);
+          }
+        }
+        ++nj;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int t = 0, nj = 0;
+      int use[4] = {0, 0, 0, 0};   // how often each row group's accumulator was used before
+      bool ok = true;
+      for (int job = blockIdx.x; ok && job < p.total_jobs; job += gridDim.x) {
+        const Job jb(p, job);
+        if (!jb.valid) continue;
+        if (!mbar_wait<true>(&sh.afull, nj & 1, abortp, p.error_word, 201)) break;
+        for (int pg = jb.pg_begin; ok && pg < p.NB; ++pg) {
+          if (jb.table[pg] == -1) continue;
+          for (int hf = 0; ok && hf < 2; ++hf, ++t) {
+            const int s = t % XT_NS, k = t / XT_NS;
+            if (!mbar_wait<true>(&sh.full[s], k & 1, abortp, p.error_word, 202)) { ok = false; break; }
+            const uint32_t b_addr = smem_u32(ring + s * XT_STAGE_BYTES);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (!jb.takes_part(g, pg)) continue;
+              if (!mbar_wait<true>(&sh.tempty[g], (use[g] & 1) ^ 1, abortp, p.error_word, 203)) { ok = false; break; }
+              fence_after_sync();
+              const uint32_t a_addr = smem_u32(bufs + (g >> 1) * XT_PAGE_BYTES + (g & 1) * 16384);
+              umma_k128(tmem_base + g * 128, a_addr, XT_ABLOCK_BYTES, b_addr, XT_SBLOCK_BYTES, IDESC);
+              umma_commit(&sh.tfull[g]);
+              ++use[g];
+            }
+            if (ok) umma_commit(&sh.empty[s]);   // the stage is free once these MMAs are done
+          }
+        }
+        if (ok) umma_commit(&sh.aempty);          // so are the resident row pages
+        ++nj;
+      }
+    }
+  } else {
+    // ---------------- epilogue groups ----------------
+    const int ew = warp - 2;
+    const int g = ew >> 2;             // row group
+    const int q = warp & 3;            // TMEM lane quadrant this warp may read
+    const int r = q * 32 + lane;       // row within the group
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + g * 128;
+    uint32_t ph_all = 0;
+    int use = 0, nj = 0;
+    bool ok = true;
+    for (int job = blockIdx.x; ok && job < p.total_jobs; job += gridDim.x) {
+      const Job jb(p, job);
+      if (!jb.valid) continue;
+      const int64_t ubase = (int64_t)jb.unit * p.NB * 256;
+      const int mypage = jb.i0 + (g >> 1);
+      const bool mine = (g < 2) ? jb.rv0 : jb.rv1;
+      const unsigned m_key = mypage * 256 + (g & 1) * 128 + r;
+      float rn_m = 1.f, ds_m = 0.f;
+      if (mine) { rn_m = p.rn[ubase + m_key]; ds_m = p.dself[ubase + m_key]; }
+      const float thr_m = p.threshold / rn_m;
+      // the unit's w into shared memory (two buffers: a group may still be reading the last job's)
+      float* wv = sh.wv[nj & 1];
+      if (ew < 4) wv[r] = p.wvec[(int64_t)jb.unit * 128 + r];
+      if (!mbar_wait(&sh.afull, nj & 1, abortp, p.error_word, 301)) break;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.all_bar);
+      if (!mbar_wait(&sh.all_bar, ph_all & 1, abortp, p.error_word, 302)) break;
+      ++ph_all;
+      if (mine) {
+        // row sum from the linear form: rn_m * (k_m . w) - S[m,m]; the row page is only read here
+        // and by the MMAs, so this overlaps the first products of the job
+        const int row = (g & 1) * 128 + r;
+        float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+          const unsigned char* base = bufs + (g >> 1) * XT_PAGE_BYTES + blk * XT_ABLOCK_BYTES + row * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const int4 rawk = *reinterpret_cast<const int4*>(base + ((c ^ (row & 7)) << 4));
+            const typename Pair<T>::V* e = reinterpret_cast<const typename Pair<T>::V*>(&rawk);
+            const float4 wa = *reinterpret_cast<const float4*>(&wv[blk * 64 + c * 8]);
+            const float4 wb = *reinterpret_cast<const float4*>(&wv[blk * 64 + c * 8 + 4]);
+            const float2 f0 = Pair<T>::unpack(e[0]), f1 = Pair<T>::unpack(e[1]);
+            const float2 f2 = Pair<T>::unpack(e[2]), f3 = Pair<T>::unpack(e[3]);
+            d0 = fmaf(f0.x, wa.x, d0); d1 = fmaf(f0.y, wa.y, d1);
+            d0 = fmaf(f1.x, wa.z, d0); d1 = fmaf(f1.y, wa.w, d1);
+            d0 = fmaf(f2.x, wb.x, d0); d1 = fmaf(f2.y, wb.y, d1);
+            d0 = fmaf(f3.x, wb.z, d0); d1 = fmaf(f3.y, wb.w, d1);
+          }
+        }
+        p.rowsum[ubase + m_key] = rn_m * (d0 + d1) - ds_m;
+      }
+      for (int pg = jb.pg_begin; ok && pg < p.NB; ++pg) {
+        if (jb.table[pg] == -1) continue;
+        if (!jb.takes_part(g, pg)) continue;
+        const bool diag_page = pg == mypage;
+#pragma unroll 1
+        for (int hf = 0; hf < 2; ++hf) {
+          float nm[4];   // smallest |k| of the four 32-column chunks of this half page
+#pragma unroll
+          for (int c = 0; c < 4; ++c) nm[c] = p.nmin[((int64_t)jb.unit * p.NB + pg) * 8 + hf * 4 + c];
+          if (!mbar_wait(&sh.tfull[g], use & 1, abortp, p.error_word, 304)) { ok = false; break; }
+          ++use;
+          fence_after_sync();
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t raw[32];
+            tmem_ld32_issue(lane_base + c * 32, raw);
+            tmem_ld32_wait(raw);
+            if (c == 3) {  // every TMEM read of this item has landed in registers
+              fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&sh.tempty[g]);
+            }
+            if (diag_page && hf == (g & 1) && c == q) {  // warp-uniform: the chunk with this warp's diagonal
+#pragma unroll
+              for (int j = 0; j < 32; ++j) raw[j] = (j == lane) ? 0u : raw[j];
+            }
+            // threshold filter on the raw accumulators: S > thr needs
+            // acc > thr * |k_m| * |k_n| >= thr * |k_m| * min|k_n|
+            float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              m0 = fmax3(m0, __uint_as_float(raw[4 * j]), __uint_as_float(raw[4 * j + 1]));
+              m1 = fmax3(m1, __uint_as_float(raw[4 * j + 2]), __uint_as_float(raw[4 * j + 3]));
+            }
+            if (fmaxf(m0, m1) > thr_m * nm[c]) {  // look at the normalised values
+              const unsigned n0 = pg * 256 + hf * 128 + c * 32;
+              const float* rnc = p.rn + ubase + n0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float v = __uint_as_float(raw[j]) * rnc[j];
+                if (v > thr_m) {
+                  const unsigned long long bits = __float_as_uint(v * rn_m);
+                  atomicMax(p.best + ubase + m_key, ((unsigned long long)(n0 + j + 1) << 32) | bits);
+                  if (!diag_page)  // the mirrored entry of the tile that is not computed
+                    atomicMax(p.best + ubase + n0 + j, ((unsigned long long)(m_key + 1) << 32) | bits);
+                }
+              }
+            }
+          }
+        }
+      }
+      ++nj;
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <typename T>
+static int launch_exact_tc(const void* k_cache, XtParams p, int64_t k_stride_layer, int64_t k_stride_page,
+                           long long* sub, float eps, cudaStream_t st) {
+  CUtensorMap tmA, tmB;
+  const uint64_t pages = p.L > 1 ? (uint64_t)(k_stride_layer / k_stride_page) : (1ull << 30);
+  const uint64_t dims[5] = {128, (uint64_t)p.Hkv, 256, pages, (uint64_t)p.L};
+  const uint64_t strides[4] = {128, (uint64_t)p.Hkv * 128, (uint64_t)k_stride_page,
+                               (uint64_t)(p.L > 1 ? k_stride_layer : k_stride_page)};
+  const uint32_t boxA[5] = {64, 1, 256, 1, 1}, boxB[5] = {64, 1, 128, 1, 1};
+  int rc = make_tensor_map_5d(&tmA, UmmaFmt<T>::tm, k_cache, dims, strides, boxA, sizeof(T));
+  if (rc) return rc;
+  rc = make_tensor_map_5d(&tmB, UmmaFmt<T>::tm, k_cache, dims, strides, boxB, sizeof(T));
+  if (rc) return rc;
+  const int units = p.L * p.B * p.Hkv;
+  p.pairs = (p.NB + 1) / 2;
+  p.total_jobs = units * p.pairs;
+  key_stats_kernel<T><<<units, 256, 0, st>>>(
+      reinterpret_cast<const T*>(k_cache), p.block_table, const_cast<float*>(p.rn),
+      const_cast<float*>(p.dself), const_cast<float*>(p.nmin), const_cast<float*>(p.wvec), p.B, p.NB,
+      p.Hkv, k_stride_layer, k_stride_page, eps);
+  const size_t smem = 2 * XT_PAGE_BYTES + XT_NS * XT_STAGE_BYTES + sizeof(XtShared) + 1024;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = p.total_jobs < sms ? p.total_jobs : sms;
+  auto kern = redundancy_exact_tc_kernel<T>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { set_error("zp_redundancy_exact(tcgen05): %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
+  kern<<<grid, XT_THREADS, smem, st>>>(tmA, tmB, p);
+  const int64_t total = (int64_t)units * p.NB * 256;
+  exempt_scatter_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p.best, sub, p.NB * 256, total);
+  return check_launch("zp_redundancy_exact(tcgen05)");
+}
+
+// Called by zp_redundancy_exact (zp_redundancy.cu).  `sub` holds 2*n zeroed 64-bit words (the
+// fixed-point subtrahends, then the latest-similar-key records), `stats` 2*n + units*(NB*8 + 128)
+// floats of scratch, n = units*NB*256.  Fills rowsum and sub; the caller's finalize kernel makes
+// the logits from them.
+int redundancy_exact_tc(const void* k_cache, const int32_t* block_table, float* rowsum, long long* sub,
+                        float* stats, int L, int B, int NB, int Hkv, int64_t k_stride_layer,
+                        int64_t k_stride_page, float threshold, float eps, int dtype, cudaStream_t st) {
+  XtParams p{};
+  const size_t units = (size_t)L * B * Hkv, n = units * NB * 256;
+  p.block_table = block_table; p.rowsum = rowsum;
+  p.best = reinterpret_cast<unsigned long long*>(sub) + n;
+  p.rn = stats; p.dself = stats + n; p.nmin = stats + 2 * n; p.wvec = stats + 2 * n + units * NB * 8;
+  p.error_word = device_error_word();
+  p.L = L; p.B = B; p.NB = NB; p.Hkv = Hkv; p.threshold = threshold;
+  if (!p.error_word) { set_error("zp_redundancy_exact(tcgen05): no device error word"); return ZP_ERR_CUDA; }
+  if (dtype == ZP_DTYPE_BF16)
+    return launch_exact_tc<__nv_bfloat16>(k_cache, p, k_stride_layer, k_stride_page, sub, eps, st);
+  if (dtype == ZP_DTYPE_F16)
+    return launch_exact_tc<__half>(k_cache, p, k_stride_layer, k_stride_page, sub, eps, st);
+  set_error("zp_redundancy_exact(tcgen05): 16-bit caches only");
+  return ZP_ERR_UNSUPPORTED;
+}
+
+}  // namespace zp
