@@ -15,14 +15,18 @@
 // bits; a small kernel afterwards turns the records into the "subtract the exempted entries" sums
 // (64-bit fixed point, 2^-32 units, so the result does not depend on execution order).
 //
-// Tiling: a job is (unit, pair of row pages).  Both row pages (512 keys, 128 KB) stay resident in
-// shared memory as the A operands of four row groups of 128; the column pages J >= I stream by
-// in half pages of 128 keys (32 KB stages, 3-deep ring), each multiplied with every row group
-// that needs it (M = 128, N = 128, K = 128 per item).  Two resident row pages halve the bytes a
-// block pulls from L2 per flop compared with one, which is what bounds this kernel.
+// Tiling: a job is (unit, row page I).  The row page (256 keys, 64 KB) is the A operand of two
+// row groups of 128; the column pages J >= I stream by as B operands (M = 128, N = 256, K = 128
+// per item, the shape that keeps the tensor pipe at its full rate).  Shared memory holds three
+// page slots that rotate between the two uses: the slots are handed out in the order in which
+// they are released (a column page once its products are issued, the row page at the end of its
+// job), so the next job's row page is fetched while the current job's last column pages are
+// still being multiplied and the pipe never waits for an operand at a job boundary.  Every role
+// replays the same hand-out order from the job sequence alone (SlotFifo).
 // Roles (576 threads, persistent blocks, one per SM): warp 0 = TMA producer and TMEM owner,
-// warp 1 = MMA issuer, warps 2-17 = four epilogue groups of four warps; group g owns row group g
-// and its 128-column accumulator in TMEM, thread <-> TMEM lane <-> similarity row.
+// warp 1 = MMA issuer, warps 2-17 = two epilogue teams of eight warps; team g owns row group g
+// and its 256-column accumulator in TMEM, thread <-> TMEM lane <-> similarity row, the two warps
+// of a lane quadrant split the 256 columns.
 #include "zp_tc.cuh"
 
 namespace zp {
@@ -31,10 +35,8 @@ using namespace tc;
 
 constexpr int XT_THREADS = 576;
 constexpr int XT_PAGE_BYTES = 65536;    // 256 keys x 128 dims x 2 bytes
-constexpr int XT_ABLOCK_BYTES = 32768;  // one 64-dim block of a resident page
-constexpr int XT_STAGE_BYTES = 32768;   // half a page: 128 keys
-constexpr int XT_SBLOCK_BYTES = 16384;  // one 64-dim block of a stage
-constexpr int XT_NS = 3;
+constexpr int XT_BLOCK_BYTES = 32768;   // one 64-dim block of a page
+constexpr int XT_NSLOT = 3;
 
 struct XtParams {
   const int32_t* block_table;
@@ -43,7 +45,7 @@ struct XtParams {
   int* error_word;
   int L, B, NB, Hkv;
   float threshold;
-  int total_jobs, pairs;       // pairs = ceil(NB / 2) row-page pairs per unit
+  int total_jobs;
   const float* rn;             // [units][NB*256]  1 / |k|
   const float* dself;          // [units][NB*256]  the key's similarity with itself
   const float* nmin;           // [units][NB*8]    smallest |k| of each 32-key chunk
@@ -51,10 +53,34 @@ struct XtParams {
 };
 
 struct __align__(16) XtShared {
-  uint64_t full[XT_NS], empty[XT_NS], tfull[4], tempty[4], afull, aempty, all_bar;
-  alignas(16) float wv[2][128];  // the unit's sum of normalised keys, by job parity
+  uint64_t full[XT_NSLOT], empty[XT_NSLOT], tfull[2], tempty[2], adone, team_bar[2];
+  alignas(16) float wv[2][2][128];  // per team, by job parity: the unit's sum of normalised keys
   uint32_t tmem_base;
   int abort_flag;
+};
+
+// The three page slots in the order in which they become free.  pop() = the slot the next load
+// goes to; a column page's slot is pushed back at once (it is released as soon as its products are
+// issued), a row page's slot at the end of its job.  `uses` counts the loads into each slot
+// (mbarrier phase).
+struct SlotFifo {
+  int q0 = 0, q1 = 1, q2 = 2, n = 3;
+  uint32_t uses[XT_NSLOT] = {0, 0, 0};
+  __device__ __forceinline__ int pop() {
+    const int s = q0;
+    q0 = q1; q1 = q2; --n;
+    return s;
+  }
+  __device__ __forceinline__ void push(int s) {
+    if (n == 0) q0 = s; else if (n == 1) q1 = s; else q2 = s;
+    ++n;
+  }
+  // phase bookkeeping of a slot: call once per load into it; returns the number of earlier loads
+  __device__ __forceinline__ uint32_t use(int s) {
+    const uint32_t u = s == 0 ? uses[0] : (s == 1 ? uses[1] : uses[2]);
+    if (s == 0) ++uses[0]; else if (s == 1) ++uses[1]; else ++uses[2];
+    return u;
+  }
 };
 
 // Pre-pass: per key 1/|k| and the key's similarity with itself, per 32-key chunk the smallest norm,
@@ -156,20 +182,19 @@ __global__ void exempt_scatter_kernel(const unsigned long long* __restrict__ bes
 
 template <typename T>
 __global__ void __launch_bounds__(XT_THREADS, 1)
-redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                           const XtParams p) {
+redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmK, const XtParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* bufs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* ring = bufs + 2 * XT_PAGE_BYTES;
-  XtShared& sh = *reinterpret_cast<XtShared*>(ring + XT_NS * XT_STAGE_BYTES);
+  XtShared& sh = *reinterpret_cast<XtShared*>(bufs + XT_NSLOT * XT_PAGE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < XT_NS; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
-    for (int i = 0; i < 4; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 4); }
-    mbar_init(&sh.afull, 1);
-    mbar_init(&sh.aempty, 1);
-    mbar_init(&sh.all_bar, 16);
+    for (int i = 0; i < XT_NSLOT; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 8);
+      mbar_init(&sh.team_bar[i], 8);
+    }
+    mbar_init(&sh.adone, 8);   // the eight warps that read the row page for the row sums
     sh.abort_flag = 0;
     fence_mbar_init();
   }
@@ -182,200 +207,201 @@ redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
   fence_after_sync();
   const uint32_t tmem_base = sh.tmem_base;
   volatile int* abortp = &sh.abort_flag;
-  constexpr uint32_t IDESC = idesc_f16(UmmaFmt<T>::fmt, 128, 128);
+  constexpr uint32_t IDESC = idesc_f16(UmmaFmt<T>::fmt, 128, 256);
 
-  // job -> (unit, row pages i0 and i0 + 1).  All roles walk the same job and item sequences:
-  // column pages pg >= first row page, two halves each; row group g (page i0 + g/2, rows
-  // (g%2)*128..) takes part in column page pg iff its page is valid and pg >= that page.
+  // job -> (unit, row page mp); all roles walk the same sequence of jobs and column pages
   struct Job {
-    int unit, i0, h, l; const int32_t* table; bool rv0, rv1, valid; int pg_begin;
+    int unit, mp, h, l; const int32_t* table; bool valid;
     __device__ __forceinline__ Job(const XtParams& p, int job) {
-      unit = job / p.pairs;
-      i0 = (job % p.pairs) * 2;
+      unit = job / p.NB;
+      mp = job % p.NB;
       h = unit % p.Hkv;
       const int b = (unit / p.Hkv) % p.B;
       l = unit / (p.Hkv * p.B);
       table = p.block_table + (int64_t)b * p.NB;
-      rv0 = table[i0] != -1;
-      rv1 = i0 + 1 < p.NB && table[i0 + 1] != -1;
-      valid = rv0 || rv1;
-      pg_begin = rv0 ? i0 : i0 + 1;
-    }
-    __device__ __forceinline__ bool takes_part(int g, int pg) const {
-      return (g < 2) ? rv0 : (rv1 && pg >= i0 + 1);
+      valid = table[mp] != -1;
     }
   };
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      prefetch_tensormap(&tmA);
-      prefetch_tensormap(&tmB);
-      int t = 0, nj = 0;
+      prefetch_tensormap(&tmK);
+      SlotFifo fifo;
       bool ok = true;
+      auto load_page = [&](int slot, int id, int h, int l, int where) -> bool {
+        const uint32_t u = fifo.use(slot);
+        if (!mbar_wait<true>(&sh.empty[slot], (u & 1) ^ 1, abortp, p.error_word, where)) return false;
+        unsigned char* dst = bufs + slot * XT_PAGE_BYTES;
+        mbar_arrive_expect_tx(&sh.full[slot], XT_PAGE_BYTES);
+        tma_load_5d(dst, &tmK, &sh.full[slot], 0, h, 0, id, l);
+        tma_load_5d(dst + XT_BLOCK_BYTES, &tmK, &sh.full[slot], 64, h, 0, id, l);
+        return true;
+      };
       for (int job = blockIdx.x; ok && job < p.total_jobs; job += gridDim.x) {
         const Job jb(p, job);
         if (!jb.valid) continue;
-        if (!mbar_wait<true>(&sh.aempty, (nj & 1) ^ 1, abortp, p.error_word, 100)) break;
-        mbar_arrive_expect_tx(&sh.afull, XT_PAGE_BYTES * ((int)jb.rv0 + (int)jb.rv1));
-        for (int a = 0; a < 2; ++a) {
-          if (!(a ? jb.rv1 : jb.rv0)) continue;
-          const int id = decode_page(jb.table[jb.i0 + a]).id;
-          tma_load_5d(bufs + a * XT_PAGE_BYTES, &tmA, &sh.afull, 0, jb.h, 0, id, jb.l);
-          tma_load_5d(bufs + a * XT_PAGE_BYTES + XT_ABLOCK_BYTES, &tmA, &sh.afull, 64, jb.h, 0, id, jb.l);
-        }
-        for (int pg = jb.pg_begin; ok && pg < p.NB; ++pg) {
+        const int sa = fifo.pop();
+        ok = load_page(sa, decode_page(jb.table[jb.mp]).id, jb.h, jb.l, 100);
+        for (int pg = jb.mp; ok && pg < p.NB; ++pg) {
           const PageRef cp = decode_page(jb.table[pg]);
           if (!cp.valid) continue;
-          for (int hf = 0; hf < 2; ++hf, ++t) {
-            const int s = t % XT_NS, k = t / XT_NS;
-            if (!mbar_wait<true>(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 101)) { ok = false; break; }
-            unsigned char* dst = ring + s * XT_STAGE_BYTES;
-            mbar_arrive_expect_tx(&sh.full[s], XT_STAGE_BYTES);
-            tma_load_5d(dst, &tmB, &sh.full[s], 0, jb.h, hf * 128, cp.id, jb.l);
-            tma_load_5d(dst + XT_SBLOCK_BYTES, &tmB, &sh.full[s], 64, jb.h, hf * 128, cp.id, jb.l);
-          }
+          const int sb = fifo.pop();
+          fifo.push(sb);
+          ok = load_page(sb, cp.id, jb.h, jb.l, 101);
         }
-        ++nj;
+        fifo.push(sa);
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      int t = 0, nj = 0;
-      int use[4] = {0, 0, 0, 0};   // how often each row group's accumulator was used before
+      SlotFifo fifo;
+      int nj = 0;
+      uint32_t use = 0;   // items issued per row group so far (both groups take part in every page)
       bool ok = true;
       for (int job = blockIdx.x; ok && job < p.total_jobs; job += gridDim.x) {
         const Job jb(p, job);
         if (!jb.valid) continue;
-        if (!mbar_wait<true>(&sh.afull, nj & 1, abortp, p.error_word, 201)) break;
-        for (int pg = jb.pg_begin; ok && pg < p.NB; ++pg) {
+        const int sa = fifo.pop();
+        if (!mbar_wait<true>(&sh.full[sa], fifo.use(sa) & 1, abortp, p.error_word, 201)) break;
+        const uint32_t a_addr = smem_u32(bufs + sa * XT_PAGE_BYTES);
+        for (int pg = jb.mp; ok && pg < p.NB; ++pg) {
           if (jb.table[pg] == -1) continue;
-          for (int hf = 0; ok && hf < 2; ++hf, ++t) {
-            const int s = t % XT_NS, k = t / XT_NS;
-            if (!mbar_wait<true>(&sh.full[s], k & 1, abortp, p.error_word, 202)) { ok = false; break; }
-            const uint32_t b_addr = smem_u32(ring + s * XT_STAGE_BYTES);
+          const int sb = fifo.pop();
+          fifo.push(sb);
+          if (!mbar_wait<true>(&sh.full[sb], fifo.use(sb) & 1, abortp, p.error_word, 202)) { ok = false; break; }
+          const uint32_t b_addr = smem_u32(bufs + sb * XT_PAGE_BYTES);
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (!jb.takes_part(g, pg)) continue;
-              if (!mbar_wait<true>(&sh.tempty[g], (use[g] & 1) ^ 1, abortp, p.error_word, 203)) { ok = false; break; }
-              fence_after_sync();
-              const uint32_t a_addr = smem_u32(bufs + (g >> 1) * XT_PAGE_BYTES + (g & 1) * 16384);
-              umma_k128(tmem_base + g * 128, a_addr, XT_ABLOCK_BYTES, b_addr, XT_SBLOCK_BYTES, IDESC);
-              umma_commit(&sh.tfull[g]);
-              ++use[g];
-            }
-            if (ok) umma_commit(&sh.empty[s]);   // the stage is free once these MMAs are done
+          for (int g = 0; g < 2; ++g) {
+            if (!mbar_wait<true>(&sh.tempty[g], (use & 1) ^ 1, abortp, p.error_word, 203)) { ok = false; break; }
+            fence_after_sync();
+            umma_k128(tmem_base + g * 256, a_addr + g * 16384, XT_BLOCK_BYTES, b_addr, XT_BLOCK_BYTES, IDESC);
+            umma_commit(&sh.tfull[g]);
           }
+          ++use;
+          if (ok) umma_commit(&sh.empty[sb]);   // the slot is free once these products are done
         }
-        if (ok) umma_commit(&sh.aempty);          // so are the resident row pages
+        // the row page: also read by the epilogue for the row sums (long done by now)
+        if (ok) ok = mbar_wait<true>(&sh.adone, nj & 1, abortp, p.error_word, 204);
+        if (ok) umma_commit(&sh.empty[sa]);
+        fifo.push(sa);
         ++nj;
       }
     }
   } else {
-    // ---------------- epilogue groups ----------------
+    // ---------------- epilogue teams ----------------
+    // thread (g, ch, r): row r of row group g, columns ch*128 .. +127 of every column page
     const int ew = warp - 2;
-    const int g = ew >> 2;             // row group
+    const int g = ew >> 3;             // team = row group
     const int q = warp & 3;            // TMEM lane quadrant this warp may read
-    const int r = q * 32 + lane;       // row within the group
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + g * 128;
-    uint32_t ph_all = 0;
-    int use = 0, nj = 0;
+    const int ch = (ew >> 2) & 1;      // column half
+    const int r = q * 32 + lane;
+    const int row = g * 128 + r;       // row within the page
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + g * 256 + ch * 128;
+    SlotFifo fifo;
+    uint32_t ph_team = 0, use = 0;
     bool ok = true;
     for (int job = blockIdx.x; ok && job < p.total_jobs; job += gridDim.x) {
       const Job jb(p, job);
       if (!jb.valid) continue;
       const int64_t ubase = (int64_t)jb.unit * p.NB * 256;
-      const int mypage = jb.i0 + (g >> 1);
-      const bool mine = (g < 2) ? jb.rv0 : jb.rv1;
-      const unsigned m_key = mypage * 256 + (g & 1) * 128 + r;
-      float rn_m = 1.f, ds_m = 0.f;
-      if (mine) { rn_m = p.rn[ubase + m_key]; ds_m = p.dself[ubase + m_key]; }
+      const unsigned m_key = jb.mp * 256 + row;
+      const float rn_m = p.rn[ubase + m_key];
       const float thr_m = p.threshold / rn_m;
-      // the unit's w into shared memory (two buffers: a group may still be reading the last job's)
-      float* wv = sh.wv[nj & 1];
-      if (ew < 4) wv[r] = p.wvec[(int64_t)jb.unit * 128 + r];
-      if (!mbar_wait(&sh.afull, nj & 1, abortp, p.error_word, 301)) break;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh.all_bar);
-      if (!mbar_wait(&sh.all_bar, ph_all & 1, abortp, p.error_word, 302)) break;
-      ++ph_all;
-      if (mine) {
-        // row sum from the linear form: rn_m * (k_m . w) - S[m,m]; the row page is only read here
-        // and by the MMAs, so this overlaps the first products of the job
-        const int row = (g & 1) * 128 + r;
-        float d0 = 0.f, d1 = 0.f;
+      const float4* nmp = reinterpret_cast<const float4*>(p.nmin + ((int64_t)jb.unit * p.NB) * 8) + ch;
+      float4 nm_next = nmp[jb.mp * 2];   // smallest |k| of this thread's four chunks, one page ahead
+      const int sa = fifo.pop();
+      {
+        // Two buffers: a warp that is already in the next job (a job can be a single item) must not
+        // overwrite what a slower warp of the team still reads.
+        float* wv = sh.wv[g][ph_team & 1];
+        // row sums from the linear form rn_m * (k_m . w) - S[m,m].  The row page is only read, so
+        // this overlaps the first products of the job; half of the team's threads do it.
+        const float ds_m = ch == 0 ? p.dself[ubase + m_key] : 0.f;
+        if (ch == 0) wv[r] = p.wvec[(int64_t)jb.unit * 128 + r];
+        if (!mbar_wait(&sh.full[sa], fifo.use(sa) & 1, abortp, p.error_word, 301)) break;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.team_bar[g]);
+        if (!mbar_wait(&sh.team_bar[g], ph_team & 1, abortp, p.error_word, 302)) break;
+        ++ph_team;
+        if (ch == 0) {
+          float d0 = 0.f, d1 = 0.f;
 #pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-          const unsigned char* base = bufs + (g >> 1) * XT_PAGE_BYTES + blk * XT_ABLOCK_BYTES + row * 128;
+          for (int blk = 0; blk < 2; ++blk) {
+            const unsigned char* base = bufs + sa * XT_PAGE_BYTES + blk * XT_BLOCK_BYTES + row * 128;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const int4 rawk = *reinterpret_cast<const int4*>(base + ((c ^ (row & 7)) << 4));
-            const typename Pair<T>::V* e = reinterpret_cast<const typename Pair<T>::V*>(&rawk);
-            const float4 wa = *reinterpret_cast<const float4*>(&wv[blk * 64 + c * 8]);
-            const float4 wb = *reinterpret_cast<const float4*>(&wv[blk * 64 + c * 8 + 4]);
-            const float2 f0 = Pair<T>::unpack(e[0]), f1 = Pair<T>::unpack(e[1]);
-            const float2 f2 = Pair<T>::unpack(e[2]), f3 = Pair<T>::unpack(e[3]);
-            d0 = fmaf(f0.x, wa.x, d0); d1 = fmaf(f0.y, wa.y, d1);
-            d0 = fmaf(f1.x, wa.z, d0); d1 = fmaf(f1.y, wa.w, d1);
-            d0 = fmaf(f2.x, wb.x, d0); d1 = fmaf(f2.y, wb.y, d1);
-            d0 = fmaf(f3.x, wb.z, d0); d1 = fmaf(f3.y, wb.w, d1);
+            for (int c = 0; c < 8; ++c) {
+              const int4 rawk = *reinterpret_cast<const int4*>(base + ((c ^ (row & 7)) << 4));
+              const typename Pair<T>::V* e = reinterpret_cast<const typename Pair<T>::V*>(&rawk);
+              const float4 wa = *reinterpret_cast<const float4*>(&wv[blk * 64 + c * 8]);
+              const float4 wb = *reinterpret_cast<const float4*>(&wv[blk * 64 + c * 8 + 4]);
+              const float2 f0 = Pair<T>::unpack(e[0]), f1 = Pair<T>::unpack(e[1]);
+              const float2 f2 = Pair<T>::unpack(e[2]), f3 = Pair<T>::unpack(e[3]);
+              d0 = fmaf(f0.x, wa.x, d0); d1 = fmaf(f0.y, wa.y, d1);
+              d0 = fmaf(f1.x, wa.z, d0); d1 = fmaf(f1.y, wa.w, d1);
+              d0 = fmaf(f2.x, wb.x, d0); d1 = fmaf(f2.y, wb.y, d1);
+              d0 = fmaf(f3.x, wb.z, d0); d1 = fmaf(f3.y, wb.w, d1);
+            }
           }
+          p.rowsum[ubase + m_key] = rn_m * (d0 + d1) - ds_m;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sh.adone);   // this warp is done with the row page and with wv
         }
-        p.rowsum[ubase + m_key] = rn_m * (d0 + d1) - ds_m;
       }
-      for (int pg = jb.pg_begin; ok && pg < p.NB; ++pg) {
+      for (int pg = jb.mp; ok && pg < p.NB; ++pg) {
         if (jb.table[pg] == -1) continue;
-        if (!jb.takes_part(g, pg)) continue;
-        const bool diag_page = pg == mypage;
+        {  // the column page's slot: not read here, but its phase count must stay in step
+          const int sb = fifo.pop();
+          fifo.push(sb);
+          (void)fifo.use(sb);
+        }
+        const float4 nm4 = nm_next;
+        nm_next = nmp[min(pg + 1, p.NB - 1) * 2];
+        const bool diag_page = pg == jb.mp;
+        if (!mbar_wait(&sh.tfull[g], use & 1, abortp, p.error_word, 304)) { ok = false; break; }
+        ++use;
+        fence_after_sync();
 #pragma unroll 1
-        for (int hf = 0; hf < 2; ++hf) {
-          float nm[4];   // smallest |k| of the four 32-column chunks of this half page
+        for (int c = 0; c < 4; ++c) {
+          uint32_t raw[32];
+          tmem_ld32_issue(lane_base + c * 32, raw);
+          tmem_ld32_wait(raw);
+          if (c == 3) {  // every TMEM read of this item has landed in registers
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.tempty[g]);
+          }
+          if (diag_page && ch == g && c == q) {  // warp-uniform: the chunk with this warp's diagonal
 #pragma unroll
-          for (int c = 0; c < 4; ++c) nm[c] = p.nmin[((int64_t)jb.unit * p.NB + pg) * 8 + hf * 4 + c];
-          if (!mbar_wait(&sh.tfull[g], use & 1, abortp, p.error_word, 304)) { ok = false; break; }
-          ++use;
-          fence_after_sync();
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t raw[32];
-            tmem_ld32_issue(lane_base + c * 32, raw);
-            tmem_ld32_wait(raw);
-            if (c == 3) {  // every TMEM read of this item has landed in registers
-              fence_before_sync();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&sh.tempty[g]);
-            }
-            if (diag_page && hf == (g & 1) && c == q) {  // warp-uniform: the chunk with this warp's diagonal
+            for (int j = 0; j < 32; ++j) raw[j] = (j == lane) ? 0u : raw[j];
+          }
+          // threshold filter on the raw accumulators: S > thr needs
+          // acc > thr * |k_m| * |k_n| >= thr * |k_m| * min|k_n|
+          float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
-              for (int j = 0; j < 32; ++j) raw[j] = (j == lane) ? 0u : raw[j];
-            }
-            // threshold filter on the raw accumulators: S > thr needs
-            // acc > thr * |k_m| * |k_n| >= thr * |k_m| * min|k_n|
-            float m0 = -INFINITY, m1 = -INFINITY;
+          for (int j = 0; j < 8; ++j) {
+            m0 = fmax3(m0, __uint_as_float(raw[4 * j]), __uint_as_float(raw[4 * j + 1]));
+            m1 = fmax3(m1, __uint_as_float(raw[4 * j + 2]), __uint_as_float(raw[4 * j + 3]));
+          }
+          const float nmc = c == 0 ? nm4.x : (c == 1 ? nm4.y : (c == 2 ? nm4.z : nm4.w));
+          if (fmaxf(m0, m1) > thr_m * nmc) {  // look at the normalised values
+            const unsigned n0 = pg * 256 + ch * 128 + c * 32;
+            const float* rnc = p.rn + ubase + n0;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              m0 = fmax3(m0, __uint_as_float(raw[4 * j]), __uint_as_float(raw[4 * j + 1]));
-              m1 = fmax3(m1, __uint_as_float(raw[4 * j + 2]), __uint_as_float(raw[4 * j + 3]));
-            }
-            if (fmaxf(m0, m1) > thr_m * nm[c]) {  // look at the normalised values
-              const unsigned n0 = pg * 256 + hf * 128 + c * 32;
-              const float* rnc = p.rn + ubase + n0;
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const float v = __uint_as_float(raw[j]) * rnc[j];
-                if (v > thr_m) {
-                  const unsigned long long bits = __float_as_uint(v * rn_m);
-                  atomicMax(p.best + ubase + m_key, ((unsigned long long)(n0 + j + 1) << 32) | bits);
-                  if (!diag_page)  // the mirrored entry of the tile that is not computed
-                    atomicMax(p.best + ubase + n0 + j, ((unsigned long long)(m_key + 1) << 32) | bits);
-                }
+            for (int j = 0; j < 32; ++j) {
+              const float v = __uint_as_float(raw[j]) * rnc[j];
+              if (v > thr_m) {
+                const unsigned long long bits = __float_as_uint(v * rn_m);
+                atomicMax(p.best + ubase + m_key, ((unsigned long long)(n0 + j + 1) << 32) | bits);
+                if (!diag_page)  // the mirrored entry of the tile that is not computed
+                  atomicMax(p.best + ubase + n0 + j, ((unsigned long long)(m_key + 1) << 32) | bits);
               }
             }
           }
         }
       }
-      ++nj;
+      fifo.push(sa);
     }
   }
   fence_before_sync();
@@ -389,24 +415,21 @@ redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
 template <typename T>
 static int launch_exact_tc(const void* k_cache, XtParams p, int64_t k_stride_layer, int64_t k_stride_page,
                            long long* sub, float eps, cudaStream_t st) {
-  CUtensorMap tmA, tmB;
+  CUtensorMap tm;
   const uint64_t pages = p.L > 1 ? (uint64_t)(k_stride_layer / k_stride_page) : (1ull << 30);
   const uint64_t dims[5] = {128, (uint64_t)p.Hkv, 256, pages, (uint64_t)p.L};
   const uint64_t strides[4] = {128, (uint64_t)p.Hkv * 128, (uint64_t)k_stride_page,
                                (uint64_t)(p.L > 1 ? k_stride_layer : k_stride_page)};
-  const uint32_t boxA[5] = {64, 1, 256, 1, 1}, boxB[5] = {64, 1, 128, 1, 1};
-  int rc = make_tensor_map_5d(&tmA, UmmaFmt<T>::tm, k_cache, dims, strides, boxA, sizeof(T));
-  if (rc) return rc;
-  rc = make_tensor_map_5d(&tmB, UmmaFmt<T>::tm, k_cache, dims, strides, boxB, sizeof(T));
+  const uint32_t box[5] = {64, 1, 256, 1, 1};
+  int rc = make_tensor_map_5d(&tm, UmmaFmt<T>::tm, k_cache, dims, strides, box, sizeof(T));
   if (rc) return rc;
   const int units = p.L * p.B * p.Hkv;
-  p.pairs = (p.NB + 1) / 2;
-  p.total_jobs = units * p.pairs;
+  p.total_jobs = units * p.NB;
   key_stats_kernel<T><<<units, 256, 0, st>>>(
       reinterpret_cast<const T*>(k_cache), p.block_table, const_cast<float*>(p.rn),
       const_cast<float*>(p.dself), const_cast<float*>(p.nmin), const_cast<float*>(p.wvec), p.B, p.NB,
       p.Hkv, k_stride_layer, k_stride_page, eps);
-  const size_t smem = 2 * XT_PAGE_BYTES + XT_NS * XT_STAGE_BYTES + sizeof(XtShared) + 1024;
+  const size_t smem = XT_NSLOT * XT_PAGE_BYTES + sizeof(XtShared) + 1024;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -414,7 +437,7 @@ static int launch_exact_tc(const void* k_cache, XtParams p, int64_t k_stride_lay
   auto kern = redundancy_exact_tc_kernel<T>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_error("zp_redundancy_exact(tcgen05): %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
-  kern<<<grid, XT_THREADS, smem, st>>>(tmA, tmB, p);
+  kern<<<grid, XT_THREADS, smem, st>>>(tm, p);
   const int64_t total = (int64_t)units * p.NB * 256;
   exempt_scatter_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p.best, sub, p.NB * 256, total);
   return check_launch("zp_redundancy_exact(tcgen05)");
