@@ -282,6 +282,31 @@ def test_redundancy_tcgen05_matches_simt_and_oracle(dtype, exact):
     assert (a[fin] - lo[fin]).abs().max() <= 2e-2 * scale
 
 
+@pytest.mark.parametrize("exact", [False, True])
+def test_redundancy_tcgen05_many_jobs_per_block(exact):
+    """Enough (unit, page) jobs that every persistent block walks through dozens of them, with
+    ragged tables: the stage rings, page-slot rotation and barrier phases wrap many times.  The
+    SIMT kernels are the reference at this size."""
+    from zipage_b200 import _lib, kernel as K
+    from zipage_b200.synthetic import make_compress_workload
+    dev = _gpu()
+    lens = [3 + (i * 7) % 8 for i in range(96)]          # 3..10 pages
+    w = make_compress_workload(B=96, L=2, Hkv=4, Hq=8, QCL=16, budget=2, pages_per_seq=lens,
+                               dtype=torch.bfloat16, device=dev, seed=5, similar_keys=True)
+    k, bt = w.kv_cache[0], w.block_tables
+    for _ in range(2):   # twice: state left behind by a launch must not matter
+        a = K.redundancy_logits(k, bt, 0.5, exact=exact, impl="tcgen05")
+        torch.cuda.synchronize()
+        assert _lib.device_error() == 0
+    b = K.redundancy_logits(k, bt, 0.5, exact=exact, impl="simt")
+    a, b = a.float().reshape(-1), b.float().reshape(-1)
+    fin = torch.isfinite(b)
+    assert torch.equal(fin, torch.isfinite(a))
+    scale = b[fin].abs().max()
+    assert scale > 2.0
+    assert (a[fin] - b[fin]).abs().max() <= 1e-2 * scale
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("Hq,Hkv,QCL,reduced", [(8, 2, 32, "mean"), (4, 2, 16, "mean"), (2, 2, 16, "max"),
                                                  (16, 2, 16, "mean")])

@@ -172,10 +172,13 @@ __global__ void __launch_bounds__(RD_THREADS, 1) redundancy_rows_kernel(const Rd
   }
 }
 
-// exact form: logits = T(rowsum - sub), padded pages -inf
+// exact form: logits = T(rowsum - sub), padded pages -inf.  With `rn` (the tcgen05 path), `rowsum`
+// holds k_m . w and the row sum is rn_m * (k_m . w) - S[m,m] (stats: rn at [0,total), S[m,m] at
+// [total, 2*total)).
 template <typename T>
 __global__ void redundancy_finalize_kernel(const float* __restrict__ rowsum,
                                            const long long* __restrict__ sub,
+                                           const float* __restrict__ rn,
                                            const int32_t* __restrict__ block_table,
                                            T* __restrict__ logits, int B, int NB, int Hkv, int BS,
                                            int64_t total) {
@@ -185,7 +188,8 @@ __global__ void redundancy_finalize_kernel(const float* __restrict__ rowsum,
   const int b = (int)((i / ((int64_t)BS * NB * Hkv)) % B);
   if (block_table[(int64_t)b * NB + pg] == -1) { logits[i] = Elem<T>::from_f32(-INFINITY); return; }
   const float s = (float)((double)sub[i] * (1.0 / 4294967296.0));
-  logits[i] = Elem<T>::from_f32(rowsum[i] - s);
+  const float rs = rn ? rn[i] * rowsum[i] - rn[total + i] : rowsum[i];
+  logits[i] = Elem<T>::from_f32(rs - s);
 }
 
 // One warp per key: norm_out = max(T(sqrt(sum k^2)), T(eps)); padded pages get T(eps).
@@ -358,8 +362,16 @@ extern "C" int zp_redundancy_exact(const void* k_cache, const int32_t* block_tab
   long long* sub = reinterpret_cast<long long*>(w);
   float* rowsum = reinterpret_cast<float*>(w + 2 * n * sizeof(long long));
   float* stats = rowsum + n;
-  const int tc = zp::pick_tc(impl, dtype, D, BS, "zp_redundancy_exact");
+  int tc = zp::pick_tc(impl, dtype, D, BS, "zp_redundancy_exact");
   if (tc < 0) return tc;
+  if (tc && NB > 64) {  // the tcgen05 kernel keeps a 64-bit mask of valid pages
+    if (impl == ZP_IMPL_TCGEN05) {
+      zp::set_error("zp_redundancy_exact: the tcgen05 kernel handles at most 64 pages per sequence");
+      return ZP_ERR_UNSUPPORTED;
+    }
+    tc = 0;
+  }
+  // zeroed: the subtrahends and, for the tcgen05 kernel, the latest-similar-key records
   cudaError_t e = cudaMemsetAsync(sub, 0, (tc ? 2 : 1) * n * sizeof(long long), st);
   if (e != cudaSuccess) { zp::set_error("zp_redundancy_exact: %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
   zp::RdParams p{};
@@ -375,8 +387,9 @@ extern "C" int zp_redundancy_exact(const void* k_cache, const int32_t* block_tab
   const int64_t total = (int64_t)n;
   const int blocks = (int)((total + 255) / 256);
   ZP_DISPATCH_DTYPE(dtype, T, {
-    zp::redundancy_finalize_kernel<T><<<blocks, 256, 0, st>>>(rowsum, sub, block_table,
-                                                             (T*)logits_out, B, NB, Hkv, BS, total);
+    zp::redundancy_finalize_kernel<T><<<blocks, 256, 0, st>>>(rowsum, sub, tc ? stats : nullptr,
+                                                             block_table, (T*)logits_out, B, NB,
+                                                             Hkv, BS, total);
   });
   return zp::check_launch("zp_redundancy_exact finalize");
 }

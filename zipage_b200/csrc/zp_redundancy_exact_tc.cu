@@ -23,24 +23,26 @@
 // job), so the next job's row page is fetched while the current job's last column pages are
 // still being multiplied and the pipe never waits for an operand at a job boundary.  Every role
 // replays the same hand-out order from the job sequence alone (SlotFifo).
-// Roles (576 threads, persistent blocks, one per SM): warp 0 = TMA producer and TMEM owner,
-// warp 1 = MMA issuer, warps 2-17 = two epilogue teams of eight warps; team g owns row group g
-// and its 256-column accumulator in TMEM, thread <-> TMEM lane <-> similarity row, the two warps
-// of a lane quadrant split the 256 columns.
+// Roles (640 threads, persistent blocks, one per SM): warp 0 = TMA producer and TMEM owner,
+// warp 1 = MMA issuer, warps 18-19 = row sums (the k_m . w products, read from the resident row
+// page while the tensor pipe works on it), warps 2-17 = two epilogue teams of eight warps.  Team g owns
+// row group g and its 256-column accumulator in TMEM (thread <-> TMEM lane <-> similarity row,
+// the two warps of a lane quadrant split the 256 columns), so one team reads its accumulator
+// while the tensor pipe fills the other's.
 #include "zp_tc.cuh"
 
 namespace zp {
 
 using namespace tc;
 
-constexpr int XT_THREADS = 576;
+constexpr int XT_THREADS = 640;
 constexpr int XT_PAGE_BYTES = 65536;    // 256 keys x 128 dims x 2 bytes
 constexpr int XT_BLOCK_BYTES = 32768;   // one 64-dim block of a page
 constexpr int XT_NSLOT = 3;
 
 struct XtParams {
   const int32_t* block_table;
-  float* rowsum;               // [units][NB*256]
+  float* rowsum;               // [units][NB*256]  k_m . w (the caller's finalize kernel scales it)
   unsigned long long* best;    // [units][NB*256] latest similar key, packed; zeroed before the launch
   int* error_word;
   int L, B, NB, Hkv;
@@ -53,32 +55,32 @@ struct XtParams {
 };
 
 struct __align__(16) XtShared {
-  uint64_t full[XT_NSLOT], empty[XT_NSLOT], tfull[2], tempty[2], adone, team_bar[2];
-  alignas(16) float wv[2][2][128];  // per team, by job parity: the unit's sum of normalised keys
+  uint64_t full[XT_NSLOT], empty[XT_NSLOT], tfull[2], tempty[2], adone[2], aready[2];
   uint32_t tmem_base;
   int abort_flag;
 };
 
 // The three page slots in the order in which they become free.  pop() = the slot the next load
 // goes to; a column page's slot is pushed back at once (it is released as soon as its products are
-// issued), a row page's slot at the end of its job.  `uses` counts the loads into each slot
-// (mbarrier phase).
+// issued), a row page's slot at the end of its job.  use() keeps the parity of the number of loads
+// into each slot (the mbarrier phase).  One register: bits 0-5 the queue (2 bits per entry), bits
+// 6-7 its length, bits 8-10 the parities.
 struct SlotFifo {
-  int q0 = 0, q1 = 1, q2 = 2, n = 3;
-  uint32_t uses[XT_NSLOT] = {0, 0, 0};
+  uint32_t st = 0u | (1u << 2) | (2u << 4) | (3u << 6);
   __device__ __forceinline__ int pop() {
-    const int s = q0;
-    q0 = q1; q1 = q2; --n;
+    const int s = st & 3u;
+    const uint32_t n = (st >> 6) & 3u;
+    st = (st & ~0xFFu) | ((st >> 2) & 0xFu) | ((n - 1) << 6);
     return s;
   }
   __device__ __forceinline__ void push(int s) {
-    if (n == 0) q0 = s; else if (n == 1) q1 = s; else q2 = s;
-    ++n;
+    const uint32_t n = (st >> 6) & 3u;
+    st = (st & ~(0xC0u | (3u << (2 * n)))) | (static_cast<uint32_t>(s) << (2 * n)) | ((n + 1) << 6);
   }
-  // phase bookkeeping of a slot: call once per load into it; returns the number of earlier loads
+  // call once per load into slot s; returns the parity of the number of earlier loads into it
   __device__ __forceinline__ uint32_t use(int s) {
-    const uint32_t u = s == 0 ? uses[0] : (s == 1 ? uses[1] : uses[2]);
-    if (s == 0) ++uses[0]; else if (s == 1) ++uses[1]; else ++uses[2];
+    const uint32_t u = (st >> (8 + s)) & 1u;
+    st ^= 1u << (8 + s);
     return u;
   }
 };
@@ -190,11 +192,16 @@ redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmK, const XtPara
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < XT_NSLOT; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 8);
-      mbar_init(&sh.team_bar[i], 8);
-    }
-    mbar_init(&sh.adone, 8);   // the eight warps that read the row page for the row sums
+    for (int i = 0; i < 2; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 8); }
+    // the two row-sum warps are done reading the row page; by job parity (two barriers, so that a waiter
+    // one job behind can never see the phase it waits for wrap around)
+    mbar_init(&sh.adone[0], 2);
+    mbar_init(&sh.adone[1], 2);
+    // the job's row page has landed (MMA issuer -> row-sum warp), by job parity as well.  The
+    // row-sum warp cannot use full[] itself: it does not wait for the column pages, so it could
+    // be more than one phase away from a slot's barrier, which a parity wait cannot tell apart.
+    mbar_init(&sh.aready[0], 1);
+    mbar_init(&sh.aready[1], 1);
     sh.abort_flag = 0;
     fence_mbar_init();
   }
@@ -229,9 +236,20 @@ redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmK, const XtPara
       prefetch_tensormap(&tmK);
       SlotFifo fifo;
       bool ok = true;
+      // Per slot: 1 + the running number of the job whose row page it held last, until it is
+      // loaded again (0 = none).  The epilogue reads that page for the row sums after the job's
+      // products are done, so the MMA commit alone does not free it.
+      int pend0 = 0, pend1 = 0, pend2 = 0;
+      uint32_t jobs_done = 0;
       auto load_page = [&](int slot, int id, int h, int l, int where) -> bool {
         const uint32_t u = fifo.use(slot);
         if (!mbar_wait<true>(&sh.empty[slot], (u & 1) ^ 1, abortp, p.error_word, where)) return false;
+        const int pend = slot == 0 ? pend0 : (slot == 1 ? pend1 : pend2);
+        if (pend) {
+          const uint32_t k = pend - 1;
+          if (!mbar_wait<true>(&sh.adone[k & 1], (k >> 1) & 1, abortp, p.error_word, 102)) return false;
+          if (slot == 0) pend0 = 0; else if (slot == 1) pend1 = 0; else pend2 = 0;
+        }
         unsigned char* dst = bufs + slot * XT_PAGE_BYTES;
         mbar_arrive_expect_tx(&sh.full[slot], XT_PAGE_BYTES);
         tma_load_5d(dst, &tmK, &sh.full[slot], 0, h, 0, id, l);
@@ -251,6 +269,8 @@ redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmK, const XtPara
           ok = load_page(sb, cp.id, jb.h, jb.l, 101);
         }
         fifo.push(sa);
+        ++jobs_done;
+        if (sa == 0) pend0 = jobs_done; else if (sa == 1) pend1 = jobs_done; else pend2 = jobs_done;
       }
     }
   } else if (warp == 1) {
@@ -265,6 +285,7 @@ redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmK, const XtPara
         if (!jb.valid) continue;
         const int sa = fifo.pop();
         if (!mbar_wait<true>(&sh.full[sa], fifo.use(sa) & 1, abortp, p.error_word, 201)) break;
+        mbar_arrive(&sh.aready[nj & 1]);
         const uint32_t a_addr = smem_u32(bufs + sa * XT_PAGE_BYTES);
         for (int pg = jb.mp; ok && pg < p.NB; ++pg) {
           if (jb.table[pg] == -1) continue;
@@ -282,110 +303,131 @@ redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmK, const XtPara
           ++use;
           if (ok) umma_commit(&sh.empty[sb]);   // the slot is free once these products are done
         }
-        // the row page: also read by the epilogue for the row sums (long done by now)
-        if (ok) ok = mbar_wait<true>(&sh.adone, nj & 1, abortp, p.error_word, 204);
-        if (ok) umma_commit(&sh.empty[sa]);
+        if (ok) umma_commit(&sh.empty[sa]);   // (the epilogue still reads it: see `adone`)
         fifo.push(sa);
         ++nj;
       }
     }
+  } else if (warp >= 18) {
+    // ---------------- row sums ----------------
+    // k_m . w for the 256 rows of the job's row page (128 per warp), read from the resident
+    // (swizzled) page; sum_n S[m,n] = rn_m * (k_m . w) - S[m,m] is finished by the caller's
+    // finalize kernel.  A lane owns four of the 128 dims (its slice of w stays in registers) and
+    // eight rows are reduced across the warp at a time.  Off the tensor pipe's critical path: the
+    // page slot is only reloaded after the arrival on `adone` (the producer waits for it), which
+    // comes early in the job.
+    const int blk = lane >> 4, cc = (lane >> 1) & 7, half = lane & 1;
+    const int myr = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+    const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+    SlotFifo fifo;
+    uint32_t nj = 0;
+    for (int job = blockIdx.x; job < p.total_jobs; job += gridDim.x) {
+      const Job jb(p, job);
+      if (!jb.valid) continue;
+      const float4 w4 = *reinterpret_cast<const float4*>(p.wvec + (int64_t)jb.unit * 128 + blk * 64 + cc * 8 + half * 4);
+      const int sa = fifo.pop();
+      for (int pg = jb.mp; pg < p.NB; ++pg) {   // replay the column pages' slots
+        if (jb.table[pg] == -1) continue;
+        fifo.push(fifo.pop());
+      }
+      fifo.push(sa);
+      if (!mbar_wait(&sh.aready[nj & 1], (nj >> 1) & 1, abortp, p.error_word, 401)) break;
+      const unsigned char* page = bufs + sa * XT_PAGE_BYTES + blk * XT_BLOCK_BYTES + half * 8;
+      float* out = p.rowsum + (int64_t)job * 256;   // = (unit * NB + row page) * 256
+#pragma unroll 2
+      for (int r0 = (warp - 18) * 128; r0 < (warp - 18) * 128 + 128; r0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int row = r0 + j;
+          const uint2 rawk = *reinterpret_cast<const uint2*>(page + row * 128 + ((cc ^ (row & 7)) << 4));
+          const float2 a = Pair<T>::unpack(*reinterpret_cast<const typename Pair<T>::V*>(&rawk.x));
+          const float2 c = Pair<T>::unpack(*reinterpret_cast<const typename Pair<T>::V*>(&rawk.y));
+          v[j] = fmaf(a.x, w4.x, a.y * w4.y) + fmaf(c.x, w4.z, c.y * w4.w);
+        }
+        // transposed reduction: 8 values x 32 lanes -> one row total per lane
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float send = b4 ? v[i] : v[i + 4], keep = b4 ? v[i + 4] : v[i];
+          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float send = b3 ? v[i] : v[i + 2], keep = b3 ? v[i + 2] : v[i];
+          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+        }
+        {
+          const float send = b2 ? v[0] : v[1], keep = b2 ? v[1] : v[0];
+          v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+        }
+        float tot = v[0];
+        tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+        tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+        if ((lane & 3) == 0) out[r0 + myr] = tot;
+      }
+      __syncwarp();   // every lane is done with the row page
+      if (lane == 0) mbar_arrive(&sh.adone[nj & 1]);
+      ++nj;
+    }
   } else {
     // ---------------- epilogue teams ----------------
-    // thread (g, ch, r): row r of row group g, columns ch*128 .. +127 of every column page
+    // thread (g, ch, r): row r of row group g, columns ch*128 .. +127 of every column page, in
+    // four 32-column chunks
     const int ew = warp - 2;
     const int g = ew >> 3;             // team = row group
     const int q = warp & 3;            // TMEM lane quadrant this warp may read
     const int ch = (ew >> 2) & 1;      // column half
     const int r = q * 32 + lane;
-    const int row = g * 128 + r;       // row within the page
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + g * 256 + ch * 128;
-    SlotFifo fifo;
-    uint32_t ph_team = 0, use = 0;
+    uint32_t use = 0;
+    // fetched during the previous job where possible: 1/|k_m| of this thread's row and the chunk
+    // minima of the first column page
+    int pref_job = -1;
+    float pref_rn = 0.f;
+    float4 pref_nm = make_float4(0.f, 0.f, 0.f, 0.f);
     bool ok = true;
     for (int job = blockIdx.x; ok && job < p.total_jobs; job += gridDim.x) {
-      const Job jb(p, job);
-      if (!jb.valid) continue;
-      const int64_t ubase = (int64_t)jb.unit * p.NB * 256;
-      const unsigned m_key = jb.mp * 256 + row;
-      const float rn_m = p.rn[ubase + m_key];
-      const float thr_m = p.threshold / rn_m;
-      const float4* nmp = reinterpret_cast<const float4*>(p.nmin + ((int64_t)jb.unit * p.NB) * 8) + ch;
-      float4 nm_next = nmp[jb.mp * 2];   // smallest |k| of this thread's four chunks, one page ahead
-      const int sa = fifo.pop();
-      {
-        // Two buffers: a warp that is already in the next job (a job can be a single item) must not
-        // overwrite what a slower warp of the team still reads.
-        float* wv = sh.wv[g][ph_team & 1];
-        // row sums from the linear form rn_m * (k_m . w) - S[m,m].  The row page is only read, so
-        // this overlaps the first products of the job; half of the team's threads do it.
-        const float ds_m = ch == 0 ? p.dself[ubase + m_key] : 0.f;
-        if (ch == 0) wv[r] = p.wvec[(int64_t)jb.unit * 128 + r];
-        if (!mbar_wait(&sh.full[sa], fifo.use(sa) & 1, abortp, p.error_word, 301)) break;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh.team_bar[g]);
-        if (!mbar_wait(&sh.team_bar[g], ph_team & 1, abortp, p.error_word, 302)) break;
-        ++ph_team;
-        if (ch == 0) {
-          float d0 = 0.f, d1 = 0.f;
-#pragma unroll
-          for (int blk = 0; blk < 2; ++blk) {
-            const unsigned char* base = bufs + sa * XT_PAGE_BYTES + blk * XT_BLOCK_BYTES + row * 128;
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              const int4 rawk = *reinterpret_cast<const int4*>(base + ((c ^ (row & 7)) << 4));
-              const typename Pair<T>::V* e = reinterpret_cast<const typename Pair<T>::V*>(&rawk);
-              const float4 wa = *reinterpret_cast<const float4*>(&wv[blk * 64 + c * 8]);
-              const float4 wb = *reinterpret_cast<const float4*>(&wv[blk * 64 + c * 8 + 4]);
-              const float2 f0 = Pair<T>::unpack(e[0]), f1 = Pair<T>::unpack(e[1]);
-              const float2 f2 = Pair<T>::unpack(e[2]), f3 = Pair<T>::unpack(e[3]);
-              d0 = fmaf(f0.x, wa.x, d0); d1 = fmaf(f0.y, wa.y, d1);
-              d0 = fmaf(f1.x, wa.z, d0); d1 = fmaf(f1.y, wa.w, d1);
-              d0 = fmaf(f2.x, wb.x, d0); d1 = fmaf(f2.y, wb.y, d1);
-              d0 = fmaf(f3.x, wb.z, d0); d1 = fmaf(f3.y, wb.w, d1);
-            }
-          }
-          p.rowsum[ubase + m_key] = rn_m * (d0 + d1) - ds_m;
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sh.adone);   // this warp is done with the row page and with wv
-        }
+      const int unit = job / p.NB, mp = job - unit * p.NB;
+      const int32_t* table = p.block_table + (int64_t)((unit / p.Hkv) % p.B) * p.NB;
+      if (table[mp] == -1) continue;
+      uint64_t vmask = 0;   // valid column pages
+      for (int pg = mp; pg < p.NB; ++pg) vmask |= (uint64_t)(table[pg] != -1) << pg;
+      const int64_t rbase = (int64_t)job * 256;   // = (unit * NB + row page) * 256
+      // smallest |k| of this thread's four 32-column chunks, fetched one page ahead
+      const float4* nmp = reinterpret_cast<const float4*>(p.nmin + ((int64_t)unit * p.NB) * 8) + ch;
+      float rn_m;
+      float4 nm_next;
+      if (pref_job == job) { rn_m = pref_rn; nm_next = pref_nm; }
+      else { rn_m = p.rn[rbase + g * 128 + r]; nm_next = __ldg(nmp + mp * 2); }
+      pref_job = job + (int)gridDim.x;
+      if (pref_job < p.total_jobs) {
+        pref_rn = p.rn[(int64_t)pref_job * 256 + g * 128 + r];
+        pref_nm = __ldg(reinterpret_cast<const float4*>(p.nmin) + (int64_t)pref_job * 2 + ch);
       }
-      for (int pg = jb.mp; ok && pg < p.NB; ++pg) {
-        if (jb.table[pg] == -1) continue;
-        {  // the column page's slot: not read here, but its phase count must stay in step
-          const int sb = fifo.pop();
-          fifo.push(sb);
-          (void)fifo.use(sb);
-        }
+      const float thr_m = p.threshold / rn_m;
+      const unsigned m_key = mp * 256 + g * 128 + r;
+      for (int pg = mp; ok && pg < p.NB; ++pg) {
+        if (!((vmask >> pg) & 1)) continue;
         const float4 nm4 = nm_next;
-        nm_next = nmp[min(pg + 1, p.NB - 1) * 2];
-        const bool diag_page = pg == jb.mp;
-        if (!mbar_wait(&sh.tfull[g], use & 1, abortp, p.error_word, 304)) { ok = false; break; }
-        ++use;
-        fence_after_sync();
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t raw[32];
-          tmem_ld32_issue(lane_base + c * 32, raw);
-          tmem_ld32_wait(raw);
-          if (c == 3) {  // every TMEM read of this item has landed in registers
-            fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh.tempty[g]);
-          }
+        nm_next = __ldg(nmp + min(pg + 1, p.NB - 1) * 2);
+        const bool diag_page = pg == mp;
+        // one 32-column chunk: the threshold filter on the raw accumulators (S > thr needs
+        // acc > thr * |k_m| * |k_n| >= thr * |k_m| * min|k_n|), then, rarely, the values
+        auto scan = [&](uint32_t (&raw)[32], int c, float nmc) {
           if (diag_page && ch == g && c == q) {  // warp-uniform: the chunk with this warp's diagonal
 #pragma unroll
             for (int j = 0; j < 32; ++j) raw[j] = (j == lane) ? 0u : raw[j];
           }
-          // threshold filter on the raw accumulators: S > thr needs
-          // acc > thr * |k_m| * |k_n| >= thr * |k_m| * min|k_n|
-          float m0 = -INFINITY, m1 = -INFINITY;
+          // maximum of the 32 values as a tree of 3-input maxima (depth 4)
+          float t[11];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            m0 = fmax3(m0, __uint_as_float(raw[4 * j]), __uint_as_float(raw[4 * j + 1]));
-            m1 = fmax3(m1, __uint_as_float(raw[4 * j + 2]), __uint_as_float(raw[4 * j + 3]));
-          }
-          const float nmc = c == 0 ? nm4.x : (c == 1 ? nm4.y : (c == 2 ? nm4.z : nm4.w));
-          if (fmaxf(m0, m1) > thr_m * nmc) {  // look at the normalised values
+          for (int j = 0; j < 10; ++j)
+            t[j] = fmax3(__uint_as_float(raw[3 * j]), __uint_as_float(raw[3 * j + 1]), __uint_as_float(raw[3 * j + 2]));
+          t[10] = fmaxf(__uint_as_float(raw[30]), __uint_as_float(raw[31]));
+          const float u0 = fmax3(t[0], t[1], t[2]), u1 = fmax3(t[3], t[4], t[5]);
+          const float u2 = fmax3(t[6], t[7], t[8]), u3 = fmaxf(t[9], t[10]);
+          if (fmaxf(fmax3(u0, u1, u2), u3) > thr_m * nmc) {
+            const int64_t ubase = rbase - (int64_t)mp * 256;
             const unsigned n0 = pg * 256 + ch * 128 + c * 32;
             const float* rnc = p.rn + ubase + n0;
 #pragma unroll
@@ -399,9 +441,23 @@ redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmK, const XtPara
               }
             }
           }
+        };
+        if (!mbar_wait(&sh.tfull[g], use & 1, abortp, p.error_word, 304)) { ok = false; break; }
+        ++use;
+        fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t raw[32];
+          tmem_ld32_issue(lane_base + c * 32, raw);
+          tmem_ld32_wait(raw);
+          if (c == 3) {  // every TMEM read of this item has landed in registers
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.tempty[g]);
+          }
+          scan(raw, c, c == 0 ? nm4.x : (c == 1 ? nm4.y : (c == 2 ? nm4.z : nm4.w)));
         }
       }
-      fifo.push(sa);
     }
   }
   fence_before_sync();
