@@ -353,12 +353,19 @@ def main():
         ncu_bytes_per_unit = {"window_score": 760.809e6 / 1024, "redundancy": 614.333e6 / 1024,
                               "compact": 2072.943e6 / 1024, "select": 9.48e6 / 1024}
         if stage_key == "redundancy" and args.variant == "exact":
+            # algorithmic flops = the reference's dense N x N x D similarity product per unit; the
+            # kernel skips the page tiles below the diagonal (S is symmetric), so it executes
+            # NB*(NB+1)/2 of the NB*NB page tiles: both figures are reported.  The stage time also
+            # holds the key-statistics pre-pass (one more read of K) and two small kernels.
             n_tok = (BUDGET + 1) * BS
+            nbp = BUDGET + 1
             flops = 2.0 * n_tok * n_tok * D * units / nlaunch
             peak = peaks.get("bf16_tflops_sustained", 1400.0)
             achieved = flops / (top_ms * 1e-3) / 1e12
-            roofline = {"bound": "tensor", "kernel": "redundancy_tc (exact)", "achieved": achieved,
-                        "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+            roofline = {"bound": "tensor", "kernel": "redundancy_exact_tc (exact similarity stage)",
+                        "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                        "executed": achieved * (nbp + 1) / (2.0 * nbp),
+                        "executed_note": "flops issued to the tensor pipe: upper-triangle page tiles only",
                         "peak_source": "measured sustained cuBLAS bf16 (MEASURED_PEAKS.json)" if peaks
                         else "fallback", "traffic": None}
         else:
