@@ -244,6 +244,61 @@ int zp_varlen_prefill(const void* q, const void* k, const void* v, const int32_t
                       int max_seqlen_q, int NBmax, int Hq, int Hkv, int D, int BS,
                       int64_t kv_stride_page, float softmax_scale, int dtype, void* stream);
 
+/* ---- Per-step ops around the attention path (the rows next to the compression path) -------- */
+
+/* Replaces RMSNorm.forward, third_party/nanovllm/layers/layernorm.py:16-50 (both branches).
+ * x [n_rows, hidden] (row stride given), weight [hidden], out [n_rows, hidden] (row stride given).
+ * residual == NULL: out = T(T(x * rsqrt(mean(x^2) + eps)) * weight).
+ * residual != NULL ([n_rows, hidden] contiguous): s = x + residual in fp32, residual_out = T(s)
+ * (may be the residual buffer itself), out from the UNROUNDED s as the reference does.
+ * out may be x.  hidden <= 2048 16-byte vectors. */
+int zp_rms_norm(const void* x, const void* residual, const void* weight, void* out,
+                void* residual_out, int n_rows, int hidden, int64_t x_stride, int64_t out_stride,
+                float eps, int dtype, void* stream);
+
+/* Replaces SiluAndMul.forward, third_party/nanovllm/layers/activation.py:11-14.
+ * x [n_rows, 2*inter] contiguous -> out [n_rows, inter] = T(T(silu(x[:, :inter])) * x[:, inter:]). */
+int zp_silu_and_mul(const void* x, void* out, int n_rows, int inter, int dtype, void* stream);
+
+/* Replaces, in one launch, the q/k normalisation and rotation of Qwen3Attention.forward
+ * (third_party/nanovllm/models/qwen3.py:75-79: RMSNorm over each q and k head, layernorm.py:17-26,
+ * then apply_rotary_emb, rotary_embedding.py:8-16 and :92-103) and the two cache writes of
+ * Attention.forward (zipage/layers/attention.py:72-77: store_kvcache, store_query_cache).
+ * qkv [n_tokens, (Hq + 2*Hkv) * D] (row stride given) = the fused projection's output;
+ * positions [n_tokens] int64; cos_sin [max_position, D] fp32 (cos in the first half of a row, sin
+ * in the second: RotaryEmbedding.cos_sin_cache); q_weight, k_weight [D].
+ * q_out [n_tokens, Hq, D]; k_out [n_tokens, Hkv, D] or NULL (decode reads K from the cache).
+ * slot_mapping [n_tokens] or NULL: flat cache slot of each token (-1 = skip); k_cache / v_cache
+ * contiguous [P*BS, Hkv, D] (one layer).  triples [n_triples, 3] int32 (row, query_id, window
+ * index) -> query_cache [C, QCL, Hq, D] (one layer; strides in elements). */
+int zp_qk_norm_rope_store(const void* qkv, const int64_t* positions, const float* cos_sin,
+                          const void* q_weight, const void* k_weight, float eps, void* q_out,
+                          void* k_out, void* k_cache, void* v_cache, const int32_t* slot_mapping,
+                          void* query_cache, const int32_t* triples, int n_triples, int n_tokens,
+                          int Hq, int Hkv, int D, int64_t qkv_stride, int64_t cache_stride_seq,
+                          int64_t cache_stride_slot, int dtype, void* stream);
+
+/* Replaces Sampler.calculate_probs + Sampler.sample, zipage/layers/sampler.py:17-31.
+ * logits [n_rows, vocab] T, temperatures [n_rows] fp32; tokens_out [n_rows] int64 =
+ * argmax(softmax(fp32 logits / T) / max(noise, 1e-10)), lowest index on ties.  noise [n_rows,
+ * vocab] fp32 holds the Exp(1) draws (the reference makes them with Tensor.exponential_); with
+ * noise == NULL they come from a counter-based generator keyed by (seed, row, index), which is a
+ * different stream of draws than torch's. */
+int zp_sample(const void* logits, const float* temperatures, const float* noise,
+              int64_t* tokens_out, int n_rows, int vocab, uint64_t seed, int dtype, void* stream);
+
+/* Replaces the host loop of ModelRunner.prepare_decode, zipage/engine/model_runner.py:633-675
+ * (with get_query_slot_mapping, :319-350), from device-resident state, so that a decode step
+ * needs no host-built lists: num_tokens [B] (len(seq)), block_tables [B, table_width] (-1 padded,
+ * e.g. as zp_update_tables leaves them), query_ids [B] (-1 = no window buffer).
+ * positions_out [B] int64 = num_tokens - 1; context_lens_out [B]; slot_mapping_out [B];
+ * triples_out [B, 3] (the first *n_triples_out rows are valid, in sequence order). */
+int zp_prepare_decode(const int32_t* num_tokens, const int32_t* block_tables,
+                      const int32_t* query_ids, int B, int table_width, int query_cache_len,
+                      int block_size, int64_t* positions_out, int32_t* context_lens_out,
+                      int32_t* slot_mapping_out, int32_t* triples_out, int32_t* n_triples_out,
+                      void* stream);
+
 #ifdef __cplusplus
 }
 #endif
