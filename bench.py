@@ -46,8 +46,10 @@ def parse_args():
     ap.add_argument("--kernel-impl", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--also-exact", action="store_true", help="time the exact variant as well")
-    ap.add_argument("--workload", default="compress", choices=["compress", "decode"],
-                    help="compress (default, the headline op) or decode (paged decode attention kernel)")
+    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops"],
+                    help="compress (default, the headline op), decode (paged decode attention kernel) or "
+                         "step_ops (the element-wise ops of a decoder layer step and the sampler)")
+    ap.add_argument("--tokens", type=int, default=32768, help="tokens per call of the step_ops workload")
     return ap.parse_args()
 
 
@@ -230,12 +232,90 @@ def run_decode(args):
     }))
 
 
+def run_step_ops(args):
+    """The per-step ops of one decoder layer at Qwen3-8B sizes (hidden 4096, intermediate 12288,
+    32 query / 8 KV heads of 128) on a prefill-sized batch of tokens, so that every input is larger
+    than the L2, plus the sampler at the full vocabulary.  Each op is timed alone with CUDA events
+    and reported as algorithmic HBM bytes per second (what the op must read and write once)."""
+    import torch
+    from zipage_b200 import kernel as K
+    from zipage_b200.layers import step_ops as P
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    N, H, I, V, Bs = args.tokens, 4096, 12288, 151936, 512
+    bf = torch.bfloat16
+    x = torch.randn(N, H, device=dev, dtype=bf)
+    res = torch.randn(N, H, device=dev, dtype=bf)
+    w = torch.ones(H, device=dev, dtype=bf)
+    gate_up = torch.randn(N, 2 * I, device=dev, dtype=bf)
+    qkv = torch.randn(N, (HQ + 2 * HKV) * D, device=dev, dtype=bf)
+    wq, wk = torch.ones(D, device=dev, dtype=bf), torch.ones(D, device=dev, dtype=bf)
+    pos = torch.randint(0, 32768, (N,), device=dev)
+    cs = P.rope_cos_sin_cache(D, 32768, 1e6, dev)
+    pages = (N + BS - 1) // BS
+    kc = torch.empty((pages * BS, HKV, D), device=dev, dtype=bf)
+    vc = torch.empty_like(kc)
+    # a prefill batch: consecutive tokens fill consecutive slots of a page, the pages are scattered
+    tok = torch.arange(N, device=dev)
+    slots = (torch.randperm(pages, device=dev)[tok // BS] * BS + tok % BS).to(torch.int32)
+    logits = torch.randn(Bs, V, device=dev, dtype=bf)
+    temps = torch.full((Bs,), 0.6, device=dev)
+    e = 2
+    ops = {
+        "add_rms_norm": (lambda: P.rms_norm(x, w, 1e-6, residual=res), N * H * e * 4 + H * e),
+        "silu_and_mul": (lambda: P.silu_and_mul(gate_up), N * I * e * 3),
+        "qk_norm_rope_store": (lambda: P.qk_norm_rope_store(qkv, pos, cs, wq, wk, 1e-6, HQ, HKV, D, k_cache=kc,
+                                                            v_cache=vc, slot_mapping=slots, return_k=False),
+                               N * (HQ + 2 * HKV) * D * e + N * HQ * D * e + 2 * N * HKV * D * e + N * (D * 4 + 12)),
+        "sample (built-in draws)": (lambda: P.sample(logits, temps, seed=1), Bs * V * e + Bs * 12),
+    }
+    peaks = {}
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        peaks = json.loads(pk.read_text())
+    hbm_peak = peaks.get("hbm_gbs", 6650.0)
+    per_op, total_ms, total_bytes = {}, 0.0, 0.0
+    K.LAUNCHES = 0
+    with ClockSampler(dev.index or 0) as clocks:
+        for name, (fn, nbytes) in ops.items():
+            for _ in range(args.warmup):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            per_op[name] = {"ms": ms, "algorithmic_bytes": nbytes, "gbs": gbs, "frac": gbs / hbm_peak}
+            total_ms += ms
+            total_bytes += nbytes
+    val = total_bytes / (total_ms * 1e-3) / 1e9
+    worst = min(per_op, key=lambda k_: per_op[k_]["frac"])
+    print(json.dumps({
+        "metric": "step_ops_hbm_gbs", "value": val, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": total_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "per-step ops of one Qwen3-8B decoder layer + sampler", "tokens": N,
+                   "sampler_rows": Bs, "vocab": V,
+                   "l2": "every op's input is larger than the 126 MB L2 (sampler: 155 MB of logits)"},
+        "per_op": per_op, "gpu_launches": K.LAUNCHES, "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "kernel": worst, "achieved": per_op[worst]["gbs"], "peak": hbm_peak,
+                     "unit": "GB/s", "frac": per_op[worst]["frac"],
+                     "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback", "traffic": None},
+    }))
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
     if args.workload == "decode":
         return run_decode(args)
+    if args.workload == "step_ops":
+        return run_step_ops(args)
 
     import torch
     import torch.distributed as dist
