@@ -244,6 +244,18 @@ int zp_varlen_prefill(const void* q, const void* k, const void* v, const int32_t
                       int max_seqlen_q, int NBmax, int Hq, int Hkv, int D, int BS,
                       int64_t kv_stride_page, float softmax_scale, int dtype, void* stream);
 
+/* zp_varlen_prefill with the row counts of q (total_q) and, for dense k/v, of k and v (total_k),
+ * which the tcgen05 kernel needs for its tensor maps (tiles that run past a tensor's end read
+ * zeros instead of memory behind it), and a choice of kernel family: ZP_IMPL_AUTO picks the
+ * tcgen05 kernel for 16-bit tensors with head_dim 128 (pages: a multiple of 128 keys) and the
+ * kernels of zp_varlen_prefill otherwise; ZP_IMPL_SIMT always takes the latter; ZP_IMPL_TCGEN05
+ * fails with ZP_ERR_UNSUPPORTED where the tcgen05 kernel cannot run. */
+int zp_varlen_prefill_ex(const void* q, const void* k, const void* v, const int32_t* cu_seqlens_q,
+                         const int32_t* cu_seqlens_k, const int32_t* block_table, void* out, int B,
+                         int max_seqlen_q, int NBmax, int Hq, int Hkv, int D, int BS,
+                         int64_t kv_stride_page, float softmax_scale, int total_q, int total_k,
+                         int impl, int dtype, void* stream);
+
 /* ---- Per-step ops around the attention path (the rows next to the compression path) -------- */
 
 /* Replaces RMSNorm.forward, third_party/nanovllm/layers/layernorm.py:16-50 (both branches).

@@ -70,6 +70,7 @@ SIGNATURES = {
     "zp_paged_decode_noalloc_max_scratch_bytes": (_Z, []),
     "zp_paged_decode_noalloc": (_I, [_P] * 6 + [_I] * 6 + [_L, _F, _I, _P]),
     "zp_varlen_prefill": (_I, [_P] * 7 + [_I] * 7 + [_L, _F, _I, _P]),
+    "zp_varlen_prefill_ex": (_I, [_P] * 7 + [_I] * 7 + [_L, _F, _I, _I, _I, _I, _P]),
     "zp_rms_norm": (_I, [_P] * 5 + [_I, _I, _L, _L, _F, _I, _P]),
     "zp_silu_and_mul": (_I, [_P, _P, _I, _I, _I, _P]),
     "zp_qk_norm_rope_store": (_I, [_P] * 5 + [_F] + [_P] * 7 + [_I] * 5 + [_L] * 3 + [_I, _P]),

@@ -179,7 +179,38 @@ int varlen_prefill_mma(const void* q, const void* k, const void* v, const int32_
                        int Hkv, int BS, int64_t kv_stride_page, float scale_log2e, int dtype,
                        cudaStream_t st);
 
+// tcgen05 path (zp_prefill_tc.cu)
+int varlen_prefill_tc(const void* q, const void* k, const void* v, const int32_t* cu_q, const int32_t* cu_k,
+                      const int32_t* table, void* out, int B, int max_seqlen_q, int NBmax, int Hq, int Hkv,
+                      int BS, int64_t kv_stride_page, float scale_log2e, int total_q, int total_k, int dtype,
+                      cudaStream_t st);
+
 }  // namespace zp
+
+extern "C" int zp_varlen_prefill_ex(const void* q, const void* k, const void* v,
+                                    const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                    const int32_t* block_table, void* out, int B, int max_seqlen_q,
+                                    int NBmax, int Hq, int Hkv, int D, int BS, int64_t kv_stride_page,
+                                    float softmax_scale, int total_q, int total_k, int impl, int dtype,
+                                    void* stream) {
+  const bool can = (dtype == ZP_DTYPE_BF16 || dtype == ZP_DTYPE_F16) && D == 128 && Hkv > 0 &&
+                   Hq % Hkv == 0 && total_q > 0 && (block_table ? BS % 128 == 0 : total_k > 0) &&
+                   ((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) % 16 == 0 &&
+                   (!block_table || (kv_stride_page * 2) % 16 == 0);
+  if (impl == ZP_IMPL_TCGEN05 && !can) {
+    zp::set_error("zp_varlen_prefill_ex: the tcgen05 kernel needs 16-bit tensors, head_dim 128, "
+                  "16-byte aligned pointers, row counts, and pages of a multiple of 128 keys");
+    return ZP_ERR_UNSUPPORTED;
+  }
+  if (impl == ZP_IMPL_SIMT || !can)
+    return zp_varlen_prefill(q, k, v, cu_seqlens_q, cu_seqlens_k, block_table, out, B, max_seqlen_q, NBmax,
+                             Hq, Hkv, D, BS, kv_stride_page, softmax_scale, dtype, stream);
+  if (B == 0 || max_seqlen_q == 0) return ZP_OK;
+  ZP_REQUIRE(q && k && v && cu_seqlens_q && cu_seqlens_k && out, "zp_varlen_prefill_ex: null pointer");
+  return zp::varlen_prefill_tc(q, k, v, cu_seqlens_q, cu_seqlens_k, block_table, out, B, max_seqlen_q, NBmax,
+                               Hq, Hkv, BS, kv_stride_page, softmax_scale * 1.4426950408889634f, total_q,
+                               total_k, dtype, (cudaStream_t)stream);
+}
 
 extern "C" int zp_varlen_prefill(const void* q, const void* k, const void* v,
                                  const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,

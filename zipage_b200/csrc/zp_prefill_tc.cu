@@ -1,0 +1,409 @@
+// Variable-length causal prefill attention (bottom-right aligned) on tcgen05 tensor cores:
+// 16-bit tensors, head_dim 128, K/V dense or paged (page size a multiple of 128).
+//
+// One block per (128-query tile, query head, sequence).  Two passes over the key tiles the query
+// tile can see, 128 keys at a time:
+//   pass 1:  S = Q K^T (M = 128 queries, N = 128 keys, K = 128 dims)   -> row maxima
+//   pass 2:  S again, P = exp2(S * scale*log2e - max) (masked entries 0), row sums of P in fp32,
+//            P rounded to the tensor dtype and written to shared memory as the A operand of
+//            O += P V (M = 128 queries, N = 128 dims, K = 128 keys; V is the B operand as it lies in
+//            memory: dims contiguous, i.e. MN-major), accumulated in TMEM over all tiles
+// and out = O / row sum.  Recomputing S costs half as many tensor-core flops again but needs no
+// rescaling of the output accumulator when a row maximum grows, so O never leaves TMEM and the
+// softmax warps only stream S.
+// Roles (320 threads, one block per SM): warp 0 = TMA producer and TMEM owner, warp 1 = MMA
+// issuer, warps 2-9 = softmax (thread <-> TMEM lane <-> query row; the two warps of a lane
+// quadrant split a tile's 128 columns).  Shared memory: the Q tile, a ring of four 32 KB K/V
+// stages, two P tiles; TMEM: two S accumulators and O (384 of 512 columns).
+// Keys past the end of a sequence: their S columns are masked by index; in the V tile their rows
+// are overwritten with zeros before the product (their P is 0, but 0 * garbage may be NaN).
+#include "zp_tc.cuh"
+
+namespace zp {
+
+using namespace tc;
+
+constexpr int PT_THREADS = 320;
+constexpr int PT_TILE_BYTES = 32768;   // 128 rows x 128 elements x 2 bytes
+constexpr int PT_BLK_BYTES = 16384;    // one 64-element block of a tile
+constexpr int PT_NRING = 4;
+
+struct PtParams {
+  const int32_t* cu_q; const int32_t* cu_k; const int32_t* table;
+  void* out;
+  int* error_word;
+  int B, NBmax, Hq, Hkv, BS;
+  int total_q, total_k;   // rows of q and of dense k/v (tensor-map extents: rows past them read as 0)
+  float scale_log2e;
+};
+
+struct __align__(16) PtShared {
+  uint64_t qfull, full[PT_NRING], empty[PT_NRING], sfull[2], sempty[2], pfull[2], pempty[2], ofull, sbar;
+  float stat[2][128];   // row statistics exchanged between the two column halves
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// MN-major operand tile, 128-byte swizzle: 64 contiguous elements (128 bytes) per K row, 8-row
+// groups `sbo` bytes apart along K, the next 64 elements along MN `lbo` bytes away.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  const uint32_t lo = ((smem_addr >> 4) & 0x3FFFu) | ((lbo >> 4) << 16);
+  const uint32_t hi = (sbo >> 4) | (1u << 14) | (2u << 29);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(PT_THREADS, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const PtParams p) {
+  // tile geometry (identical in every role)
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
+  const int k0 = p.cu_k[b], lk = p.cu_k[b + 1] - k0;
+  const int nqt = (lq + 127) >> 7;
+  if ((int)blockIdx.x >= nqt) return;
+  const int qt = nqt - 1 - blockIdx.x;          // the tiles with the most keys start first
+  const int qi0 = qt * 128;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int shift = lk - lq;                    // query i sees keys j <= i + shift
+  const int rows = min(128, lq - qi0);
+  const int kmax = min(lk, qi0 + rows + shift); // keys any row of the tile can see
+  const int n = kmax > 0 ? (kmax + 127) >> 7 : 0;
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* bufs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* qbuf = bufs;
+  unsigned char* ring = bufs + PT_TILE_BYTES;
+  unsigned char* pbuf = ring + PT_NRING * PT_TILE_BYTES;
+  PtShared& sh = *reinterpret_cast<PtShared*>(pbuf + 2 * PT_TILE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (n == 0) {   // nothing visible: zeros
+    if (warp >= 2) {
+      const int t = threadIdx.x - 64;           // 256 threads: row t >> 1, half t & 1
+      const int r = t >> 1;
+      if (r < rows) {
+        T* o = reinterpret_cast<T*>(p.out) + ((int64_t)(q0 + qi0 + r) * p.Hq + h) * 128 + (t & 1) * 64;
+        for (int i = 0; i < 64; i += 8) *reinterpret_cast<int4*>(o + i) = make_int4(0, 0, 0, 0);
+      }
+    }
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sh.qfull, 1);
+    for (int i = 0; i < PT_NRING; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sh.sfull[i], 1); mbar_init(&sh.sempty[i], 8);
+      mbar_init(&sh.pfull[i], 8); mbar_init(&sh.pempty[i], 1);
+    }
+    mbar_init(&sh.ofull, 1);
+    mbar_init(&sh.sbar, 8);   // the eight softmax warps (a bounded wait, unlike bar.sync)
+    sh.abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&sh.tmem_base, 512);
+    tmem_relinquish();
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = sh.tmem_base;
+  volatile int* abortp = &sh.abort_flag;
+  constexpr uint32_t IDESC_QK = idesc_f16(UmmaFmt<T>::fmt, 128, 128);
+  constexpr uint32_t IDESC_PV = IDESC_QK | (1u << 16);   // B operand MN-major
+
+  // ring position of a load: pass 1: K_j -> j; pass 2: K_j -> n + 2j, V_j -> n + 2j + 1
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      prefetch_tensormap(&tmQ);
+      prefetch_tensormap(&tmK);
+      prefetch_tensormap(&tmV);
+      mbar_arrive_expect_tx(&sh.qfull, PT_TILE_BYTES);
+      tma_load_5d(qbuf, &tmQ, &sh.qfull, 0, h, q0 + qi0, 0, 0);
+      tma_load_5d(qbuf + PT_BLK_BYTES, &tmQ, &sh.qfull, 64, h, q0 + qi0, 0, 0);
+      bool ok = true;
+      auto load = [&](int t, const CUtensorMap* tm, int j) -> bool {
+        const int s = t % PT_NRING, k = t / PT_NRING;
+        if (!mbar_wait<true>(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 501)) return false;
+        unsigned char* dst = ring + s * PT_TILE_BYTES;
+        int c2, c3;
+        if (p.table) {   // a 128-key tile never straddles a page
+          c2 = (j * 128) % p.BS;
+          c3 = p.table[(int64_t)b * p.NBmax + (j * 128) / p.BS];
+        } else {
+          c2 = k0 + j * 128;
+          c3 = 0;
+        }
+        mbar_arrive_expect_tx(&sh.full[s], PT_TILE_BYTES);
+        tma_load_5d(dst, tm, &sh.full[s], 0, hk, c2, c3, 0);
+        tma_load_5d(dst + PT_BLK_BYTES, tm, &sh.full[s], 64, hk, c2, c3, 0);
+        return true;
+      };
+      for (int j = 0; ok && j < n; ++j) ok = load(j, &tmK, j);
+      for (int j = 0; ok && j < n; ++j) {
+        ok = load(n + 2 * j, &tmK, j);
+        if (ok) ok = load(n + 2 * j + 1, &tmV, j);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      bool ok = mbar_wait<true>(&sh.qfull, 0, abortp, p.error_word, 601);
+      const uint32_t q_addr = smem_u32(qbuf);
+      auto issue_s = [&](int su, int t) -> bool {   // S tile number su (both passes) from ring position t
+        const int s = t % PT_NRING, k = t / PT_NRING, sb = su & 1, use = su >> 1;
+        if (!mbar_wait<true>(&sh.full[s], k & 1, abortp, p.error_word, 602)) return false;
+        if (!mbar_wait<true>(&sh.sempty[sb], (use & 1) ^ 1, abortp, p.error_word, 603)) return false;
+        fence_after_sync();
+        umma_k128(tmem_base + sb * 128, q_addr, PT_BLK_BYTES, smem_u32(ring + s * PT_TILE_BYTES), PT_BLK_BYTES,
+                  IDESC_QK);
+        umma_commit(&sh.sfull[sb]);
+        umma_commit(&sh.empty[s]);
+        return true;
+      };
+      for (int j = 0; ok && j < n; ++j) ok = issue_s(j, j);
+      if (ok) ok = issue_s(n, n);
+      for (int j = 0; ok && j < n; ++j) {
+        if (j + 1 < n) ok = issue_s(n + j + 1, n + 2 * (j + 1));   // S of the next tile first
+        if (!ok) break;
+        const int t = n + 2 * j + 1, s = t % PT_NRING, k = t / PT_NRING, pb = j & 1;
+        if (!mbar_wait<true>(&sh.full[s], k & 1, abortp, p.error_word, 604)) { ok = false; break; }
+        if (!mbar_wait<true>(&sh.pfull[pb], (j >> 1) & 1, abortp, p.error_word, 605)) { ok = false; break; }
+        fence_after_sync();
+        const uint32_t p_addr = smem_u32(pbuf + pb * PT_TILE_BYTES);
+        const uint32_t v_addr = smem_u32(ring + s * PT_TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {   // 16 keys per step
+          const uint64_t ad = smem_desc_sw128(p_addr + (ks >> 2) * PT_BLK_BYTES) + 2u * (ks & 3);
+          const uint64_t bd = smem_desc_sw128_mn(v_addr + ks * 2048, PT_BLK_BYTES, 1024);
+          umma_f16(tmem_base + 256, ad, bd, IDESC_PV, (j | ks) ? 1u : 0u);
+        }
+        umma_commit(&sh.pempty[pb]);
+        umma_commit(&sh.empty[s]);
+      }
+      if (ok) umma_commit(&sh.ofull);
+    }
+  } else {
+    // ---------------- softmax ----------------
+    const int q = warp & 3;               // TMEM lane quadrant
+    const int ch = (warp - 2) >> 2;       // column half
+    const int r = q * 32 + lane;          // query row of the tile
+    const int lim = r < rows ? min(lk - 1, qi0 + r + shift) : -1;   // last visible key (-1: none)
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ch * 64;
+    bool ok = true;
+    uint32_t sph = 0;
+    auto softmax_sync = [&](int where) -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.sbar);
+      const bool ok_ = mbar_wait(&sh.sbar, sph & 1, abortp, p.error_word, where);
+      ++sph;
+      return ok_;
+    };
+    uint32_t ra[32], rb[32];
+    // ---- pass 1: row maxima of the raw products ----
+    float rmax = -INFINITY;
+    for (int j = 0; ok && j < n; ++j) {
+      const int sb = j & 1, use = j >> 1;
+      if (!mbar_wait(&sh.sfull[sb], use & 1, abortp, p.error_word, 701)) { ok = false; break; }
+      fence_after_sync();
+      tmem_ld32_issue(lane_base + sb * 128, ra);
+      tmem_ld32_issue(lane_base + sb * 128 + 32, rb);
+      tmem_ld32_wait(ra);
+      tmem_ld32_wait(rb);
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.sempty[sb]);
+      const int key0 = j * 128 + ch * 64;
+      if (key0 + 63 <= lim) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          rmax = fmax3(rmax, __uint_as_float(ra[i]), __uint_as_float(ra[i + 1]));
+          rmax = fmax3(rmax, __uint_as_float(rb[i]), __uint_as_float(rb[i + 1]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (key0 + i <= lim) rmax = fmaxf(rmax, __uint_as_float(ra[i]));
+          if (key0 + 32 + i <= lim) rmax = fmaxf(rmax, __uint_as_float(rb[i]));
+        }
+      }
+    }
+    if (ok) {
+      sh.stat[ch][r] = rmax;
+      ok = softmax_sync(711);
+      if (ok) {
+        rmax = fmaxf(sh.stat[0][r], sh.stat[1][r]);
+        ok = softmax_sync(712);   // both halves have read before `stat` is reused
+      }
+    }
+    const float m_s = rmax == -INFINITY ? 0.f : rmax * p.scale_log2e;
+    // ---- pass 2: P = exp2(S * scale_log2e - max), row sums, P to shared memory ----
+    float l = 0.f;
+    for (int j = 0; ok && j < n; ++j) {
+      const int su = n + j, sb = su & 1, use = su >> 1, pb = j & 1;
+      if (!mbar_wait(&sh.sfull[sb], use & 1, abortp, p.error_word, 702)) { ok = false; break; }
+      fence_after_sync();
+      tmem_ld32_issue(lane_base + sb * 128, ra);
+      tmem_ld32_issue(lane_base + sb * 128 + 32, rb);
+      tmem_ld32_wait(ra);
+      tmem_ld32_wait(rb);
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.sempty[sb]);
+      const int key0 = j * 128 + ch * 64;
+      const bool full_vis = key0 + 63 <= lim;
+      uint32_t pk[32];   // 64 values of P, packed in pairs
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float a0 = ex2f(fmaf(__uint_as_float(ra[i]), p.scale_log2e, -m_s));
+        float a1 = ex2f(fmaf(__uint_as_float(ra[i + 1]), p.scale_log2e, -m_s));
+        float b0 = ex2f(fmaf(__uint_as_float(rb[i]), p.scale_log2e, -m_s));
+        float b1 = ex2f(fmaf(__uint_as_float(rb[i + 1]), p.scale_log2e, -m_s));
+        if (!full_vis) {
+          if (key0 + i > lim) a0 = 0.f;
+          if (key0 + i + 1 > lim) a1 = 0.f;
+          if (key0 + 32 + i > lim) b0 = 0.f;
+          if (key0 + 32 + i + 1 > lim) b1 = 0.f;
+        }
+        l += (a0 + a1) + (b0 + b1);
+        const typename Pair<T>::V pa = Pair<T>::pack(a0, a1), pq = Pair<T>::pack(b0, b1);
+        pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&pa);
+        pk[16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&pq);
+      }
+      // the V tile's rows past the end of the sequence become zeros (0 * garbage could be NaN)
+      if ((j + 1) * 128 > lk) {
+        const int t = n + 2 * j + 1, s = t % PT_NRING, k = t / PT_NRING;
+        if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 703)) { ok = false; break; }
+        unsigned char* vt = ring + s * PT_TILE_BYTES;
+        const int first = lk - j * 128;   // first row to clear
+        // 256 threads: row (first + i), 16-byte chunk c of both blocks
+        for (int idx = threadIdx.x - 64; idx < (128 - first) * 16; idx += 256) {
+          const int row = first + (idx >> 4), c = idx & 15;
+          *reinterpret_cast<int4*>(vt + (c >> 3) * PT_BLK_BYTES + row * 128 + ((c & 7) << 4)) = make_int4(0, 0, 0, 0);
+        }
+      }
+      if (!mbar_wait(&sh.pempty[pb], ((j >> 1) & 1) ^ 1, abortp, p.error_word, 704)) { ok = false; break; }
+      {
+        unsigned char* prow = pbuf + pb * PT_TILE_BYTES + ch * PT_BLK_BYTES + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)   // 8 keys (16 bytes) per chunk
+          *reinterpret_cast<int4*>(prow + ((c ^ (r & 7)) << 4)) =
+              make_int4((int)pk[4 * c], (int)pk[4 * c + 1], (int)pk[4 * c + 2], (int)pk[4 * c + 3]);
+      }
+      fence_proxy_async();   // shared-memory writes of this thread -> visible to the tensor core's reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.pfull[pb]);
+    }
+    // ---- output ----
+    if (ok) {
+      sh.stat[ch][r] = l;
+      ok = softmax_sync(713);
+      if (ok) {
+        l = sh.stat[0][r] + sh.stat[1][r];
+        ok = mbar_wait(&sh.ofull, 0, abortp, p.error_word, 705);
+      }
+    }
+    if (ok) {
+      fence_after_sync();
+      const uint32_t obase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + 256 + ch * 64;
+      tmem_ld32_issue(obase, ra);
+      tmem_ld32_issue(obase + 32, rb);
+      tmem_ld32_wait(ra);
+      tmem_ld32_wait(rb);
+      if (r < rows) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        T* o = reinterpret_cast<T*>(p.out) + ((int64_t)(q0 + qi0 + r) * p.Hq + h) * 128 + ch * 64;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t w0[4], w1[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const typename Pair<T>::V x = Pair<T>::pack(__uint_as_float(ra[8 * c + 2 * i]) * inv,
+                                                        __uint_as_float(ra[8 * c + 2 * i + 1]) * inv);
+            const typename Pair<T>::V y = Pair<T>::pack(__uint_as_float(rb[8 * c + 2 * i]) * inv,
+                                                        __uint_as_float(rb[8 * c + 2 * i + 1]) * inv);
+            w0[i] = *reinterpret_cast<const uint32_t*>(&x);
+            w1[i] = *reinterpret_cast<const uint32_t*>(&y);
+          }
+          *reinterpret_cast<int4*>(o + 8 * c) = make_int4((int)w0[0], (int)w0[1], (int)w0[2], (int)w0[3]);
+          *reinterpret_cast<int4*>(o + 32 + 8 * c) = make_int4((int)w1[0], (int)w1[1], (int)w1[2], (int)w1[3]);
+        }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <typename T>
+static int launch_prefill_tc(const void* q, const void* k, const void* v, const PtParams& p,
+                             int max_seqlen_q, int64_t kv_stride_page, cudaStream_t st) {
+  CUtensorMap tmQ, tmK, tmV;
+  const uint32_t box[5] = {64, 1, 128, 1, 1};
+  {
+    const uint64_t dims[5] = {128, (uint64_t)p.Hq, (uint64_t)p.total_q, 1, 1};
+    const uint64_t strides[4] = {128, (uint64_t)p.Hq * 128, (uint64_t)p.Hq * 128, (uint64_t)p.Hq * 128};
+    int rc = make_tensor_map_5d(&tmQ, UmmaFmt<T>::tm, q, dims, strides, box, sizeof(T));
+    if (rc) return rc;
+  }
+  for (int which = 0; which < 2; ++which) {
+    const void* base = which ? v : k;
+    CUtensorMap* tm = which ? &tmV : &tmK;
+    int rc;
+    if (p.table) {
+      const uint64_t dims[5] = {128, (uint64_t)p.Hkv, (uint64_t)p.BS, 1ull << 30, 1};
+      const uint64_t strides[4] = {128, (uint64_t)p.Hkv * 128, (uint64_t)kv_stride_page, (uint64_t)kv_stride_page};
+      rc = make_tensor_map_5d(tm, UmmaFmt<T>::tm, base, dims, strides, box, sizeof(T));
+    } else {
+      const uint64_t dims[5] = {128, (uint64_t)p.Hkv, (uint64_t)p.total_k, 1, 1};
+      const uint64_t strides[4] = {128, (uint64_t)p.Hkv * 128, (uint64_t)p.Hkv * 128, (uint64_t)p.Hkv * 128};
+      rc = make_tensor_map_5d(tm, UmmaFmt<T>::tm, base, dims, strides, box, sizeof(T));
+    }
+    if (rc) return rc;
+  }
+  const size_t smem = (1 + PT_NRING + 2) * PT_TILE_BYTES + sizeof(PtShared) + 1024;
+  auto kern = prefill_tc_kernel<T>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { set_error("zp_varlen_prefill(tcgen05): %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
+  dim3 grid((max_seqlen_q + 127) / 128, p.Hq, p.B);
+  kern<<<grid, PT_THREADS, smem, st>>>(tmQ, tmK, tmV, p);
+  return check_launch("zp_varlen_prefill(tcgen05)");
+}
+
+// Called by zp_varlen_prefill_ex (zp_prefill.cu).
+// total_q / total_k: rows of q and (dense case) of k and v.
+int varlen_prefill_tc(const void* q, const void* k, const void* v, const int32_t* cu_q, const int32_t* cu_k,
+                      const int32_t* table, void* out, int B, int max_seqlen_q, int NBmax, int Hq, int Hkv,
+                      int BS, int64_t kv_stride_page, float scale_log2e, int total_q, int total_k, int dtype,
+                      cudaStream_t st) {
+  PtParams p{};
+  p.total_q = total_q; p.total_k = total_k;
+  p.cu_q = cu_q; p.cu_k = cu_k; p.table = table; p.out = out;
+  p.error_word = device_error_word();
+  p.B = B; p.NBmax = NBmax; p.Hq = Hq; p.Hkv = Hkv; p.BS = BS; p.scale_log2e = scale_log2e;
+  if (!p.error_word) { set_error("zp_varlen_prefill(tcgen05): no device error word"); return ZP_ERR_CUDA; }
+  if (dtype == ZP_DTYPE_BF16)
+    return launch_prefill_tc<__nv_bfloat16>(q, k, v, p, max_seqlen_q, kv_stride_page, st);
+  if (dtype == ZP_DTYPE_F16)
+    return launch_prefill_tc<__half>(q, k, v, p, max_seqlen_q, kv_stride_page, st);
+  set_error("zp_varlen_prefill(tcgen05): 16-bit tensors only");
+  return ZP_ERR_UNSUPPORTED;
+}
+
+}  // namespace zp

@@ -47,7 +47,7 @@ def paged_decode_attention(q, k_cache, v_cache, cache_seqlens, block_table, soft
 
 
 def varlen_prefill_attention(q, k, v, max_seqlen_q, cu_seqlens_q, max_seqlen_k, cu_seqlens_k,
-                             softmax_scale=None, block_table=None):
+                             softmax_scale=None, block_table=None, impl="auto"):
     """Replaces flash_attn_varlen_func(..., causal=True, block_table=...) as called at
     zipage/layers/attention.py:82-93.  q [sum_q,Hq,D]; k,v dense [sum_k,Hkv,D] or, with
     block_table, the paged caches [P,BS,Hkv,D]."""
@@ -66,10 +66,12 @@ def varlen_prefill_attention(q, k, v, max_seqlen_q, cu_seqlens_q, max_seqlen_k, 
         stride_page, nbmax = k.stride(0), block_table.shape[1]
     out = torch.empty_like(q)
     B = cu_seqlens_q.numel() - 1
-    L.check(L.load().zp_varlen_prefill(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(cu_seqlens_q),
-                                       L.ptr(cu_seqlens_k), L.ptr(block_table), L.ptr(out), B,
-                                       int(max_seqlen_q), nbmax, Hq, Hkv, D, BS, stride_page,
-                                       float(softmax_scale), L.dtype_code(q), L.stream_ptr()),
+    total_k = 0 if block_table is not None else k.shape[0]
+    L.check(L.load().zp_varlen_prefill_ex(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(cu_seqlens_q),
+                                          L.ptr(cu_seqlens_k), L.ptr(block_table), L.ptr(out), B,
+                                          int(max_seqlen_q), nbmax, Hq, Hkv, D, BS, stride_page,
+                                          float(softmax_scale), q.shape[0], total_k, L.IMPL[impl],
+                                          L.dtype_code(q), L.stream_ptr()),
             "varlen_prefill_attention")
     return out
 
