@@ -46,9 +46,10 @@ def parse_args():
     ap.add_argument("--kernel-impl", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--also-exact", action="store_true", help="time the exact variant as well")
-    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops"],
+    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops", "prefill"],
                     help="compress (default, the headline op), decode (paged decode attention kernel) or "
-                         "step_ops (the element-wise ops of a decoder layer step and the sampler)")
+                         "step_ops (the element-wise ops of a decoder layer step and the sampler) or "
+                         "prefill (varlen causal prefill attention, one layer)")
     ap.add_argument("--tokens", type=int, default=32768, help="tokens per call of the step_ops workload")
     return ap.parse_args()
 
@@ -308,10 +309,67 @@ def run_step_ops(args):
     }))
 
 
+def run_prefill(args):
+    """Varlen causal prefill attention of one layer at Qwen3-8B head shapes (32 query / 8 KV heads of
+    128, bf16): 4 sequences of 4096 tokens and one of 16 384 (config 5 sizes), dense K/V.  Reported
+    as causal attention flops per second, 4 * D * sum(len^2) / 2 per query head, for the tcgen05
+    kernel, with the mma.sync kernel timed beside it."""
+    import torch
+    from zipage_b200.layers.attention import varlen_prefill_attention
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    peaks = {}
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        peaks = json.loads(pk.read_text())
+    peak = peaks.get("bf16_tflops", 1590.0)
+    res = {}
+    launches = 0
+    with ClockSampler(dev.index or 0) as clocks:
+        for S, B in [(4096, 4), (16384, 1)]:
+            q = torch.randn(B * S, HQ, D, device=dev, dtype=torch.bfloat16)
+            k = torch.randn(B * S, HKV, D, device=dev, dtype=torch.bfloat16)
+            v = torch.randn(B * S, HKV, D, device=dev, dtype=torch.bfloat16)
+            cu = torch.arange(0, (B + 1) * S, S, device=dev, dtype=torch.int32)
+            flops = 4.0 * D * (S * S / 2.0) * HQ * B
+            for impl in ("tcgen05", "simt"):
+                fn = lambda: varlen_prefill_attention(q, k, v, S, cu, S, cu, impl=impl)
+                for _ in range(args.warmup):
+                    fn()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(args.steps):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / args.steps
+                res[f"{B}x{S} {'tcgen05' if impl == 'tcgen05' else 'mma.sync'}"] = {
+                    "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12}
+                launches += args.steps if impl == "tcgen05" else 0
+    head = res["1x16384 tcgen05"]
+    print(json.dumps({
+        "metric": "prefill_attention_tflops", "value": head["tflops"], "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": head["ms"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "varlen causal prefill attention, one layer, 32 q / 8 kv heads of 128, 1 x 16384 tokens "
+                               "(headline) and 4 x 4096 tokens", "l2": "q, k, v and out of a call: 168 MB > 126 MB L2"},
+        "cases": res, "gpu_launches": launches, "clocks": clocks.summary(),
+        "roofline": {"bound": "tensor", "kernel": "prefill_tc_kernel", "achieved": head["tflops"], "peak": peak,
+                     "unit": "TFLOP/s", "frac": head["tflops"] / peak,
+                     "executed": head["tflops"] * 1.5,
+                     "executed_note": "the kernel recomputes Q.K^T in its second pass: 3 tile products per 2 counted",
+                     "peak_source": "measured burst cuBLAS bf16 (MEASURED_PEAKS.json)" if peaks else "fallback",
+                     "traffic": None},
+    }))
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload == "prefill":
+        return run_prefill(args)
     if args.workload == "decode":
         return run_decode(args)
     if args.workload == "step_ops":

@@ -221,3 +221,71 @@ def test_async_compress_overlaps_decode_on_another_stream():
     assert torch.equal(w_par.kv_cache, w_seq.kv_cache)
     for a, b in zip(got, ref):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_varlen_prefill_tcgen05_matches_mma_and_oracle(dtype):
+    """The tcgen05 kernel against the mma.sync kernel and the oracle: dense with ragged lengths
+    around the 128-key tile, and paged with a cached prefix (fewer queries than keys), whose last
+    page holds NaN beyond the context (the kernel must not let masked keys leak into the output)."""
+    from oracle import zipage_oracle as O
+    from zipage_b200 import _lib
+    from zipage_b200.layers.attention import varlen_prefill_attention
+    dev = torch.device("cuda:0")
+    Hq, Hkv, D = 8, 2, 128
+    g = torch.Generator().manual_seed(23)
+    lens = [700, 127, 128, 129, 1, 385, 256]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    tot = int(cu[-1])
+    q = torch.randn(tot, Hq, D, generator=g).to(dtype)
+    k = torch.randn(tot, Hkv, D, generator=g).to(dtype)
+    v = torch.randn(tot, Hkv, D, generator=g).to(dtype)
+    ref = O.varlen_prefill_attention(q, k, v, cu, cu).float()
+    outs = {}
+    for impl in ("simt", "tcgen05"):
+        outs[impl] = varlen_prefill_attention(q.to(dev), k.to(dev), v.to(dev), max(lens), cu.to(dev), max(lens),
+                                              cu.to(dev), impl=impl).float().cpu()
+        assert (outs[impl] - ref).abs().max() <= 2e-2 * ref.abs().max(), impl
+    assert (outs["simt"] - outs["tcgen05"]).abs().max() <= 1e-2 * ref.abs().max()
+    # paged, prefix cached: queries are the last lq tokens of each sequence
+    lens_k = [300, 1, 640, 517, 256]
+    lens_q = [44, 1, 300, 5, 256]
+    cuk = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32)
+    cuq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    P = sum((n + BS - 1) // BS for n in lens_k) + 2
+    kc = torch.randn(P, BS, Hkv, D, generator=g).to(dtype)
+    vc = torch.randn(P, BS, Hkv, D, generator=g).to(dtype)
+    table = torch.full((len(lens_k), 3), -1, dtype=torch.int32)
+    perm = torch.randperm(P, generator=g)
+    pos = 0
+    for b, lk in enumerate(lens_k):
+        npg = (lk + BS - 1) // BS
+        table[b, :npg] = perm[pos:pos + npg].to(torch.int32)
+        pos += npg
+    q2 = torch.randn(int(cuq[-1]), Hq, D, generator=g).to(dtype)
+    ref2 = O.varlen_prefill_attention(q2, kc, vc, cuq, cuk, block_table=table).float()
+    kd, vd = kc.to(dev), vc.to(dev)
+    for b, lk in enumerate(lens_k):          # poison everything past the context in the last page
+        if lk % BS:
+            page = int(table[b, (lk - 1) // BS])
+            kd[page, lk % BS:] = float("nan")
+            vd[page, lk % BS:] = float("nan")
+    for impl in ("simt", "tcgen05"):
+        out2 = varlen_prefill_attention(q2.to(dev), kd, vd, max(lens_q), cuq.to(dev), max(lens_k), cuk.to(dev),
+                                        block_table=table.to(dev), impl=impl).float().cpu()
+        assert torch.isfinite(out2).all(), impl
+        assert (out2 - ref2).abs().max() <= 2e-2 * ref2.abs().max(), impl
+    torch.cuda.synchronize()
+    assert _lib.device_error() == 0
+
+
+def test_varlen_prefill_tcgen05_is_refused_where_it_cannot_run():
+    from zipage_b200 import _lib
+    from zipage_b200.layers.attention import varlen_prefill_attention
+    dev = torch.device("cuda:0")
+    cu = torch.tensor([0, 5], dtype=torch.int32, device=dev)
+    q = torch.randn(5, 4, 128, device=dev)                      # fp32
+    with pytest.raises(_lib.ZipageError):
+        varlen_prefill_attention(q, q[:, :2].contiguous(), q[:, :2].contiguous(), 5, cu, 5, cu, impl="tcgen05")
+    out = varlen_prefill_attention(q, q[:, :2].contiguous(), q[:, :2].contiguous(), 5, cu, 5, cu)   # auto: fp32 kernel
+    assert torch.isfinite(out).all()

@@ -11,8 +11,8 @@
 // and out = O / row sum.  Recomputing S costs half as many tensor-core flops again but needs no
 // rescaling of the output accumulator when a row maximum grows, so O never leaves TMEM and the
 // softmax warps only stream S.
-// Roles (320 threads, one block per SM): warp 0 = TMA producer and TMEM owner, warp 1 = MMA
-// issuer, warps 2-9 = softmax (thread <-> TMEM lane <-> query row; the two warps of a lane
+// Roles (576 threads, one block per SM): warp 0 = TMA producer and TMEM owner, warp 1 = MMA
+// issuer, warps 2-17 = softmax (thread <-> TMEM lane <-> query row; the four warps of a lane
 // quadrant split a tile's 128 columns).  Shared memory: the Q tile, a ring of four 32 KB K/V
 // stages, two P tiles; TMEM: two S accumulators and O (384 of 512 columns).
 // Keys past the end of a sequence: their S columns are masked by index; in the V tile their rows
@@ -23,10 +23,11 @@ namespace zp {
 
 using namespace tc;
 
-constexpr int PT_THREADS = 320;
+constexpr int PT_THREADS = 576;
 constexpr int PT_TILE_BYTES = 32768;   // 128 rows x 128 elements x 2 bytes
 constexpr int PT_BLK_BYTES = 16384;    // one 64-element block of a tile
 constexpr int PT_NRING = 4;
+constexpr int PT_SLACK = 128;          // alignment padding the launch provides for
 
 struct PtParams {
   const int32_t* cu_q; const int32_t* cu_k; const int32_t* table;
@@ -39,7 +40,7 @@ struct PtParams {
 
 struct __align__(16) PtShared {
   uint64_t qfull, full[PT_NRING], empty[PT_NRING], sfull[2], sempty[2], pfull[2], pempty[2], ofull, sbar;
-  float stat[2][128];   // row statistics exchanged between the two column halves
+  float stat[4][128];   // row statistics exchanged between the four column quarters
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -79,8 +80,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const int kmax = min(lk, qi0 + rows + shift); // keys any row of the tile can see
   const int n = kmax > 0 ? (kmax + 127) >> 7 : 0;
 
-  extern __shared__ unsigned char smem_raw[];
+  // The tiles need 1024-byte alignment and all but ~2 KB of the SM's shared memory, so there is no
+  // room for a full kilobyte of alignment slack: the declaration asks for the alignment, and a base
+  // that is not aligned after all (more than PT_SLACK bytes of padding) is reported, not used.
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* bufs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if (bufs - smem_raw > PT_SLACK) {
+    if (threadIdx.x == 0) atomicCAS(p.error_word, 0, 500);
+    return;
+  }
   unsigned char* qbuf = bufs;
   unsigned char* ring = bufs + PT_TILE_BYTES;
   unsigned char* pbuf = ring + PT_NRING * PT_TILE_BYTES;
@@ -89,11 +97,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
   if (n == 0) {   // nothing visible: zeros
     if (warp >= 2) {
-      const int t = threadIdx.x - 64;           // 256 threads: row t >> 1, half t & 1
-      const int r = t >> 1;
+      const int t = threadIdx.x - 64;           // 512 threads: row t >> 2, quarter t & 3
+      const int r = t >> 2;
       if (r < rows) {
-        T* o = reinterpret_cast<T*>(p.out) + ((int64_t)(q0 + qi0 + r) * p.Hq + h) * 128 + (t & 1) * 64;
-        for (int i = 0; i < 64; i += 8) *reinterpret_cast<int4*>(o + i) = make_int4(0, 0, 0, 0);
+        T* o = reinterpret_cast<T*>(p.out) + ((int64_t)(q0 + qi0 + r) * p.Hq + h) * 128 + (t & 3) * 32;
+        for (int i = 0; i < 32; i += 8) *reinterpret_cast<int4*>(o + i) = make_int4(0, 0, 0, 0);
       }
     }
     return;
@@ -103,11 +111,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     mbar_init(&sh.qfull, 1);
     for (int i = 0; i < PT_NRING; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&sh.sfull[i], 1); mbar_init(&sh.sempty[i], 8);
-      mbar_init(&sh.pfull[i], 8); mbar_init(&sh.pempty[i], 1);
+      mbar_init(&sh.sfull[i], 1); mbar_init(&sh.sempty[i], 16);
+      mbar_init(&sh.pfull[i], 16); mbar_init(&sh.pempty[i], 1);
     }
     mbar_init(&sh.ofull, 1);
-    mbar_init(&sh.sbar, 8);   // the eight softmax warps (a bounded wait, unlike bar.sync)
+    mbar_init(&sh.sbar, 16);  // the sixteen softmax warps (a bounded wait, unlike bar.sync)
     sh.abort_flag = 0;
     fence_mbar_init();
   }
@@ -160,12 +168,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      bool ok = mbar_wait<true>(&sh.qfull, 0, abortp, p.error_word, 601);
+      bool ok = mbar_wait(&sh.qfull, 0, abortp, p.error_word, 601);
       const uint32_t q_addr = smem_u32(qbuf);
       auto issue_s = [&](int su, int t) -> bool {   // S tile number su (both passes) from ring position t
         const int s = t % PT_NRING, k = t / PT_NRING, sb = su & 1, use = su >> 1;
-        if (!mbar_wait<true>(&sh.full[s], k & 1, abortp, p.error_word, 602)) return false;
-        if (!mbar_wait<true>(&sh.sempty[sb], (use & 1) ^ 1, abortp, p.error_word, 603)) return false;
+        if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 602)) return false;
+        if (!mbar_wait(&sh.sempty[sb], (use & 1) ^ 1, abortp, p.error_word, 603)) return false;
         fence_after_sync();
         umma_k128(tmem_base + sb * 128, q_addr, PT_BLK_BYTES, smem_u32(ring + s * PT_TILE_BYTES), PT_BLK_BYTES,
                   IDESC_QK);
@@ -179,8 +187,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (j + 1 < n) ok = issue_s(n + j + 1, n + 2 * (j + 1));   // S of the next tile first
         if (!ok) break;
         const int t = n + 2 * j + 1, s = t % PT_NRING, k = t / PT_NRING, pb = j & 1;
-        if (!mbar_wait<true>(&sh.full[s], k & 1, abortp, p.error_word, 604)) { ok = false; break; }
-        if (!mbar_wait<true>(&sh.pfull[pb], (j >> 1) & 1, abortp, p.error_word, 605)) { ok = false; break; }
+        if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 604)) { ok = false; break; }
+        if (!mbar_wait(&sh.pfull[pb], (j >> 1) & 1, abortp, p.error_word, 605)) { ok = false; break; }
         fence_after_sync();
         const uint32_t p_addr = smem_u32(pbuf + pb * PT_TILE_BYTES);
         const uint32_t v_addr = smem_u32(ring + s * PT_TILE_BYTES);
@@ -198,10 +206,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   } else {
     // ---------------- softmax ----------------
     const int q = warp & 3;               // TMEM lane quadrant
-    const int ch = (warp - 2) >> 2;       // column half
+    const int cq = (warp - 2) >> 2;       // column quarter: keys / dims cq*32 .. +31 of a tile
     const int r = q * 32 + lane;          // query row of the tile
     const int lim = r < rows ? min(lk - 1, qi0 + r + shift) : -1;   // last visible key (-1: none)
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ch * 64;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + cq * 32;
     bool ok = true;
     uint32_t sph = 0;
     auto softmax_sync = [&](int where) -> bool {
@@ -211,7 +219,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       ++sph;
       return ok_;
     };
-    uint32_t ra[32], rb[32];
+    uint32_t ra[32];
     // ---- pass 1: row maxima of the raw products ----
     float rmax = -INFINITY;
     for (int j = 0; ok && j < n; ++j) {
@@ -219,68 +227,64 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       if (!mbar_wait(&sh.sfull[sb], use & 1, abortp, p.error_word, 701)) { ok = false; break; }
       fence_after_sync();
       tmem_ld32_issue(lane_base + sb * 128, ra);
-      tmem_ld32_issue(lane_base + sb * 128 + 32, rb);
       tmem_ld32_wait(ra);
-      tmem_ld32_wait(rb);
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh.sempty[sb]);
-      const int key0 = j * 128 + ch * 64;
-      if (key0 + 63 <= lim) {
+      const int key0 = j * 128 + cq * 32;
+      if (key0 + 31 <= lim) {
+        float m0 = rmax, m1 = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          rmax = fmax3(rmax, __uint_as_float(ra[i]), __uint_as_float(ra[i + 1]));
-          rmax = fmax3(rmax, __uint_as_float(rb[i]), __uint_as_float(rb[i + 1]));
+        for (int i = 0; i < 32; i += 4) {
+          m0 = fmax3(m0, __uint_as_float(ra[i]), __uint_as_float(ra[i + 1]));
+          m1 = fmax3(m1, __uint_as_float(ra[i + 2]), __uint_as_float(ra[i + 3]));
         }
+        rmax = fmaxf(m0, m1);
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < 32; ++i)
           if (key0 + i <= lim) rmax = fmaxf(rmax, __uint_as_float(ra[i]));
-          if (key0 + 32 + i <= lim) rmax = fmaxf(rmax, __uint_as_float(rb[i]));
-        }
       }
     }
     if (ok) {
-      sh.stat[ch][r] = rmax;
+      sh.stat[cq][r] = rmax;
       ok = softmax_sync(711);
       if (ok) {
-        rmax = fmaxf(sh.stat[0][r], sh.stat[1][r]);
-        ok = softmax_sync(712);   // both halves have read before `stat` is reused
+        rmax = fmaxf(fmaxf(sh.stat[0][r], sh.stat[1][r]), fmaxf(sh.stat[2][r], sh.stat[3][r]));
+        ok = softmax_sync(712);   // everyone has read before `stat` is reused
       }
     }
     const float m_s = rmax == -INFINITY ? 0.f : rmax * p.scale_log2e;
     // ---- pass 2: P = exp2(S * scale_log2e - max), row sums, P to shared memory ----
-    float l = 0.f;
+    float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
     for (int j = 0; ok && j < n; ++j) {
       const int su = n + j, sb = su & 1, use = su >> 1, pb = j & 1;
       if (!mbar_wait(&sh.sfull[sb], use & 1, abortp, p.error_word, 702)) { ok = false; break; }
       fence_after_sync();
       tmem_ld32_issue(lane_base + sb * 128, ra);
-      tmem_ld32_issue(lane_base + sb * 128 + 32, rb);
       tmem_ld32_wait(ra);
-      tmem_ld32_wait(rb);
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh.sempty[sb]);
-      const int key0 = j * 128 + ch * 64;
-      const bool full_vis = key0 + 63 <= lim;
-      uint32_t pk[32];   // 64 values of P, packed in pairs
+      const int key0 = j * 128 + cq * 32;
+      const bool full_vis = key0 + 31 <= lim;
+      uint32_t pk[16];   // 32 values of P, packed in pairs
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
+      for (int i = 0; i < 32; i += 4) {
         float a0 = ex2f(fmaf(__uint_as_float(ra[i]), p.scale_log2e, -m_s));
         float a1 = ex2f(fmaf(__uint_as_float(ra[i + 1]), p.scale_log2e, -m_s));
-        float b0 = ex2f(fmaf(__uint_as_float(rb[i]), p.scale_log2e, -m_s));
-        float b1 = ex2f(fmaf(__uint_as_float(rb[i + 1]), p.scale_log2e, -m_s));
+        float a2 = ex2f(fmaf(__uint_as_float(ra[i + 2]), p.scale_log2e, -m_s));
+        float a3 = ex2f(fmaf(__uint_as_float(ra[i + 3]), p.scale_log2e, -m_s));
         if (!full_vis) {
           if (key0 + i > lim) a0 = 0.f;
           if (key0 + i + 1 > lim) a1 = 0.f;
-          if (key0 + 32 + i > lim) b0 = 0.f;
-          if (key0 + 32 + i + 1 > lim) b1 = 0.f;
+          if (key0 + i + 2 > lim) a2 = 0.f;
+          if (key0 + i + 3 > lim) a3 = 0.f;
         }
-        l += (a0 + a1) + (b0 + b1);
-        const typename Pair<T>::V pa = Pair<T>::pack(a0, a1), pq = Pair<T>::pack(b0, b1);
+        l0 += a0; l1 += a1; l2 += a2; l3 += a3;
+        const typename Pair<T>::V pa = Pair<T>::pack(a0, a1), pq = Pair<T>::pack(a2, a3);
         pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&pa);
-        pk[16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&pq);
+        pk[(i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&pq);
       }
       // the V tile's rows past the end of the sequence become zeros (0 * garbage could be NaN)
       if ((j + 1) * 128 > lk) {
@@ -288,18 +292,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 703)) { ok = false; break; }
         unsigned char* vt = ring + s * PT_TILE_BYTES;
         const int first = lk - j * 128;   // first row to clear
-        // 256 threads: row (first + i), 16-byte chunk c of both blocks
-        for (int idx = threadIdx.x - 64; idx < (128 - first) * 16; idx += 256) {
+        // 512 threads: row (first + i), 16-byte chunk c of both blocks
+        for (int idx = threadIdx.x - 64; idx < (128 - first) * 16; idx += 512) {
           const int row = first + (idx >> 4), c = idx & 15;
           *reinterpret_cast<int4*>(vt + (c >> 3) * PT_BLK_BYTES + row * 128 + ((c & 7) << 4)) = make_int4(0, 0, 0, 0);
         }
       }
       if (!mbar_wait(&sh.pempty[pb], ((j >> 1) & 1) ^ 1, abortp, p.error_word, 704)) { ok = false; break; }
       {
-        unsigned char* prow = pbuf + pb * PT_TILE_BYTES + ch * PT_BLK_BYTES + r * 128;
+        // keys cq*32 .. +31 of the row: block cq / 2, 16-byte chunks (cq % 2) * 4 .. +3
+        unsigned char* prow = pbuf + pb * PT_TILE_BYTES + (cq >> 1) * PT_BLK_BYTES + r * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c)   // 8 keys (16 bytes) per chunk
-          *reinterpret_cast<int4*>(prow + ((c ^ (r & 7)) << 4)) =
+        for (int c = 0; c < 4; ++c)
+          *reinterpret_cast<int4*>(prow + ((((cq & 1) * 4 + c) ^ (r & 7)) << 4)) =
               make_int4((int)pk[4 * c], (int)pk[4 * c + 1], (int)pk[4 * c + 2], (int)pk[4 * c + 3]);
       }
       fence_proxy_async();   // shared-memory writes of this thread -> visible to the tensor core's reads
@@ -307,38 +312,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       if (lane == 0) mbar_arrive(&sh.pfull[pb]);
     }
     // ---- output ----
+    float l = (l0 + l1) + (l2 + l3);
     if (ok) {
-      sh.stat[ch][r] = l;
+      sh.stat[cq][r] = l;
       ok = softmax_sync(713);
       if (ok) {
-        l = sh.stat[0][r] + sh.stat[1][r];
+        l = (sh.stat[0][r] + sh.stat[1][r]) + (sh.stat[2][r] + sh.stat[3][r]);
         ok = mbar_wait(&sh.ofull, 0, abortp, p.error_word, 705);
       }
     }
     if (ok) {
       fence_after_sync();
-      const uint32_t obase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + 256 + ch * 64;
-      tmem_ld32_issue(obase, ra);
-      tmem_ld32_issue(obase + 32, rb);
+      tmem_ld32_issue(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + 256 + cq * 32, ra);
       tmem_ld32_wait(ra);
-      tmem_ld32_wait(rb);
       if (r < rows) {
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        T* o = reinterpret_cast<T*>(p.out) + ((int64_t)(q0 + qi0 + r) * p.Hq + h) * 128 + ch * 64;
+        T* o = reinterpret_cast<T*>(p.out) + ((int64_t)(q0 + qi0 + r) * p.Hq + h) * 128 + cq * 32;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint32_t w0[4], w1[4];
+          uint32_t w0[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const typename Pair<T>::V x = Pair<T>::pack(__uint_as_float(ra[8 * c + 2 * i]) * inv,
                                                         __uint_as_float(ra[8 * c + 2 * i + 1]) * inv);
-            const typename Pair<T>::V y = Pair<T>::pack(__uint_as_float(rb[8 * c + 2 * i]) * inv,
-                                                        __uint_as_float(rb[8 * c + 2 * i + 1]) * inv);
             w0[i] = *reinterpret_cast<const uint32_t*>(&x);
-            w1[i] = *reinterpret_cast<const uint32_t*>(&y);
           }
           *reinterpret_cast<int4*>(o + 8 * c) = make_int4((int)w0[0], (int)w0[1], (int)w0[2], (int)w0[3]);
-          *reinterpret_cast<int4*>(o + 32 + 8 * c) = make_int4((int)w1[0], (int)w1[1], (int)w1[2], (int)w1[3]);
         }
       }
     }
@@ -377,7 +376,7 @@ static int launch_prefill_tc(const void* q, const void* k, const void* v, const 
     }
     if (rc) return rc;
   }
-  const size_t smem = (1 + PT_NRING + 2) * PT_TILE_BYTES + sizeof(PtShared) + 1024;
+  const size_t smem = (1 + PT_NRING + 2) * PT_TILE_BYTES + sizeof(PtShared) + PT_SLACK;
   auto kern = prefill_tc_kernel<T>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_error("zp_varlen_prefill(tcgen05): %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
