@@ -5,7 +5,7 @@
 // tile can see, 128 keys at a time:
 //   pass 1:  S = Q K^T (M = 128 queries, N = 128 keys, K = 128 dims)   -> row maxima
 //   pass 2:  S again, P = exp2(S * scale*log2e - max) (masked entries 0), row sums of P in fp32,
-//            P rounded to the tensor dtype and written to shared memory as the A operand of
+//            P rounded to the tensor dtype and stored to TMEM as the A operand of
 //            O += P V (M = 128 queries, N = 128 dims, K = 128 keys; V is the B operand as it lies in
 //            memory: dims contiguous, i.e. MN-major), accumulated in TMEM over all tiles
 // and out = O / row sum.  Recomputing S costs half as many tensor-core flops again but needs no
@@ -13,8 +13,8 @@
 // softmax warps only stream S.
 // Roles (576 threads, one block per SM): warp 0 = TMA producer and TMEM owner, warp 1 = MMA
 // issuer, warps 2-17 = softmax (thread <-> TMEM lane <-> query row; the four warps of a lane
-// quadrant split a tile's 128 columns).  Shared memory: the Q tile, a ring of four 32 KB K/V
-// stages, two P tiles; TMEM: two S accumulators and O (384 of 512 columns).
+// quadrant split a tile's 128 columns).  Shared memory: the Q tile and a ring of five 32 KB K/V
+// stages; TMEM: two S accumulators, O and two P tiles (all 512 columns).
 // Keys past the end of a sequence: their S columns are masked by index; in the V tile their rows
 // are overwritten with zeros before the product (their P is 0, but 0 * garbage may be NaN).
 #include "zp_tc.cuh"
@@ -26,8 +26,8 @@ using namespace tc;
 constexpr int PT_THREADS = 576;
 constexpr int PT_TILE_BYTES = 32768;   // 128 rows x 128 elements x 2 bytes
 constexpr int PT_BLK_BYTES = 16384;    // one 64-element block of a tile
-constexpr int PT_NRING = 4;
-constexpr int PT_SLACK = 128;          // alignment padding the launch provides for
+constexpr int PT_NRING = 5;
+constexpr int PT_PCOL = 384;           // TMEM columns of the two P tiles (64 each), after S0, S1 and O
 
 struct PtParams {
   const int32_t* cu_q; const int32_t* cu_k; const int32_t* table;
@@ -56,6 +56,28 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_addr, uint3
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// A operand taken from TMEM (one row per lane, two 16-bit elements per 32-bit column)
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ float ex2f(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -80,19 +102,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const int kmax = min(lk, qi0 + rows + shift); // keys any row of the tile can see
   const int n = kmax > 0 ? (kmax + 127) >> 7 : 0;
 
-  // The tiles need 1024-byte alignment and all but ~2 KB of the SM's shared memory, so there is no
-  // room for a full kilobyte of alignment slack: the declaration asks for the alignment, and a base
-  // that is not aligned after all (more than PT_SLACK bytes of padding) is reported, not used.
-  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  extern __shared__ unsigned char smem_raw[];
   unsigned char* bufs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  if (bufs - smem_raw > PT_SLACK) {
-    if (threadIdx.x == 0) atomicCAS(p.error_word, 0, 500);
-    return;
-  }
   unsigned char* qbuf = bufs;
   unsigned char* ring = bufs + PT_TILE_BYTES;
-  unsigned char* pbuf = ring + PT_NRING * PT_TILE_BYTES;
-  PtShared& sh = *reinterpret_cast<PtShared*>(pbuf + 2 * PT_TILE_BYTES);
+  PtShared& sh = *reinterpret_cast<PtShared*>(ring + PT_NRING * PT_TILE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (n == 0) {   // nothing visible: zeros
@@ -190,13 +204,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 604)) { ok = false; break; }
         if (!mbar_wait(&sh.pfull[pb], (j >> 1) & 1, abortp, p.error_word, 605)) { ok = false; break; }
         fence_after_sync();
-        const uint32_t p_addr = smem_u32(pbuf + pb * PT_TILE_BYTES);
         const uint32_t v_addr = smem_u32(ring + s * PT_TILE_BYTES);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {   // 16 keys per step
-          const uint64_t ad = smem_desc_sw128(p_addr + (ks >> 2) * PT_BLK_BYTES) + 2u * (ks & 3);
+        for (int ks = 0; ks < 8; ++ks) {   // 16 keys per step: 8 columns of P
           const uint64_t bd = smem_desc_sw128_mn(v_addr + ks * 2048, PT_BLK_BYTES, 1024);
-          umma_f16(tmem_base + 256, ad, bd, IDESC_PV, (j | ks) ? 1u : 0u);
+          umma_f16_ts(tmem_base + 256, tmem_base + PT_PCOL + pb * 64 + ks * 8, bd, IDESC_PV, (j | ks) ? 1u : 0u);
         }
         umma_commit(&sh.pempty[pb]);
         umma_commit(&sh.empty[s]);
@@ -299,15 +311,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
       }
       if (!mbar_wait(&sh.pempty[pb], ((j >> 1) & 1) ^ 1, abortp, p.error_word, 704)) { ok = false; break; }
-      {
-        // keys cq*32 .. +31 of the row: block cq / 2, 16-byte chunks (cq % 2) * 4 .. +3
-        unsigned char* prow = pbuf + pb * PT_TILE_BYTES + (cq >> 1) * PT_BLK_BYTES + r * 128;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          *reinterpret_cast<int4*>(prow + ((((cq & 1) * 4 + c) ^ (r & 7)) << 4)) =
-              make_int4((int)pk[4 * c], (int)pk[4 * c + 1], (int)pk[4 * c + 2], (int)pk[4 * c + 3]);
-      }
-      fence_proxy_async();   // shared-memory writes of this thread -> visible to the tensor core's reads
+      // keys cq*32 .. +31 of the row -> 16 columns of the P tile in TMEM (the A operand of P.V)
+      fence_after_sync();
+      tmem_st16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + PT_PCOL + pb * 64 + cq * 16, pk);
+      tmem_st_wait();
+      if ((j + 1) * 128 > lk) fence_proxy_async();   // the zeros written into the V tile above
+      fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh.pfull[pb]);
     }
@@ -376,7 +385,7 @@ static int launch_prefill_tc(const void* q, const void* k, const void* v, const 
     }
     if (rc) return rc;
   }
-  const size_t smem = (1 + PT_NRING + 2) * PT_TILE_BYTES + sizeof(PtShared) + PT_SLACK;
+  const size_t smem = (1 + PT_NRING) * PT_TILE_BYTES + sizeof(PtShared) + 1024;
   auto kern = prefill_tc_kernel<T>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_error("zp_varlen_prefill(tcgen05): %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
