@@ -289,3 +289,29 @@ def test_varlen_prefill_tcgen05_is_refused_where_it_cannot_run():
         varlen_prefill_attention(q, q[:, :2].contiguous(), q[:, :2].contiguous(), 5, cu, 5, cu, impl="tcgen05")
     out = varlen_prefill_attention(q, q[:, :2].contiguous(), q[:, :2].contiguous(), 5, cu, 5, cu)   # auto: fp32 kernel
     assert torch.isfinite(out).all()
+
+
+def test_varlen_prefill_tcgen05_long_sequences_against_mma():
+    """Config-5 sizes (4 x 4096 and 1 x 16384 tokens, 32 query / 8 KV heads): hundreds of key tiles
+    per block, every ring stage and barrier phase wrapping many times; the mma.sync kernel is the
+    reference at this size.  Also a property of causal attention: the first query attends to one key,
+    so its output is exactly that key's value row."""
+    from zipage_b200 import _lib
+    from zipage_b200.layers.attention import varlen_prefill_attention
+    dev = torch.device("cuda:0")
+    Hq, Hkv, D = 32, 8, 128
+    g = torch.Generator(device=dev).manual_seed(1)
+    for S, B in [(4096, 4), (16384, 1)]:
+        q = torch.randn(B * S, Hq, D, device=dev, dtype=torch.bfloat16, generator=g)
+        k = torch.randn(B * S, Hkv, D, device=dev, dtype=torch.bfloat16, generator=g)
+        v = torch.randn(B * S, Hkv, D, device=dev, dtype=torch.bfloat16, generator=g)
+        cu = torch.arange(0, (B + 1) * S, S, device=dev, dtype=torch.int32)
+        a = varlen_prefill_attention(q, k, v, S, cu, S, cu, impl="tcgen05").float()
+        b = varlen_prefill_attention(q, k, v, S, cu, S, cu, impl="simt").float()
+        torch.cuda.synchronize()
+        assert _lib.device_error() == 0
+        assert torch.isfinite(a).all()
+        assert (a - b).abs().max() <= 1e-2 * b.abs().max()
+        first = torch.arange(B, device=dev) * S
+        want = v[first].float().repeat_interleave(Hq // Hkv, dim=1)   # query head h reads kv head h // G
+        assert torch.equal(a[first], want)
