@@ -315,3 +315,35 @@ def test_varlen_prefill_tcgen05_long_sequences_against_mma():
         first = torch.arange(B, device=dev) * S
         want = v[first].float().repeat_interleave(Hq // Hkv, dim=1)   # query head h reads kv head h // G
         assert torch.equal(a[first], want)
+
+
+def test_varlen_prefill_tcgen05_pages_of_128_keys():
+    """Pages of 128 keys: pass 1 of the tcgen05 kernel falls back to 128-key tiles."""
+    from oracle import zipage_oracle as O
+    from zipage_b200 import _lib
+    from zipage_b200.layers.attention import varlen_prefill_attention
+    dev = torch.device("cuda:0")
+    Hq, Hkv, D, bs = 4, 2, 128, 128
+    g = torch.Generator().manual_seed(31)
+    lens_k = [520, 128, 77, 1000]
+    lens_q = [520, 3, 77, 200]
+    cuk = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32)
+    cuq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    P = sum((n + bs - 1) // bs for n in lens_k) + 1
+    kc = torch.randn(P, bs, Hkv, D, generator=g).to(torch.bfloat16)
+    vc = torch.randn(P, bs, Hkv, D, generator=g).to(torch.bfloat16)
+    width = max((n + bs - 1) // bs for n in lens_k)
+    table = torch.full((len(lens_k), width), -1, dtype=torch.int32)
+    perm = torch.randperm(P, generator=g)
+    pos = 0
+    for b, lk in enumerate(lens_k):
+        npg = (lk + bs - 1) // bs
+        table[b, :npg] = perm[pos:pos + npg].to(torch.int32)
+        pos += npg
+    q = torch.randn(int(cuq[-1]), Hq, D, generator=g).to(torch.bfloat16)
+    ref = O.varlen_prefill_attention(q, kc, vc, cuq, cuk, block_table=table).float()
+    out = varlen_prefill_attention(q.to(dev), kc.to(dev), vc.to(dev), max(lens_q), cuq.to(dev), max(lens_k),
+                                   cuk.to(dev), block_table=table.to(dev), impl="tcgen05").float().cpu()
+    torch.cuda.synchronize()
+    assert _lib.device_error() == 0
+    assert (out - ref).abs().max() <= 2e-2 * ref.abs().max()

@@ -3,7 +3,8 @@
 //
 // One block per (128-query tile, query head, sequence).  Two passes over the key tiles the query
 // tile can see, 128 keys at a time:
-//   pass 1:  S = Q K^T (M = 128 queries, N = 128 keys, K = 128 dims)   -> row maxima
+//   pass 1:  S = Q K^T (M = 128 queries, N = 256 keys where the layout allows, else 128;
+//            K = 128 dims)                                               -> row maxima
 //   pass 2:  S again, P = exp2(S * scale*log2e - max) (masked entries 0), row sums of P in fp32,
 //            P rounded to the tensor dtype and stored to TMEM as the A operand of
 //            O += P V (M = 128 queries, N = 128 dims, K = 128 keys; V is the B operand as it lies in
@@ -13,7 +14,7 @@
 // softmax warps only stream S.
 // Roles (576 threads, one block per SM): warp 0 = TMA producer and TMEM owner, warp 1 = MMA
 // issuer, warps 2-17 = softmax (thread <-> TMEM lane <-> query row; the four warps of a lane
-// quadrant split a tile's 128 columns).  Shared memory: the Q tile and a ring of five 32 KB K/V
+// quadrant split a tile's 128 columns).  Shared memory: the Q tile and a ring of four 32 KB K/V
 // stages; TMEM: two S accumulators, O and two P tiles (all 512 columns).
 // Keys past the end of a sequence: their S columns are masked by index; in the V tile their rows
 // are overwritten with zeros before the product (their P is 0, but 0 * garbage may be NaN).
@@ -26,7 +27,7 @@ using namespace tc;
 constexpr int PT_THREADS = 576;
 constexpr int PT_TILE_BYTES = 32768;   // 128 rows x 128 elements x 2 bytes
 constexpr int PT_BLK_BYTES = 16384;    // one 64-element block of a tile
-constexpr int PT_NRING = 5;
+constexpr int PT_NRING = 4;
 constexpr int PT_PCOL = 384;           // TMEM columns of the two P tiles (64 each), after S0, S1 and O
 
 struct PtParams {
@@ -84,10 +85,13 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
-template <typename T>
+// W1: pass 1 works on 256-key tiles (two adjacent ring stages hold the two 64-dim blocks of 256
+// keys; both halves of TMEM serve as its two S tiles, nothing else lives there yet).
+template <typename T, bool W1>
 __global__ void __launch_bounds__(PT_THREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                  const __grid_constant__ CUtensorMap tmV, const PtParams p) {
+                  const __grid_constant__ CUtensorMap tmK2, const __grid_constant__ CUtensorMap tmV,
+                  const PtParams p) {
   // tile geometry (identical in every role)
   const int b = blockIdx.z, h = blockIdx.y;
   const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
@@ -101,6 +105,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const int rows = min(128, lq - qi0);
   const int kmax = min(lk, qi0 + rows + shift); // keys any row of the tile can see
   const int n = kmax > 0 ? (kmax + 127) >> 7 : 0;
+  const int n1 = W1 ? (n + 1) >> 1 : n;         // tiles of pass 1
+  const int base2 = W1 ? 2 * n1 : n;            // ring position of pass 2's first load
+  // S tile bookkeeping: pass-1 tile jj -> TMEM buffer jj & 1, its (jj >> 1)-th use; pass-2 tile j ->
+  // buffer j & 1, use u1[j & 1] + (j >> 1) with u1[b] = pass-1 uses of buffer b
+  const int u1_0 = (n1 + 1) >> 1, u1_1 = n1 >> 1;
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char* bufs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -144,8 +153,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   volatile int* abortp = &sh.abort_flag;
   constexpr uint32_t IDESC_QK = idesc_f16(UmmaFmt<T>::fmt, 128, 128);
   constexpr uint32_t IDESC_PV = IDESC_QK | (1u << 16);   // B operand MN-major
+  constexpr uint32_t IDESC_QK1 = W1 ? idesc_f16(UmmaFmt<T>::fmt, 128, 256) : IDESC_QK;
 
-  // ring position of a load: pass 1: K_j -> j; pass 2: K_j -> n + 2j, V_j -> n + 2j + 1
+  // ring position of a load: pass 1: K_j -> j (W1: tile jj -> 2jj and 2jj + 1);
+  // pass 2: K_j -> base2 + 2j, V_j -> base2 + 2j + 1
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
@@ -173,10 +184,33 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tma_load_5d(dst + PT_BLK_BYTES, tm, &sh.full[s], 64, hk, c2, c3, 0);
         return true;
       };
-      for (int j = 0; ok && j < n; ++j) ok = load(j, &tmK, j);
+      if (W1) {
+        prefetch_tensormap(&tmK2);
+        for (int jj = 0; ok && jj < n1; ++jj) {
+          const int t = 2 * jj, s = t % PT_NRING, k = t / PT_NRING;   // s is even: stages s and s + 1
+          if (!mbar_wait<true>(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 502) ||
+              !mbar_wait<true>(&sh.empty[s + 1], (k & 1) ^ 1, abortp, p.error_word, 503)) { ok = false; break; }
+          int c2, c3;
+          if (p.table) {   // the page size is a multiple of 256 here
+            c2 = (jj * 256) % p.BS;
+            c3 = p.table[(int64_t)b * p.NBmax + (jj * 256) / p.BS];
+          } else {
+            c2 = k0 + jj * 256;
+            c3 = 0;
+          }
+          // one 64-dim block of the 256 keys per stage, each on its own stage barrier (every stage's
+          // barriers complete exactly once per trip round the ring, in both passes)
+          mbar_arrive_expect_tx(&sh.full[s], PT_TILE_BYTES);
+          tma_load_5d(ring + s * PT_TILE_BYTES, &tmK2, &sh.full[s], 0, hk, c2, c3, 0);
+          mbar_arrive_expect_tx(&sh.full[s + 1], PT_TILE_BYTES);
+          tma_load_5d(ring + (s + 1) * PT_TILE_BYTES, &tmK2, &sh.full[s + 1], 64, hk, c2, c3, 0);
+        }
+      } else {
+        for (int j = 0; ok && j < n; ++j) ok = load(j, &tmK, j);
+      }
       for (int j = 0; ok && j < n; ++j) {
-        ok = load(n + 2 * j, &tmK, j);
-        if (ok) ok = load(n + 2 * j + 1, &tmV, j);
+        ok = load(base2 + 2 * j, &tmK, j);
+        if (ok) ok = load(base2 + 2 * j + 1, &tmV, j);
       }
     }
   } else if (warp == 1) {
@@ -184,23 +218,41 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (lane == 0) {
       bool ok = mbar_wait(&sh.qfull, 0, abortp, p.error_word, 601);
       const uint32_t q_addr = smem_u32(qbuf);
-      auto issue_s = [&](int su, int t) -> bool {   // S tile number su (both passes) from ring position t
-        const int s = t % PT_NRING, k = t / PT_NRING, sb = su & 1, use = su >> 1;
+      // one S tile: TMEM buffer sb (its `use`-th use), key tile at ring position t
+      auto issue_s = [&](int sb, int use, int t, bool wide) -> bool {
+        const int s = t % PT_NRING, k = t / PT_NRING;
         if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 602)) return false;
+        if (wide && !mbar_wait(&sh.full[s + 1], k & 1, abortp, p.error_word, 610)) return false;
         if (!mbar_wait(&sh.sempty[sb], (use & 1) ^ 1, abortp, p.error_word, 603)) return false;
         fence_after_sync();
-        umma_k128(tmem_base + sb * 128, q_addr, PT_BLK_BYTES, smem_u32(ring + s * PT_TILE_BYTES), PT_BLK_BYTES,
-                  IDESC_QK);
-        umma_commit(&sh.sfull[sb]);
-        umma_commit(&sh.empty[s]);
+        if (wide) {
+          umma_k128(tmem_base + sb * 256, q_addr, PT_BLK_BYTES, smem_u32(ring + s * PT_TILE_BYTES), PT_TILE_BYTES,
+                    IDESC_QK1);
+          umma_commit(&sh.sfull[sb]);
+          umma_commit(&sh.empty[s]);
+          umma_commit(&sh.empty[s + 1]);
+        } else {
+          umma_k128(tmem_base + sb * 128, q_addr, PT_BLK_BYTES, smem_u32(ring + s * PT_TILE_BYTES), PT_BLK_BYTES,
+                    IDESC_QK);
+          umma_commit(&sh.sfull[sb]);
+          umma_commit(&sh.empty[s]);
+        }
         return true;
       };
-      for (int j = 0; ok && j < n; ++j) ok = issue_s(j, j);
-      if (ok) ok = issue_s(n, n);
+      for (int jj = 0; ok && jj < n1; ++jj) ok = issue_s(jj & 1, jj >> 1, W1 ? 2 * jj : jj, W1);
+      if (W1 && ok) {
+        // pass 2 lays S, O and P over the two wide tiles: both must have been read to the end
+        if (u1_0 > 0) ok = mbar_wait(&sh.sempty[0], (u1_0 - 1) & 1, abortp, p.error_word, 608);
+        if (ok && u1_1 > 0) ok = mbar_wait(&sh.sempty[1], (u1_1 - 1) & 1, abortp, p.error_word, 609);
+      }
+      auto issue_s2 = [&](int j) -> bool {
+        return issue_s(j & 1, ((j & 1) ? u1_1 : u1_0) + (j >> 1), base2 + 2 * j, false);
+      };
+      if (ok) ok = issue_s2(0);
       for (int j = 0; ok && j < n; ++j) {
-        if (j + 1 < n) ok = issue_s(n + j + 1, n + 2 * (j + 1));   // S of the next tile first
+        if (j + 1 < n) ok = issue_s2(j + 1);   // S of the next tile first
         if (!ok) break;
-        const int t = n + 2 * j + 1, s = t % PT_NRING, k = t / PT_NRING, pb = j & 1;
+        const int t = base2 + 2 * j + 1, s = t % PT_NRING, k = t / PT_NRING, pb = j & 1;
         if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 604)) { ok = false; break; }
         if (!mbar_wait(&sh.pfull[pb], (j >> 1) & 1, abortp, p.error_word, 605)) { ok = false; break; }
         fence_after_sync();
@@ -234,28 +286,44 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     uint32_t ra[32];
     // ---- pass 1: row maxima of the raw products ----
     float rmax = -INFINITY;
-    for (int j = 0; ok && j < n; ++j) {
-      const int sb = j & 1, use = j >> 1;
-      if (!mbar_wait(&sh.sfull[sb], use & 1, abortp, p.error_word, 701)) { ok = false; break; }
-      fence_after_sync();
-      tmem_ld32_issue(lane_base + sb * 128, ra);
-      tmem_ld32_wait(ra);
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh.sempty[sb]);
-      const int key0 = j * 128 + cq * 32;
+    auto row_max32 = [&](const uint32_t (&v)[32], int key0) {   // 32 keys from key0 on
       if (key0 + 31 <= lim) {
         float m0 = rmax, m1 = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
-          m0 = fmax3(m0, __uint_as_float(ra[i]), __uint_as_float(ra[i + 1]));
-          m1 = fmax3(m1, __uint_as_float(ra[i + 2]), __uint_as_float(ra[i + 3]));
+          m0 = fmax3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+          m1 = fmax3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
         }
         rmax = fmaxf(m0, m1);
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-          if (key0 + i <= lim) rmax = fmaxf(rmax, __uint_as_float(ra[i]));
+          if (key0 + i <= lim) rmax = fmaxf(rmax, __uint_as_float(v[i]));
+      }
+    };
+    for (int jj = 0; ok && jj < n1; ++jj) {
+      const int sb = jj & 1, use = jj >> 1;
+      if (!mbar_wait(&sh.sfull[sb], use & 1, abortp, p.error_word, 701)) { ok = false; break; }
+      fence_after_sync();
+      if (W1) {   // 256 keys: this warp's 64 columns
+        uint32_t rb[32];
+        const uint32_t tb = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + sb * 256 + cq * 64;
+        tmem_ld32_issue(tb, ra);
+        tmem_ld32_issue(tb + 32, rb);
+        tmem_ld32_wait(ra);
+        tmem_ld32_wait(rb);
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.sempty[sb]);
+        row_max32(ra, jj * 256 + cq * 64);
+        row_max32(rb, jj * 256 + cq * 64 + 32);
+      } else {
+        tmem_ld32_issue(lane_base + sb * 128, ra);
+        tmem_ld32_wait(ra);
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.sempty[sb]);
+        row_max32(ra, jj * 128 + cq * 32);
       }
     }
     if (ok) {
@@ -270,7 +338,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     // ---- pass 2: P = exp2(S * scale_log2e - max), row sums, P to shared memory ----
     float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
     for (int j = 0; ok && j < n; ++j) {
-      const int su = n + j, sb = su & 1, use = su >> 1, pb = j & 1;
+      const int sb = j & 1, use = ((j & 1) ? u1_1 : u1_0) + (j >> 1), pb = j & 1;
       if (!mbar_wait(&sh.sfull[sb], use & 1, abortp, p.error_word, 702)) { ok = false; break; }
       fence_after_sync();
       tmem_ld32_issue(lane_base + sb * 128, ra);
@@ -300,7 +368,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
       // the V tile's rows past the end of the sequence become zeros (0 * garbage could be NaN)
       if ((j + 1) * 128 > lk) {
-        const int t = n + 2 * j + 1, s = t % PT_NRING, k = t / PT_NRING;
+        const int t = base2 + 2 * j + 1, s = t % PT_NRING, k = t / PT_NRING;
         if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 703)) { ok = false; break; }
         unsigned char* vt = ring + s * PT_TILE_BYTES;
         const int first = lk - j * 128;   // first row to clear
@@ -362,35 +430,37 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 template <typename T>
 static int launch_prefill_tc(const void* q, const void* k, const void* v, const PtParams& p,
                              int max_seqlen_q, int64_t kv_stride_page, cudaStream_t st) {
-  CUtensorMap tmQ, tmK, tmV;
-  const uint32_t box[5] = {64, 1, 128, 1, 1};
+  CUtensorMap tmQ, tmK, tmK2, tmV;
+  const uint32_t box[5] = {64, 1, 128, 1, 1}, box2[5] = {64, 1, 256, 1, 1};
+  const bool wide = !p.table || p.BS % 256 == 0;   // 256-key tiles in pass 1 never straddle a page
   {
     const uint64_t dims[5] = {128, (uint64_t)p.Hq, (uint64_t)p.total_q, 1, 1};
     const uint64_t strides[4] = {128, (uint64_t)p.Hq * 128, (uint64_t)p.Hq * 128, (uint64_t)p.Hq * 128};
     int rc = make_tensor_map_5d(&tmQ, UmmaFmt<T>::tm, q, dims, strides, box, sizeof(T));
     if (rc) return rc;
   }
-  for (int which = 0; which < 2; ++which) {
-    const void* base = which ? v : k;
-    CUtensorMap* tm = which ? &tmV : &tmK;
+  for (int which = 0; which < 3; ++which) {   // K (128-key box), K (256-key box), V
+    const void* base = which == 2 ? v : k;
+    CUtensorMap* tm = which == 0 ? &tmK : (which == 1 ? &tmK2 : &tmV);
+    const uint32_t* bx = which == 1 ? box2 : box;
     int rc;
     if (p.table) {
       const uint64_t dims[5] = {128, (uint64_t)p.Hkv, (uint64_t)p.BS, 1ull << 30, 1};
       const uint64_t strides[4] = {128, (uint64_t)p.Hkv * 128, (uint64_t)kv_stride_page, (uint64_t)kv_stride_page};
-      rc = make_tensor_map_5d(tm, UmmaFmt<T>::tm, base, dims, strides, box, sizeof(T));
+      rc = make_tensor_map_5d(tm, UmmaFmt<T>::tm, base, dims, strides, which == 1 && !wide ? box : bx, sizeof(T));
     } else {
       const uint64_t dims[5] = {128, (uint64_t)p.Hkv, (uint64_t)p.total_k, 1, 1};
       const uint64_t strides[4] = {128, (uint64_t)p.Hkv * 128, (uint64_t)p.Hkv * 128, (uint64_t)p.Hkv * 128};
-      rc = make_tensor_map_5d(tm, UmmaFmt<T>::tm, base, dims, strides, box, sizeof(T));
+      rc = make_tensor_map_5d(tm, UmmaFmt<T>::tm, base, dims, strides, bx, sizeof(T));
     }
     if (rc) return rc;
   }
   const size_t smem = (1 + PT_NRING) * PT_TILE_BYTES + sizeof(PtShared) + 1024;
-  auto kern = prefill_tc_kernel<T>;
+  auto kern = wide ? prefill_tc_kernel<T, true> : prefill_tc_kernel<T, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_error("zp_varlen_prefill(tcgen05): %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
   dim3 grid((max_seqlen_q + 127) / 128, p.Hq, p.B);
-  kern<<<grid, PT_THREADS, smem, st>>>(tmQ, tmK, tmV, p);
+  kern<<<grid, PT_THREADS, smem, st>>>(tmQ, tmK, tmK2, tmV, p);
   return check_launch("zp_varlen_prefill(tcgen05)");
 }
 
