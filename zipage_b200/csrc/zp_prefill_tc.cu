@@ -2,9 +2,9 @@
 // 16-bit tensors, head_dim 128, K/V dense or paged (page size a multiple of 128).
 //
 // One block per (128-query tile, query head, sequence).  Two passes over the key tiles the query
-// tile can see, 128 keys at a time:
-//   pass 1:  S = Q K^T (M = 128 queries, N = 256 keys where the layout allows, else 128;
-//            K = 128 dims)                                               -> row maxima
+// tile can see.  This is the kernel for pages of an odd multiple of 128 keys, 128 keys at a time;
+// dense K/V and pages of a multiple of 256 keys take the 256-key-tile kernel further down:
+//   pass 1:  S = Q K^T (M = 128 queries, N = 128 keys, K = 128 dims)   -> row maxima
 //   pass 2:  S again, P = exp2(S * scale*log2e - max) (masked entries 0), row sums of P in fp32,
 //            P rounded to the tensor dtype and stored to TMEM as the A operand of
 //            O += P V (M = 128 queries, N = 128 dims, K = 128 keys; V is the B operand as it lies in
@@ -36,7 +36,6 @@ struct PtParams {
   int* error_word;
   int B, NBmax, Hq, Hkv, BS;
   int total_q, total_k;   // rows of q and of dense k/v (tensor-map extents: rows past them read as 0)
-  int wide2;              // 256-key tiles in both passes where the layout allows (else pass 1 only)
   float scale_log2e;
 };
 
@@ -86,13 +85,10 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
-// W1: pass 1 works on 256-key tiles (two adjacent ring stages hold the two 64-dim blocks of 256
-// keys; both halves of TMEM serve as its two S tiles, nothing else lives there yet).
-template <typename T, bool W1>
+template <typename T>
 __global__ void __launch_bounds__(PT_THREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                  const __grid_constant__ CUtensorMap tmK2, const __grid_constant__ CUtensorMap tmV,
-                  const PtParams p) {
+                  const __grid_constant__ CUtensorMap tmV, const PtParams p) {
   // tile geometry (identical in every role)
   const int b = blockIdx.z, h = blockIdx.y;
   const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
@@ -106,8 +102,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const int rows = min(128, lq - qi0);
   const int kmax = min(lk, qi0 + rows + shift); // keys any row of the tile can see
   const int n = kmax > 0 ? (kmax + 127) >> 7 : 0;
-  const int n1 = W1 ? (n + 1) >> 1 : n;         // tiles of pass 1
-  const int base2 = W1 ? 2 * n1 : n;            // ring position of pass 2's first load
+  const int n1 = n;                             // tiles of pass 1
+  const int base2 = n;                          // ring position of pass 2's first load
   // S tile bookkeeping: pass-1 tile jj -> TMEM buffer jj & 1, its (jj >> 1)-th use; pass-2 tile j ->
   // buffer j & 1, use u1[j & 1] + (j >> 1) with u1[b] = pass-1 uses of buffer b
   const int u1_0 = (n1 + 1) >> 1, u1_1 = n1 >> 1;
@@ -154,10 +150,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   volatile int* abortp = &sh.abort_flag;
   constexpr uint32_t IDESC_QK = idesc_f16(UmmaFmt<T>::fmt, 128, 128);
   constexpr uint32_t IDESC_PV = IDESC_QK | (1u << 16);   // B operand MN-major
-  constexpr uint32_t IDESC_QK1 = W1 ? idesc_f16(UmmaFmt<T>::fmt, 128, 256) : IDESC_QK;
 
-  // ring position of a load: pass 1: K_j -> j (W1: tile jj -> 2jj and 2jj + 1);
-  // pass 2: K_j -> base2 + 2j, V_j -> base2 + 2j + 1
+  // ring position of a load: pass 1: K_j -> j; pass 2: K_j -> base2 + 2j, V_j -> base2 + 2j + 1
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
@@ -185,30 +179,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tma_load_5d(dst + PT_BLK_BYTES, tm, &sh.full[s], 64, hk, c2, c3, 0);
         return true;
       };
-      if (W1) {
-        prefetch_tensormap(&tmK2);
-        for (int jj = 0; ok && jj < n1; ++jj) {
-          const int t = 2 * jj, s = t % PT_NRING, k = t / PT_NRING;   // s is even: stages s and s + 1
-          if (!mbar_wait<true>(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 502) ||
-              !mbar_wait<true>(&sh.empty[s + 1], (k & 1) ^ 1, abortp, p.error_word, 503)) { ok = false; break; }
-          int c2, c3;
-          if (p.table) {   // the page size is a multiple of 256 here
-            c2 = (jj * 256) % p.BS;
-            c3 = p.table[(int64_t)b * p.NBmax + (jj * 256) / p.BS];
-          } else {
-            c2 = k0 + jj * 256;
-            c3 = 0;
-          }
-          // one 64-dim block of the 256 keys per stage, each on its own stage barrier (every stage's
-          // barriers complete exactly once per trip round the ring, in both passes)
-          mbar_arrive_expect_tx(&sh.full[s], PT_TILE_BYTES);
-          tma_load_5d(ring + s * PT_TILE_BYTES, &tmK2, &sh.full[s], 0, hk, c2, c3, 0);
-          mbar_arrive_expect_tx(&sh.full[s + 1], PT_TILE_BYTES);
-          tma_load_5d(ring + (s + 1) * PT_TILE_BYTES, &tmK2, &sh.full[s + 1], 64, hk, c2, c3, 0);
-        }
-      } else {
-        for (int j = 0; ok && j < n; ++j) ok = load(j, &tmK, j);
-      }
+      for (int j = 0; ok && j < n; ++j) ok = load(j, &tmK, j);
       for (int j = 0; ok && j < n; ++j) {
         ok = load(base2 + 2 * j, &tmK, j);
         if (ok) ok = load(base2 + 2 * j + 1, &tmV, j);
@@ -220,34 +191,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       bool ok = mbar_wait(&sh.qfull, 0, abortp, p.error_word, 601);
       const uint32_t q_addr = smem_u32(qbuf);
       // one S tile: TMEM buffer sb (its `use`-th use), key tile at ring position t
-      auto issue_s = [&](int sb, int use, int t, bool wide) -> bool {
+      auto issue_s = [&](int sb, int use, int t) -> bool {
         const int s = t % PT_NRING, k = t / PT_NRING;
         if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 602)) return false;
-        if (wide && !mbar_wait(&sh.full[s + 1], k & 1, abortp, p.error_word, 610)) return false;
         if (!mbar_wait(&sh.sempty[sb], (use & 1) ^ 1, abortp, p.error_word, 603)) return false;
         fence_after_sync();
-        if (wide) {
-          umma_k128(tmem_base + sb * 256, q_addr, PT_BLK_BYTES, smem_u32(ring + s * PT_TILE_BYTES), PT_TILE_BYTES,
-                    IDESC_QK1);
-          umma_commit(&sh.sfull[sb]);
-          umma_commit(&sh.empty[s]);
-          umma_commit(&sh.empty[s + 1]);
-        } else {
-          umma_k128(tmem_base + sb * 128, q_addr, PT_BLK_BYTES, smem_u32(ring + s * PT_TILE_BYTES), PT_BLK_BYTES,
-                    IDESC_QK);
-          umma_commit(&sh.sfull[sb]);
-          umma_commit(&sh.empty[s]);
-        }
+        umma_k128(tmem_base + sb * 128, q_addr, PT_BLK_BYTES, smem_u32(ring + s * PT_TILE_BYTES), PT_BLK_BYTES,
+                  IDESC_QK);
+        umma_commit(&sh.sfull[sb]);
+        umma_commit(&sh.empty[s]);
         return true;
       };
-      for (int jj = 0; ok && jj < n1; ++jj) ok = issue_s(jj & 1, jj >> 1, W1 ? 2 * jj : jj, W1);
-      if (W1 && ok) {
-        // pass 2 lays S, O and P over the two wide tiles: both must have been read to the end
-        if (u1_0 > 0) ok = mbar_wait(&sh.sempty[0], (u1_0 - 1) & 1, abortp, p.error_word, 608);
-        if (ok && u1_1 > 0) ok = mbar_wait(&sh.sempty[1], (u1_1 - 1) & 1, abortp, p.error_word, 609);
-      }
+      for (int jj = 0; ok && jj < n1; ++jj) ok = issue_s(jj & 1, jj >> 1, jj);
       auto issue_s2 = [&](int j) -> bool {
-        return issue_s(j & 1, ((j & 1) ? u1_1 : u1_0) + (j >> 1), base2 + 2 * j, false);
+        return issue_s(j & 1, ((j & 1) ? u1_1 : u1_0) + (j >> 1), base2 + 2 * j);
       };
       if (ok) ok = issue_s2(0);
       for (int j = 0; ok && j < n; ++j) {
@@ -306,26 +263,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const int sb = jj & 1, use = jj >> 1;
       if (!mbar_wait(&sh.sfull[sb], use & 1, abortp, p.error_word, 701)) { ok = false; break; }
       fence_after_sync();
-      if (W1) {   // 256 keys: this warp's 64 columns
-        uint32_t rb[32];
-        const uint32_t tb = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + sb * 256 + cq * 64;
-        tmem_ld32_issue(tb, ra);
-        tmem_ld32_issue(tb + 32, rb);
-        tmem_ld32_wait(ra);
-        tmem_ld32_wait(rb);
-        fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh.sempty[sb]);
-        row_max32(ra, jj * 256 + cq * 64);
-        row_max32(rb, jj * 256 + cq * 64 + 32);
-      } else {
-        tmem_ld32_issue(lane_base + sb * 128, ra);
-        tmem_ld32_wait(ra);
-        fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh.sempty[sb]);
-        row_max32(ra, jj * 128 + cq * 32);
-      }
+      tmem_ld32_issue(lane_base + sb * 128, ra);
+      tmem_ld32_wait(ra);
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.sempty[sb]);
+      row_max32(ra, jj * 128 + cq * 32);
     }
     if (ok) {
       sh.stat[cq][r] = rmax;
@@ -761,7 +704,7 @@ static int launch_prefill_tc(const void* q, const void* k, const void* v, const 
                              int max_seqlen_q, int64_t kv_stride_page, cudaStream_t st) {
   CUtensorMap tmQ, tmK, tmK2, tmV, tmV2;
   const uint32_t box[5] = {64, 1, 128, 1, 1}, box2[5] = {64, 1, 256, 1, 1};
-  const bool wide = !p.table || p.BS % 256 == 0;   // 256-key tiles in pass 1 never straddle a page
+  const bool wide = !p.table || p.BS % 256 == 0;   // a 256-key tile never straddles a page
   {
     const uint64_t dims[5] = {128, (uint64_t)p.Hq, (uint64_t)p.total_q, 1, 1};
     const uint64_t strides[4] = {128, (uint64_t)p.Hq * 128, (uint64_t)p.Hq * 128, (uint64_t)p.Hq * 128};
@@ -786,7 +729,7 @@ static int launch_prefill_tc(const void* q, const void* k, const void* v, const 
   }
   const size_t smem = (1 + PT_NRING) * PT_TILE_BYTES + sizeof(PtShared) + 1024;
   dim3 grid((max_seqlen_q + 127) / 128, p.Hq, p.B);
-  if (wide && p.wide2) {
+  if (wide) {
     const size_t smem2 = (1 + PW_NRING) * PT_TILE_BYTES + sizeof(PwShared) + PW_SLACK;
     auto kern2 = prefill_tc_wide_kernel<T>;
     cudaError_t e2 = cudaFuncSetAttribute(kern2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
@@ -794,10 +737,10 @@ static int launch_prefill_tc(const void* q, const void* k, const void* v, const 
     kern2<<<grid, PT_THREADS, smem2, st>>>(tmQ, tmK2, tmV2, p);
     return check_launch("zp_varlen_prefill(tcgen05, 256-key tiles)");
   }
-  auto kern = wide ? prefill_tc_kernel<T, true> : prefill_tc_kernel<T, false>;
+  auto kern = prefill_tc_kernel<T>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_error("zp_varlen_prefill(tcgen05): %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
-  kern<<<grid, PT_THREADS, smem, st>>>(tmQ, tmK, tmK2, tmV, p);
+  kern<<<grid, PT_THREADS, smem, st>>>(tmQ, tmK, tmV, p);
   return check_launch("zp_varlen_prefill(tcgen05)");
 }
 
@@ -809,7 +752,6 @@ int varlen_prefill_tc(const void* q, const void* k, const void* v, const int32_t
                       cudaStream_t st) {
   PtParams p{};
   p.total_q = total_q; p.total_k = total_k;
-  p.wide2 = 1;
   p.cu_q = cu_q; p.cu_k = cu_k; p.table = table; p.out = out;
   p.error_word = device_error_word();
   p.B = B; p.NBmax = NBmax; p.Hq = Hq; p.Hkv = Hkv; p.BS = BS; p.scale_log2e = scale_log2e;
