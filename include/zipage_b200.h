@@ -282,11 +282,14 @@ int zp_silu_and_mul(const void* x, void* out, int n_rows, int inter, int dtype, 
  * q_out [n_tokens, Hq, D]; k_out [n_tokens, Hkv, D] or NULL (decode reads K from the cache).
  * slot_mapping [n_tokens] or NULL: flat cache slot of each token (-1 = skip); k_cache / v_cache
  * contiguous [P*BS, Hkv, D] (one layer).  triples [n_triples, 3] int32 (row, query_id, window
- * index) -> query_cache [C, QCL, Hq, D] (one layer; strides in elements). */
+ * index) -> query_cache [C, QCL, Hq, D] (one layer; strides in elements).  n_triples_device: NULL,
+ * or a device word with the number of valid triples (as zp_prepare_decode leaves it), in which case
+ * n_triples is only an upper bound (the rows of `triples`) and no host read-back is needed. */
 int zp_qk_norm_rope_store(const void* qkv, const int64_t* positions, const float* cos_sin,
                           const void* q_weight, const void* k_weight, float eps, void* q_out,
                           void* k_out, void* k_cache, void* v_cache, const int32_t* slot_mapping,
-                          void* query_cache, const int32_t* triples, int n_triples, int n_tokens,
+                          void* query_cache, const int32_t* triples, int n_triples,
+                          const int32_t* n_triples_device, int n_tokens,
                           int Hq, int Hkv, int D, int64_t qkv_stride, int64_t cache_stride_seq,
                           int64_t cache_stride_slot, int dtype, void* stream);
 

@@ -181,3 +181,36 @@ def test_prepare_decode_large_batch_against_oracle():
     assert torch.equal(gp.cpu(), pos) and torch.equal(gc.cpu(), ctx) and torch.equal(gs.cpu(), slot)
     k = int(gn.item())
     assert k == len(trip) and torch.equal(gt[:k].cpu(), trip)
+
+
+def test_decode_step_without_host_lists():
+    """prepare_decode -> fused q/k kernel with the triple count left on the device: the window
+    rows of exactly the sequences inside their observation window are written, nothing else."""
+    from oracle import step_ops_oracle as S
+    from zipage_b200.layers import step_ops as P
+    dev = _gpu()
+    st = decode_state()
+    B, Hq, Hkv, D, QCL = len(st["num_tokens"]), 4, 2, 128, st["query_cache_len"]
+    g = torch.Generator().manual_seed(2)
+    width = max(len(t) for t in st["block_tables"])
+    tables = torch.tensor([t + [-1] * (width - len(t)) for t in st["block_tables"]], dtype=torch.int32, device=dev)
+    pos, ctx, slot, trip, ntrip = P.prepare_decode(
+        torch.tensor(st["num_tokens"], dtype=torch.int32, device=dev), tables,
+        torch.tensor(st["query_ids"], dtype=torch.int32, device=dev), QCL)
+    qkv = torch.randn(B, (Hq + 2 * Hkv) * D, generator=g).to(torch.bfloat16)
+    w = torch.ones(D, dtype=torch.bfloat16)
+    cache = S.rope_cos_sin_cache(D, 8192, 1e6)
+    pages = int(tables.max()) + 1
+    kc = torch.zeros((pages * 256, Hkv, D), dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros_like(kc)
+    qc = torch.full((8, QCL, Hq, D), 7.0, dtype=torch.bfloat16, device=dev)
+    q, _, _ = P.qk_norm_rope_store(qkv.to(dev), pos, cache.to(dev), w.to(dev), w.to(dev), 1e-6, Hq, Hkv, D,
+                                   k_cache=kc, v_cache=vc, slot_mapping=slot, query_cache=qc,
+                                   query_slot_mapping=trip, query_slot_count=ntrip, return_k=False)
+    _, _, _, _, want = S.prepare_decode(st["num_tokens"], st["block_tables"], st["query_ids"], QCL)
+    mask = torch.ones(8, QCL, dtype=torch.bool)
+    for row, qid, idx in want.tolist():
+        assert torch.equal(qc[qid, idx].cpu(), q[row].cpu())
+        mask[qid, idx] = False
+    assert (qc.cpu()[mask] == 7.0).all()
+    assert (kc[slot.long()].float().abs().sum(dim=(1, 2)) > 0).all()   # every sequence's K row was stored

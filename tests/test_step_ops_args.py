@@ -38,7 +38,7 @@ def test_other_step_ops_reject_bad_arguments():
     assert lib.zp_silu_and_mul(None, p, 3, 128, 0, None) == INVALID
     assert lib.zp_silu_and_mul(p, p, 3, 100, 0, None) == INVALID          # 100 bf16 is not whole vectors
     args = lambda **kw: [kw.get("qkv", p), p, p, p, p, 1e-6, kw.get("q_out", p), None, kw.get("kc"), kw.get("vc"),
-                         kw.get("slots"), kw.get("qc"), kw.get("trip"), kw.get("ntrip", 0), kw.get("n", 5), 8, 2,
+                         kw.get("slots"), kw.get("qc"), kw.get("trip"), kw.get("ntrip", 0), None, kw.get("n", 5), 8, 2,
                          kw.get("D", 128), 1536, 0, 0, 0, None]
     assert lib.zp_qk_norm_rope_store(*args(n=0)) == 0
     assert lib.zp_qk_norm_rope_store(*args(q_out=None)) == INVALID

@@ -73,7 +73,7 @@ SIGNATURES = {
     "zp_varlen_prefill_ex": (_I, [_P] * 7 + [_I] * 7 + [_L, _F, _I, _I, _I, _I, _P]),
     "zp_rms_norm": (_I, [_P] * 5 + [_I, _I, _L, _L, _F, _I, _P]),
     "zp_silu_and_mul": (_I, [_P, _P, _I, _I, _I, _P]),
-    "zp_qk_norm_rope_store": (_I, [_P] * 5 + [_F] + [_P] * 7 + [_I] * 5 + [_L] * 3 + [_I, _P]),
+    "zp_qk_norm_rope_store": (_I, [_P] * 5 + [_F] + [_P] * 7 + [_I, _P] + [_I] * 4 + [_L] * 3 + [_I, _P]),
     "zp_sample": (_I, [_P, _P, _P, _P, _I, _I, C.c_uint64, _I, _P]),
     "zp_prepare_decode": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
 }

@@ -166,6 +166,7 @@ struct QkArgs {
   const void* q_weight; const void* k_weight;
   void* q_out; void* k_out; void* k_cache; void* v_cache;
   const int32_t* slot_mapping; void* query_cache; const int32_t* triples;
+  const int32_t* n_triples_dev;   // NULL, or the device word that holds the number of valid triples
   int n_tokens, n_triples, Hq, Hkv;
   int64_t qkv_stride, cache_stride_seq, cache_stride_slot;
   float eps;
@@ -233,6 +234,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkArgs a)
   if (!window) n = item;
   else {
     const int t = item - a.n_tokens;
+    if (a.n_triples_dev && t >= *a.n_triples_dev) return;   // n_triples was only the upper bound
     n = a.triples[3 * t]; qid = a.triples[3 * t + 1]; idx = a.triples[3 * t + 2];
   }
   const T* row = qkv + (int64_t)n * a.qkv_stride;
@@ -512,7 +514,8 @@ extern "C" int zp_qk_norm_rope_store(const void* qkv, const int64_t* positions, 
                                      const void* q_weight, const void* k_weight, float eps,
                                      void* q_out, void* k_out, void* k_cache, void* v_cache,
                                      const int32_t* slot_mapping, void* query_cache,
-                                     const int32_t* triples, int n_triples, int n_tokens, int Hq,
+                                     const int32_t* triples, int n_triples,
+                                     const int32_t* n_triples_device, int n_tokens, int Hq,
                                      int Hkv, int D, int64_t qkv_stride, int64_t cache_stride_seq,
                                      int64_t cache_stride_slot, int dtype, void* stream) {
   if (n_tokens == 0) return ZP_OK;
@@ -533,6 +536,7 @@ extern "C" int zp_qk_norm_rope_store(const void* qkv, const int64_t* positions, 
   a.qkv = qkv; a.positions = positions; a.cos_sin = cos_sin; a.q_weight = q_weight; a.k_weight = k_weight;
   a.q_out = q_out; a.k_out = k_out; a.k_cache = k_cache; a.v_cache = v_cache;
   a.slot_mapping = slot_mapping; a.query_cache = query_cache; a.triples = triples;
+  a.n_triples_dev = n_triples_device;
   a.n_tokens = n_tokens; a.n_triples = n_triples; a.Hq = Hq; a.Hkv = Hkv;
   a.qkv_stride = qkv_stride; a.cache_stride_seq = cache_stride_seq; a.cache_stride_slot = cache_stride_slot;
   a.eps = eps;

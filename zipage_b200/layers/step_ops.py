@@ -80,12 +80,14 @@ def rope_cos_sin_cache(head_dim, max_position, base, device):
 
 def qk_norm_rope_store(qkv, positions, cos_sin, q_weight, k_weight, eps, num_heads, num_kv_heads,
                        head_dim, k_cache=None, v_cache=None, slot_mapping=None, query_cache=None,
-                       query_slot_mapping=None, return_k=True):
+                       query_slot_mapping=None, return_k=True, query_slot_count=None):
     """qkv [N, (Hq+2Hkv)*D] -> q [N,Hq,D] (normalised, rotated), k [N,Hkv,D] (or None), and, when
     given, K/V rows written to the paged caches at slot_mapping and window queries written to
-    query_cache at the (row, query_id, index) triples — one launch."""
+    query_cache at the (row, query_id, index) triples — one launch.  `query_slot_count`: a device
+    int32 tensor with the number of valid rows of `query_slot_mapping` (as `prepare_decode` returns
+    it); without it every row is taken."""
     L.require_cuda(qkv, positions, cos_sin, q_weight, k_weight, k_cache, v_cache, slot_mapping,
-                   query_cache, query_slot_mapping)
+                   query_cache, query_slot_mapping, query_slot_count)
     N = qkv.shape[0]
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
     assert qkv.shape[1] == (Hq + 2 * Hkv) * D and qkv.stride(1) == 1
@@ -100,7 +102,7 @@ def qk_norm_rope_store(qkv, positions, cos_sin, q_weight, k_weight, eps, num_hea
     L.check(L.load().zp_qk_norm_rope_store(
         L.ptr(qkv), L.ptr(positions), L.ptr(cos_sin), L.ptr(q_weight), L.ptr(k_weight), float(eps),
         L.ptr(q), L.ptr(k), L.ptr(k_cache), L.ptr(v_cache), L.ptr(slot_mapping), L.ptr(query_cache),
-        L.ptr(query_slot_mapping), ntrip, N, Hq, Hkv, D, qkv.stride(0), cs_seq, cs_slot,
+        L.ptr(query_slot_mapping), ntrip, L.ptr(query_slot_count), N, Hq, Hkv, D, qkv.stride(0), cs_seq, cs_slot,
         L.dtype_code(qkv), L.stream_ptr()), "qk_norm_rope_store")
     _count(1)
     v = qkv[:, (Hq + Hkv) * D:].view(N, Hkv, D)
