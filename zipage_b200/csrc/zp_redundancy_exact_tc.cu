@@ -89,7 +89,7 @@ struct SlotFifo {
 // per unit w = sum_n k_n / |k_n| in fp32.  One block per unit walks the unit's pages in order (a
 // fixed summation order); a warp owns one 32-key chunk of each page, a lane four of the 128 dims.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 key_stats_kernel(const T* __restrict__ k_cache, const int32_t* __restrict__ block_table,
                  float* __restrict__ rn, float* __restrict__ dself, float* __restrict__ nmin,
                  float* __restrict__ wvec, int B, int NB, int Hkv, int64_t k_stride_layer,
