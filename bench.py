@@ -46,10 +46,11 @@ def parse_args():
     ap.add_argument("--kernel-impl", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--also-exact", action="store_true", help="time the exact variant as well")
-    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops", "prefill"],
+    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops", "prefill", "decode_step"],
                     help="compress (default, the headline op), decode (paged decode attention kernel) or "
                          "step_ops (the element-wise ops of a decoder layer step and the sampler) or "
-                         "prefill (varlen causal prefill attention, one layer)")
+                         "prefill (varlen causal prefill attention, one layer) or decode_step (the decode "
+                         "forward of Qwen3-8B-shaped blocks, launch by launch and as a replayed CUDA graph)")
     ap.add_argument("--tokens", type=int, default=32768, help="tokens per call of the step_ops workload")
     return ap.parse_args()
 
@@ -269,6 +270,101 @@ def run_decode(args):
     }))
 
 
+def run_decode_step(args):
+    """The decode forward of Qwen3-8B-shaped decoder blocks (hidden 4096, 32 q / 8 kv heads of 128,
+    MLP 12288, bf16, random weights; cuBLAS projections, everything else this library's kernels)
+    over compressed tables (context 2049..2304 tokens in 9 pages), timed launch by launch and as
+    one replayed CUDA graph whose inputs are device state only.  `value` is the graph's rate with
+    the inputs already in the graph's buffers; `e2e` copies the step's inputs from pinned host
+    memory and reads the hidden states back."""
+    import torch
+    from types import SimpleNamespace
+    from zipage_b200 import kernel as K
+    from zipage_b200.engine.decode_graph import DecodeGraphRunner
+    from zipage_b200.layers.qwen3_block import Qwen3Model
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, Ln, NBs = min(args.batch, 256), min(args.layers, 36), BUDGET + 1
+    cfg = SimpleNamespace(hidden_size=4096, num_attention_heads=HQ, num_key_value_heads=HKV, head_dim=D,
+                          intermediate_size=12288, hidden_act="silu", rms_norm_eps=1e-6, vocab_size=151936,
+                          num_hidden_layers=Ln, max_position_embeddings=40960, rope_theta=1e6)
+    torch.manual_seed(1)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(dev):
+            model = Qwen3Model(cfg).eval()
+    finally:
+        torch.set_default_dtype(prev)
+    P = B * (NBs + 1)
+    kv = torch.empty((2, Ln, P, BS, HKV, D), dtype=torch.bfloat16, device=dev).normal_()
+    qc = torch.zeros((Ln, B, QCL, HQ, D), dtype=torch.bfloat16, device=dev)
+    model.bind_caches(kv, qc)
+    g = torch.Generator(device="cpu").manual_seed(5)
+    table = torch.randperm(P, generator=g)[: B * NBs].view(B, NBs).to(torch.int32).pin_memory()
+    ntok = torch.randint(BUDGET * BS + 1, NBs * BS + 1, (B,), generator=g).to(torch.int32).pin_memory()
+    ids = torch.randint(0, cfg.vocab_size, (B,), generator=g).pin_memory()
+    qid = torch.arange(B, dtype=torch.int32).pin_memory()
+    runner = DecodeGraphRunner(model, cfg.hidden_size, max_bs=B, max_num_blocks=NBs + 1, query_cache_len=QCL,
+                               device=dev, graph_bs=[B])
+    runner.capture()
+    host_out = torch.empty((B, cfg.hidden_size), dtype=torch.bfloat16).pin_memory()
+    d_args = [x.to(dev) for x in (ids, ntok, table, qid)]
+    runner._fill(*d_args)
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    def e2e_step():
+        out = runner.run(ids.to(dev, non_blocking=True), ntok.to(dev, non_blocking=True),
+                         table.to(dev, non_blocking=True), qid.to(dev, non_blocking=True))
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    graph = runner.graphs[B]
+    K.LAUNCHES = 0
+    runner._step(B)
+    per_step = K.LAUNCHES
+    with ClockSampler(dev.index or 0) as clocks:
+        ms_graph = timed(graph.replay)
+    ms_eager = timed(lambda: runner._step(B))
+    ms_e2e = timed(e2e_step)
+    h2d = ids.numel() * 8 + ntok.numel() * 4 + table.numel() * 4 + qid.numel() * 4
+    # bytes a step must read once: every block's weights and the K/V rows of every context token
+    wbytes = sum(p.numel() for n, p in model.named_parameters() if "embed" not in n) * 2
+    kvbytes = float(ntok.sum().item()) * HKV * D * 2 * 2 * Ln
+    peaks = {}
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        peaks = json.loads(pk.read_text())
+    hbm_peak = peaks.get("hbm_gbs", 6650.0)
+    ach = (wbytes + kvbytes) / (ms_graph * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "decode_step_tokens_per_s", "value": B / (ms_graph * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_graph, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "decode forward, Qwen3-8B-shaped blocks, compressed tables (2049..2304 tokens "
+                               "in 9 pages), one CUDA graph replay per step", "sequences": B, "layers": Ln,
+                   "l2": "weights + K/V of a step (%.1f GB) far exceed the 126 MB L2" % ((wbytes + kvbytes) / 1e9)},
+        "launch_by_launch_ms_per_step": ms_eager, "graph_speedup": ms_eager / ms_graph,
+        "e2e": {"value": B / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": host_out.numel() * 2},
+        "gpu_launches": per_step * args.steps, "own_kernels_per_step": per_step, "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "kernel": "whole step (weights + K/V read once)", "achieved": ach,
+                     "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
+                     "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback", "traffic": None},
+    }))
+
+
 def run_step_ops(args):
     """The per-step ops of one decoder layer at Qwen3-8B sizes (hidden 4096, intermediate 12288,
     32 query / 8 KV heads of 128) on a prefill-sized batch of tokens, so that every input is larger
@@ -410,6 +506,8 @@ def main():
         return run_decode(args)
     if args.workload == "step_ops":
         return run_step_ops(args)
+    if args.workload == "decode_step":
+        return run_decode_step(args)
 
     import torch
     import torch.distributed as dist

@@ -314,6 +314,42 @@ int zp_prepare_decode(const int32_t* num_tokens, const int32_t* block_tables,
                       int32_t* slot_mapping_out, int32_t* triples_out, int32_t* n_triples_out,
                       void* stream);
 
+/* ---- tensor-parallel all-reduce over NVLink peer memory (one process per GPU, one node) ----------
+ * Replaces dist.all_reduce(y) of RowParallelLinear.forward, third_party/nanovllm/layers/linear.py:
+ * 149-153 (o_proj and down_proj of every decoder block), and, fused with it, the
+ * RMSNorm.add_rms_forward that consumes the reduced tensor (third_party/nanovllm/layers/layernorm.py:
+ * 28-40, called at third_party/nanovllm/models/qwen3.py:146-152).  The sum is taken in fp32 in rank
+ * order and rounded to T once, so every rank holds the same bits.
+ *
+ * Set-up, once per rank: zp_comm_create allocates this rank's segment (flags + four message areas
+ * of max_bytes) with cudaMalloc; the ranks exchange the 64-byte handles of zp_comm_ipc_handle by
+ * any host channel and map each other's segment with zp_comm_open_peer (CUDA IPC), or map the
+ * segments themselves and pass the pointers to zp_comm_attach_peer.  All ranks must make the same
+ * sequence of calls with the same sizes.  Every device-side wait ends after timeout_ms: the call's
+ * result is then undefined, zp_comm_status reports ZP_COMM_TIMEOUT and the communicator must be
+ * destroyed and created again; the CUDA context stays usable. */
+typedef struct zp_comm zp_comm;
+#define ZP_COMM_OK 0
+#define ZP_COMM_TIMEOUT 1
+int zp_comm_create(int rank, int world, size_t max_bytes, int timeout_ms, zp_comm** comm_out);
+int zp_comm_segment(zp_comm* comm, void** ptr_out, size_t* bytes_out);
+int zp_comm_ipc_handle(zp_comm* comm, void* handle64_out);
+int zp_comm_open_peer(zp_comm* comm, int peer, const void* handle64);
+int zp_comm_attach_peer(zp_comm* comm, int peer, void* segment);
+int zp_comm_status(zp_comm* comm, int* status_out);   /* synchronous 4-byte read */
+int zp_comm_destroy(zp_comm* comm);
+/* out[i] = T(sum over ranks of in[i]); count elements, count * sizeof(T) a multiple of 16 and at
+ * most max_bytes; in == out allowed.  algo: 0 = by size and world, 1 = one-shot (every rank reads
+ * all inputs), 2 = two-shot (reduce-scatter into every rank's result area, then a local read). */
+int zp_all_reduce(zp_comm* comm, const void* in, void* out, int64_t count, int dtype, int algo,
+                  void* stream);
+/* x = all-reduce(in) [rows, hidden]; s = x + residual; residual_out = T(s);
+ * out = T(T(s * rsqrt(mean(s^2) + eps)) * weight) — zp_all_reduce followed by zp_rms_norm with a
+ * residual, in one launch.  out may alias in, residual_out may alias residual. */
+int zp_all_reduce_add_rms_norm(zp_comm* comm, const void* in, const void* residual, const void* weight,
+                               void* out, void* residual_out, int64_t rows, int hidden, float eps,
+                               int dtype, int algo, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -95,6 +95,11 @@ def prepare_decode(num_tokens, block_tables, query_ids, query_cache_len, block_s
     [B, max_len] i32 (-1 padded), triples [n,3] i32."""
     pos, ctx, slot, trip = [], [], [], []
     for i, (n, table, qid) in enumerate(zip(num_tokens, block_tables, query_ids)):
+        if n <= 0 or len(table) == 0:
+            # padding row of a fixed-size graph batch, filled as the replay branch fills it
+            # (model_runner.py:716-719: slot -1, context length 0)
+            pos.append(0); ctx.append(0); slot.append(-1)
+            continue
         nblocks = (n + block_size - 1) // block_size
         last = n - (nblocks - 1) * block_size
         pos.append(n - 1)
@@ -102,7 +107,7 @@ def prepare_decode(num_tokens, block_tables, query_ids, query_cache_len, block_s
         slot.append(table[-1] * block_size + last - 1)
         if qid != -1 and last > block_size - query_cache_len:
             trip.append((i, qid, last - (block_size - query_cache_len) - 1))
-    width = max(len(t) for t in block_tables)
+    width = max(1, max(len(t) for t in block_tables))
     padded = [list(t) + [-1] * (width - len(t)) for t in block_tables]
     return (torch.tensor(pos, dtype=torch.int64), torch.tensor(ctx, dtype=torch.int32),
             torch.tensor(slot, dtype=torch.int32), torch.tensor(padded, dtype=torch.int32),

@@ -1,0 +1,113 @@
+"""One rank of the two-GPU all-reduce test (run by test_gpu_tp_comm.py under torch.distributed.run).
+
+Checks the peer-memory all-reduce bit for bit against the fp32 rank-order sum of the gathered
+inputs, the fused residual + RMSNorm form against all-reduce followed by the RMSNorm kernel, and
+the area hand-over between consecutive calls without any host synchronisation in between.
+"""
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+
+def expected(x, dtype):
+    parts = [torch.empty_like(x) for _ in range(dist.get_world_size())]
+    dist.all_gather(parts, x)
+    acc = parts[0].float()
+    for p in parts[1:]:
+        acc = acc + p.float()
+    return acc.to(dtype)
+
+
+def main():
+    from zipage_b200.layers.step_ops import rms_norm
+    from zipage_b200.layers.tp_comm import TPCommunicator
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    comm = TPCommunicator(max_bytes=8 << 20, timeout_ms=5000)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        per = 16 // torch.empty((), dtype=dtype).element_size()
+        for n in (per, 4096, 1000 * per + 3 * per, 256 * 4096, 2 * 1024 * 1024):
+            for algo in ("one_shot", "two_shot", "auto"):
+                x = torch.randn(n, device=dev, generator=g).to(dtype)
+                want = expected(x, dtype)
+                got = comm.all_reduce(x.clone(), algo=algo)
+                assert torch.equal(got, want), (dtype, n, algo)
+                out = torch.empty_like(x)
+                assert comm.all_reduce(x, out=out, algo=algo) is out and torch.equal(out, want)
+
+    # consecutive calls with nothing between them: each call's areas must survive until every
+    # peer has read them, and sizes (hence grids) change from call to call
+    sizes = [4096, 1 << 20, 8, 65536, 1 << 21, 512, 4096, 1 << 19] * 3
+    xs = [torch.randn(n, device=dev, generator=g).to(torch.bfloat16) for n in sizes]
+    wants = [expected(x, torch.bfloat16) for x in xs]
+    torch.cuda.synchronize()
+    dist.barrier()
+    for algo in ("one_shot", "two_shot"):
+        outs = [comm.all_reduce(x, out=torch.empty_like(x), algo=algo) for x in xs]
+        torch.cuda.synchronize()
+        for o, w in zip(outs, wants):
+            assert torch.equal(o, w), algo
+
+    # fused residual add + RMSNorm
+    for dtype in (torch.bfloat16, torch.float32):
+        for rows, hidden in ((256, 4096), (3, 1024), (300, 2048)):
+            x = torch.randn(rows, hidden, device=dev, generator=g).to(dtype)
+            torch.manual_seed(7)   # residual and weight are replicated across the ranks
+            res = torch.randn(rows, hidden).to(dtype).to(dev)
+            w = (1 + 0.1 * torch.randn(hidden)).to(dtype).to(dev)
+            for algo in ("one_shot", "two_shot"):
+                y0, r0 = rms_norm(comm.all_reduce(x.clone(), algo=algo), w, 1e-6, res)
+                y1, r1 = comm.all_reduce_add_rms_norm(x, res, w, 1e-6, algo=algo)
+                assert torch.equal(r0, r1), (dtype, rows, hidden, algo)
+                # the sum of squares is reduced over 512 threads here, 256 there: the scale can differ
+                # in its last bit — a few ulps in fp32, one rounding step of T in a few bf16 elements
+                if dtype == torch.float32:
+                    assert torch.allclose(y0, y1, rtol=3e-6, atol=1e-6), (rows, hidden, algo)
+                else:
+                    d = (y0.float() - y1.float()).abs()
+                    assert (d <= 2.0 ** -7 * y0.float().abs().clamp_min(1e-3)).all(), (rows, hidden, algo)
+                    assert (d > 0).float().mean() < 0.01, (rows, hidden, algo, (d > 0).float().mean())
+
+    # timing of the 4 MiB message of a 512-sequence decode step against the library collective
+    x = torch.randn(2 * 1024 * 1024, device=dev, generator=g).to(torch.bfloat16)
+    y = x.clone()
+
+    def timed(fn, n=50):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e3
+
+    t1 = timed(lambda: comm.all_reduce(x, out=y, algo="one_shot"))
+    t2 = timed(lambda: comm.all_reduce(x, out=y, algo="two_shot"))
+    t3 = timed(lambda: dist.all_reduce(y))
+    small = torch.randn(8 * 4096, device=dev, generator=g).to(torch.bfloat16)
+    s1 = timed(lambda: comm.all_reduce(small, algo="one_shot"))
+    s3 = timed(lambda: dist.all_reduce(small))
+    assert comm.status() == 0
+    if rank == 0:
+        print(f"TPCOMM world={world} 4MiB: one_shot {t1:.1f} us, two_shot {t2:.1f} us, nccl {t3:.1f} us; "
+              f"64KiB: one_shot {s1:.1f} us, nccl {s3:.1f} us", flush=True)
+    comm.close()
+    dist.destroy_process_group()
+    print(f"rank {rank} OK", flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -76,6 +76,15 @@ SIGNATURES = {
     "zp_qk_norm_rope_store": (_I, [_P] * 5 + [_F] + [_P] * 7 + [_I, _P] + [_I] * 4 + [_L] * 3 + [_I, _P]),
     "zp_sample": (_I, [_P, _P, _P, _P, _I, _I, C.c_uint64, _I, _P]),
     "zp_prepare_decode": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "zp_comm_create": (_I, [_I, _I, _Z, _I, C.POINTER(_P)]),
+    "zp_comm_segment": (_I, [_P, C.POINTER(_P), C.POINTER(_Z)]),
+    "zp_comm_ipc_handle": (_I, [_P, _P]),
+    "zp_comm_open_peer": (_I, [_P, _I, _P]),
+    "zp_comm_attach_peer": (_I, [_P, _I, _P]),
+    "zp_comm_status": (_I, [_P, C.POINTER(C.c_int)]),
+    "zp_comm_destroy": (_I, [_P]),
+    "zp_all_reduce": (_I, [_P, _P, _P, _L, _I, _I, _P]),
+    "zp_all_reduce_add_rms_norm": (_I, [_P] * 6 + [_L, _I, _F, _I, _I, _P]),
 }
 
 _lib = None

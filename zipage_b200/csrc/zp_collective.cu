@@ -1,0 +1,408 @@
+// Tensor-parallel all-reduce over NVLink peer memory, with the residual add + RMSNorm that follows
+// it in a decoder block fused into the same kernel.
+//
+// Replaces, for the row-parallel projections of a decode step, `dist.all_reduce(y)` of
+// RowParallelLinear.forward (third_party/nanovllm/layers/linear.py:149-153) and, fused, the
+// `RMSNorm.add_rms_forward` that consumes its result (third_party/nanovllm/layers/layernorm.py:
+// 28-40; call sites third_party/nanovllm/models/qwen3.py:146-152).
+//
+// Every rank owns one segment of device memory that all ranks of the node map (CUDA IPC, or any
+// mapping the caller attaches): [flags | 2 parities x (input area, result area)].  One launch:
+//   1. each block copies its rows of the input into the local input area of this call's parity,
+//   2. meets the same block of every peer (a flag per (phase, source rank, block) written into
+//      the peer's segment with release/system scope, polled locally with acquire/system scope),
+//   3. one-shot: reads its rows from every rank's input area and sums them in fp32 in rank order
+//      (so every rank gets the same bits), rounding to T once;
+//      two-shot: each rank sums only the 512-byte chunks it owns and stores the result into every
+//      rank's result area, the blocks meet again, and each reads its rows from its own result area,
+//   4. writes the sum, or (fused) adds the residual, writes the new residual, and writes the
+//      RMS-normalised, weighted row — the same arithmetic as the stand-alone RMSNorm kernel.
+// The two parities alternate between calls, so a rank may start the next call while a peer still
+// reads this call's areas; a rank reaches the call after that only after meeting every peer in the
+// call between, by which time the peer's earlier kernel has ended.
+//
+// Every wait is bounded (wall-clock limit given at creation): when it runs out the kernel records
+// ZP_COMM_TIMEOUT in the communicator's status word and finishes without waiting further; the
+// result of that call is undefined and the communicator must be destroyed and built again, but
+// the context stays usable.  Blocks only ever wait for the block of the same index on the peers,
+// and a launch has at most one block per SM, so on a GPU otherwise free of spinning kernels every
+// waiting block's partner gets to run.
+#include "zp_common.cuh"
+
+#include <algorithm>
+#include <cstring>
+#include <new>
+
+namespace zp { namespace coll {
+
+constexpr int MAX_WORLD = 8;
+constexpr int MAX_BLOCKS = 256;
+constexpr int THREADS = 512;
+constexpr int VPT = 2;                                   // 16-byte vectors of a row per thread
+constexpr size_t FLAG_BYTES = 2 * MAX_WORLD * MAX_BLOCKS * sizeof(uint32_t);
+constexpr int STATUS_TIMEOUT = 1;
+
+struct Dev {
+  char* seg[MAX_WORLD];     // every rank's segment as mapped here (seg[rank] is the local one)
+  uint32_t* state;          // local only: [0] epoch, [1] blocks done, [2] status
+  size_t area_bytes;
+  long long timeout_ns;
+  int rank, world;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ long long now_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ int4 ld16_l2(const void* p) {   // L2 only: the line may be a peer's write
+  return __ldcg(reinterpret_cast<const int4*>(p));
+}
+// `seg`: the segment pointers in shared memory (a kernel parameter array indexed by a run-time
+// value would be copied to the stack)
+__device__ __forceinline__ uint32_t* flag_of(char* const* seg, int owner, int phase, int src, int blk) {
+  return reinterpret_cast<uint32_t*>(seg[owner]) + (phase * MAX_WORLD + src) * MAX_BLOCKS + blk;
+}
+__device__ __forceinline__ char* area_of(char* const* seg, size_t area_bytes, int owner, uint32_t parity,
+                                         int which) {
+  return seg[owner] + FLAG_BYTES + (size_t)(parity * 2 + which) * area_bytes;
+}
+
+// All threads of the block have issued their stores; meet the same block of every peer.
+__device__ __forceinline__ void meet_peers(const Dev& c, char* const* seg, int phase, uint32_t epoch) {
+  __threadfence_system();
+  __syncthreads();
+  const int t = threadIdx.x;
+  if (t < c.world && t != c.rank) {
+    st_release_sys(flag_of(seg, t, phase, c.rank, blockIdx.x), epoch);
+    const uint32_t* mine = flag_of(seg, c.rank, phase, t, blockIdx.x);
+    const long long t0 = now_ns();
+    uint32_t spins = 0;
+    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+      if (++spins > 1024u) {
+        __nanosleep(64);
+        if ((spins & 63u) == 0 && now_ns() - t0 > c.timeout_ns) {
+          atomicCAS(c.state + 2, 0u, (uint32_t)STATUS_TIMEOUT);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
+
+template <typename T> struct Pack {
+  static constexpr int N = 16 / sizeof(T);
+  int4 raw;
+  __device__ __forceinline__ float get(int i) const { return Elem<T>::to_f32(reinterpret_cast<const T*>(&raw)[i]); }
+  __device__ __forceinline__ void set(int i, float v) { reinterpret_cast<T*>(&raw)[i] = Elem<T>::from_f32(v); }
+};
+
+// fp32 sum over the ranks, in rank order, of vector `v` of the input areas; rounded to T.
+template <typename T, int WORLD>
+__device__ __forceinline__ int4 reduce_vector(const Dev& c, char* const* seg, uint32_t parity, int64_t v) {
+  constexpr int EPV = Pack<T>::N;
+  Pack<T> x[WORLD];
+#pragma unroll
+  for (int r = 0; r < WORLD; ++r) x[r].raw = ld16_l2(area_of(seg, c.area_bytes, r, parity, 0) + v * 16);
+  Pack<T> o;
+#pragma unroll
+  for (int j = 0; j < EPV; ++j) {
+    float acc = x[0].get(j);
+#pragma unroll
+    for (int r = 1; r < WORLD; ++r) acc += x[r].get(j);
+    o.set(j, acc);
+  }
+  return o.raw;
+}
+
+// Rows of `row_vecs` 16-byte vectors (<= THREADS * VPT); row r belongs to block r % gridDim.x.
+template <typename T, int WORLD, bool TWO_SHOT, bool FUSED>
+__global__ void __launch_bounds__(THREADS)
+all_reduce_kernel(const Dev c, const T* in, T* out, int64_t nvec, int row_vecs, int64_t nrows,
+                  const T* residual, const T* __restrict__ weight, T* residual_out, float eps) {
+  constexpr int EPV = Pack<T>::N;
+  __shared__ uint32_t s_epoch;
+  __shared__ float red[32];
+  __shared__ char* seg[MAX_WORLD];
+  if (threadIdx.x == 0) {
+    s_epoch = *reinterpret_cast<volatile uint32_t*>(c.state) + 1u;
+#pragma unroll
+    for (int r = 0; r < MAX_WORLD; ++r) seg[r] = c.seg[r];
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch, parity = epoch & 1u;
+  char* my_in = area_of(seg, c.area_bytes, c.rank, parity, 0);
+
+  for (int64_t row = blockIdx.x; row < nrows; row += gridDim.x) {
+    const int64_t v0 = row * row_vecs, v1 = min(v0 + row_vecs, nvec);
+    for (int64_t v = v0 + threadIdx.x; v < v1; v += THREADS)
+      st16(my_in + v * 16, ld16(reinterpret_cast<const char*>(in) + v * 16));
+  }
+  meet_peers(c, seg, 0, epoch);
+
+  if constexpr (TWO_SHOT) {
+    for (int64_t row = blockIdx.x; row < nrows; row += gridDim.x) {
+      const int64_t v0 = row * row_vecs, v1 = min(v0 + row_vecs, nvec);
+      for (int64_t v = v0 + threadIdx.x; v < v1; v += THREADS) {
+        if ((int)((v >> 5) % WORLD) != c.rank) continue;   // 512-byte chunks, dealt round-robin
+        const int4 s = reduce_vector<T, WORLD>(c, seg, parity, v);
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r) st16(area_of(seg, c.area_bytes, r, parity, 1) + v * 16, s);
+      }
+    }
+    meet_peers(c, seg, 1, epoch);
+  }
+
+  const char* my_res = area_of(seg, c.area_bytes, c.rank, parity, 1);
+  for (int64_t row = blockIdx.x; row < nrows; row += gridDim.x) {
+    const int64_t v0 = row * row_vecs, v1 = min(v0 + row_vecs, nvec);
+    Pack<T> x[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int64_t v = v0 + threadIdx.x + i * THREADS;
+      if (v < v1) {
+        if constexpr (TWO_SHOT) x[i].raw = ld16_l2(my_res + v * 16);
+        else x[i].raw = reduce_vector<T, WORLD>(c, seg, parity, v);
+      }
+    }
+    if constexpr (!FUSED) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int64_t v = v0 + threadIdx.x + i * THREADS;
+        if (v < v1) st16(reinterpret_cast<char*>(out) + v * 16, x[i].raw);
+      }
+    } else {
+      // s = x + residual (fp32); residual_out = T(s); y = T(T(s * rsqrt(mean(s^2) + eps)) * w)
+      const int H = row_vecs * EPV;
+      float s[VPT][EPV];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int64_t v = v0 + threadIdx.x + i * THREADS;
+        if (v < v1) {
+          Pack<T> b, o;
+          b.raw = ld16(reinterpret_cast<const char*>(residual) + v * 16);
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) {
+            s[i][j] = x[i].get(j) + b.get(j);
+            ss = fmaf(s[i][j], s[i][j], ss);
+            o.set(j, s[i][j]);
+          }
+          st16(reinterpret_cast<char*>(residual_out) + v * 16, o.raw);
+        }
+      }
+      ss = block_sum(ss, red);
+      const float rinv = 1.f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int64_t v = v0 + threadIdx.x + i * THREADS;
+        if (v < v1) {
+          Pack<T> w, o;
+          w.raw = ld16(reinterpret_cast<const char*>(weight) + (v - v0) * 16);
+#pragma unroll
+          for (int j = 0; j < EPV; ++j)
+            o.set(j, __fmul_rn(round_to<T>(__fmul_rn(s[i][j], rinv)), w.get(j)));
+          st16(reinterpret_cast<char*>(out) + v * 16, o.raw);
+        }
+      }
+      __syncthreads();   // `red` is reused by the next row
+    }
+  }
+
+  // the last block to finish advances the epoch for the next launch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(c.state + 1, 1u) == gridDim.x - 1) {
+      c.state[1] = 0;
+      c.state[0] = epoch;
+      __threadfence();
+    }
+  }
+}
+
+}}  // namespace zp::coll
+
+struct zp_comm {
+  int rank = 0, world = 0, device = 0, sms = 0;
+  size_t area_bytes = 0;
+  char* seg[zp::coll::MAX_WORLD] = {};
+  bool ipc_opened[zp::coll::MAX_WORLD] = {};
+  uint32_t* state = nullptr;
+  long long timeout_ns = 0;
+};
+
+namespace {
+
+size_t segment_bytes(size_t area_bytes) { return zp::coll::FLAG_BYTES + 4 * area_bytes; }
+
+template <typename T, int WORLD>
+void launch(const zp_comm* c, bool two_shot, bool fused, const void* in, void* out, int64_t nvec,
+            int row_vecs, int64_t nrows, const void* residual, const void* weight, void* residual_out,
+            float eps, cudaStream_t st) {
+  using namespace zp::coll;
+  Dev d;
+  for (int r = 0; r < MAX_WORLD; ++r) d.seg[r] = c->seg[r];
+  d.state = c->state; d.area_bytes = c->area_bytes; d.timeout_ns = c->timeout_ns;
+  d.rank = c->rank; d.world = c->world;
+  const int grid = (int)std::min<int64_t>(nrows, std::min(c->sms, MAX_BLOCKS));
+  auto go = [&](auto kernel) {
+    kernel<<<grid, THREADS, 0, st>>>(d, (const T*)in, (T*)out, nvec, row_vecs, nrows, (const T*)residual,
+                                     (const T*)weight, (T*)residual_out, eps);
+  };
+  if (two_shot) { if (fused) go(all_reduce_kernel<T, WORLD, true, true>); else go(all_reduce_kernel<T, WORLD, true, false>); }
+  else          { if (fused) go(all_reduce_kernel<T, WORLD, false, true>); else go(all_reduce_kernel<T, WORLD, false, false>); }
+}
+
+int run(zp_comm* c, int algo, bool fused, const void* in, void* out, int64_t nvec, int row_vecs,
+        int64_t nrows, const void* residual, const void* weight, void* residual_out, float eps, int dtype,
+        void* stream, const char* what) {
+  using namespace zp::coll;
+  ZP_REQUIRE(c && c->state, "%s: null communicator", what);
+  for (int r = 0; r < c->world; ++r) ZP_REQUIRE(c->seg[r], "%s: the segment of rank %d is not attached", what, r);
+  ZP_REQUIRE(algo >= 0 && algo <= 2, "%s: algorithm %d (0 auto, 1 one-shot, 2 two-shot)", what, algo);
+  ZP_REQUIRE((size_t)nvec * 16 <= c->area_bytes, "%s: %lld bytes exceed the communicator's %zu", what,
+             (long long)nvec * 16, c->area_bytes);
+  ZP_REQUIRE(((uintptr_t)in | (uintptr_t)out | (uintptr_t)residual | (uintptr_t)weight | (uintptr_t)residual_out) % 16 == 0,
+             "%s: pointers must be 16-byte aligned", what);
+  if (nvec == 0) return ZP_OK;
+  // one-shot moves (world-1) x the message into every GPU, two-shot 2 x (world-1)/world of it
+  const bool two_shot = algo == 2 || (algo == 0 && c->world > 2 && (size_t)nvec * 16 >= (512u << 10));
+  cudaStream_t st = (cudaStream_t)stream;
+#define ZP_COLL_WORLD(W) \
+  ZP_DISPATCH_DTYPE(dtype, T, (launch<T, W>(c, two_shot, fused, in, out, nvec, row_vecs, nrows, residual, weight, residual_out, eps, st)))
+  switch (c->world) {
+    case 2: ZP_COLL_WORLD(2); break;
+    case 4: ZP_COLL_WORLD(4); break;
+    case 8: ZP_COLL_WORLD(8); break;
+    default: zp::set_error("%s: world size %d (2, 4 or 8)", what, c->world); return ZP_ERR_INVALID_ARGUMENT;
+  }
+#undef ZP_COLL_WORLD
+  return zp::check_launch(what);
+}
+
+}  // namespace
+
+extern "C" int zp_comm_create(int rank, int world, size_t max_bytes, int timeout_ms, zp_comm** out) {
+  using namespace zp::coll;
+  ZP_REQUIRE(out, "zp_comm_create: null output");
+  ZP_REQUIRE(world == 2 || world == 4 || world == 8, "zp_comm_create: world size %d (2, 4 or 8)", world);
+  ZP_REQUIRE(rank >= 0 && rank < world, "zp_comm_create: rank %d of %d", rank, world);
+  ZP_REQUIRE(max_bytes > 0 && timeout_ms > 0, "zp_comm_create: max_bytes and timeout_ms must be positive");
+  zp_comm* c = new (std::nothrow) zp_comm();
+  ZP_REQUIRE(c, "zp_comm_create: out of host memory");
+  c->rank = rank; c->world = world;
+  c->area_bytes = (max_bytes + 255) / 256 * 256;
+  c->timeout_ns = (long long)timeout_ms * 1000000ll;
+  cudaError_t e = cudaGetDevice(&c->device);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&c->sms, cudaDevAttrMultiProcessorCount, c->device);
+  void* seg = nullptr; void* state = nullptr;
+  if (e == cudaSuccess) e = cudaMalloc(&seg, segment_bytes(c->area_bytes));
+  if (e == cudaSuccess) e = cudaMemset(seg, 0, FLAG_BYTES);
+  if (e == cudaSuccess) e = cudaMalloc(&state, 256);
+  if (e == cudaSuccess) e = cudaMemset(state, 0, 256);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    zp::set_error("zp_comm_create: %s", cudaGetErrorString(e));
+    if (seg) cudaFree(seg);
+    if (state) cudaFree(state);
+    delete c;
+    return ZP_ERR_CUDA;
+  }
+  c->seg[rank] = (char*)seg;
+  c->state = (uint32_t*)state;
+  *out = c;
+  return ZP_OK;
+}
+
+extern "C" int zp_comm_segment(zp_comm* c, void** ptr_out, size_t* bytes_out) {
+  ZP_REQUIRE(c && ptr_out && bytes_out, "zp_comm_segment: null pointer");
+  *ptr_out = c->seg[c->rank];
+  *bytes_out = segment_bytes(c->area_bytes);
+  return ZP_OK;
+}
+
+extern "C" int zp_comm_ipc_handle(zp_comm* c, void* handle64) {
+  ZP_REQUIRE(c && handle64, "zp_comm_ipc_handle: null pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, c->seg[c->rank]);
+  if (e != cudaSuccess) { zp::set_error("zp_comm_ipc_handle: %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
+  memcpy(handle64, &h, 64);
+  return ZP_OK;
+}
+
+extern "C" int zp_comm_open_peer(zp_comm* c, int peer, const void* handle64) {
+  ZP_REQUIRE(c && handle64, "zp_comm_open_peer: null pointer");
+  ZP_REQUIRE(peer >= 0 && peer < c->world && peer != c->rank, "zp_comm_open_peer: peer %d", peer);
+  ZP_REQUIRE(!c->seg[peer], "zp_comm_open_peer: peer %d is attached already", peer);
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) { zp::set_error("zp_comm_open_peer: %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
+  c->seg[peer] = (char*)p;
+  c->ipc_opened[peer] = true;
+  return ZP_OK;
+}
+
+extern "C" int zp_comm_attach_peer(zp_comm* c, int peer, void* segment) {
+  ZP_REQUIRE(c && segment, "zp_comm_attach_peer: null pointer");
+  ZP_REQUIRE(peer >= 0 && peer < c->world && peer != c->rank, "zp_comm_attach_peer: peer %d", peer);
+  ZP_REQUIRE(!c->seg[peer], "zp_comm_attach_peer: peer %d is attached already", peer);
+  c->seg[peer] = (char*)segment;
+  return ZP_OK;
+}
+
+extern "C" int zp_comm_status(zp_comm* c, int* status_out) {
+  ZP_REQUIRE(c && status_out, "zp_comm_status: null pointer");
+  uint32_t v = 0;
+  cudaError_t e = cudaMemcpy(&v, c->state + 2, sizeof(v), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) { zp::set_error("zp_comm_status: %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
+  *status_out = (int)v;
+  return ZP_OK;
+}
+
+extern "C" int zp_comm_destroy(zp_comm* c) {
+  if (!c) return ZP_OK;
+  cudaDeviceSynchronize();
+  for (int r = 0; r < c->world; ++r)
+    if (c->ipc_opened[r]) cudaIpcCloseMemHandle(c->seg[r]);
+  if (c->seg[c->rank]) cudaFree(c->seg[c->rank]);
+  if (c->state) cudaFree(c->state);
+  delete c;
+  return ZP_OK;
+}
+
+extern "C" int zp_all_reduce(zp_comm* c, const void* in, void* out, int64_t count, int dtype, int algo,
+                             void* stream) {
+  ZP_REQUIRE(in && out, "zp_all_reduce: null pointer");
+  ZP_REQUIRE(count >= 0 && (count * (int64_t)zp::dtype_size(dtype)) % 16 == 0,
+             "zp_all_reduce: the message must be a multiple of 16 bytes");
+  const int64_t nvec = count * (int64_t)zp::dtype_size(dtype) / 16;
+  const int row_vecs = zp::coll::THREADS * zp::coll::VPT;
+  return run(c, algo, false, in, out, nvec, row_vecs, (nvec + row_vecs - 1) / row_vecs, nullptr, nullptr,
+             nullptr, 0.f, dtype, stream, "zp_all_reduce");
+}
+
+extern "C" int zp_all_reduce_add_rms_norm(zp_comm* c, const void* in, const void* residual, const void* weight,
+                                          void* out, void* residual_out, int64_t rows, int hidden, float eps,
+                                          int dtype, int algo, void* stream) {
+  ZP_REQUIRE(in && residual && weight && out && residual_out, "zp_all_reduce_add_rms_norm: null pointer");
+  const int64_t row_bytes = (int64_t)hidden * (int64_t)zp::dtype_size(dtype);
+  ZP_REQUIRE(rows >= 0 && hidden > 0 && row_bytes % 16 == 0 &&
+                 row_bytes / 16 <= zp::coll::THREADS * zp::coll::VPT,
+             "zp_all_reduce_add_rms_norm: a row must be a multiple of 16 bytes and at most %d bytes",
+             zp::coll::THREADS * zp::coll::VPT * 16);
+  return run(c, algo, true, in, out, rows * (row_bytes / 16), (int)(row_bytes / 16), rows, residual, weight,
+             residual_out, eps, dtype, stream, "zp_all_reduce_add_rms_norm");
+}

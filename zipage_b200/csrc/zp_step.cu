@@ -424,12 +424,18 @@ prepare_decode_kernel(const int32_t* __restrict__ num_tokens, const int32_t* __r
       int len = 0;
       while (len < W && block_tables[(int64_t)i * W + len] != -1) ++len;
       const int last_page = len > 0 ? block_tables[(int64_t)i * W + len - 1] : 0;
-      positions[i] = n - 1;
-      context_lens[i] = (len - 1) * bs + last;
-      slot_mapping[i] = last_page * bs + last - 1;
-      qid = query_ids[i];
-      flag = qid != -1 && last > bs - qcl;
-      widx = last - (bs - qcl) - 1;
+      if (n > 0 && len > 0) {
+        positions[i] = n - 1;
+        context_lens[i] = (len - 1) * bs + last;
+        slot_mapping[i] = last_page * bs + last - 1;
+        qid = query_ids[i];
+        flag = qid != -1 && last > bs - qcl;
+        widx = last - (bs - qcl) - 1;
+      } else {  // a padding row of a fixed-size (graph) batch: nothing is stored, nothing attended
+        positions[i] = 0;
+        context_lens[i] = 0;
+        slot_mapping[i] = -1;
+      }
     }
     // exclusive scan of `flag` over the block
     int incl = flag;

@@ -11,7 +11,7 @@ import torch
 from torch import nn
 
 from .. import _lib as L
-from ..kernel import store_kvcache, store_query_cache
+from ..kernel import _count, store_kvcache, store_query_cache
 from ..utils.context import get_context
 
 _ws_cache: dict = {}
@@ -43,6 +43,7 @@ def paged_decode_attention(q, k_cache, v_cache, cache_seqlens, block_table, soft
                                 L.ptr(block_table), L.ptr(out), B, block_table.shape[1], Hq, Hkv, D,
                                 BS, k_cache.stride(0), float(softmax_scale), L.dtype_code(q),
                                 L.ptr(ws), ws.numel(), L.stream_ptr()), "paged_decode_attention")
+    _count(1)
     return out
 
 
@@ -73,6 +74,7 @@ def varlen_prefill_attention(q, k, v, max_seqlen_q, cu_seqlens_q, max_seqlen_k, 
                                           float(softmax_scale), q.shape[0], total_k, L.IMPL[impl],
                                           L.dtype_code(q), L.stream_ptr()),
             "varlen_prefill_attention")
+    _count(1)
     return out
 
 
@@ -95,6 +97,13 @@ class Attention(nn.Module):
             store_kvcache(k, v, k_cache, v_cache, context.slot_mapping)
         if context.query_slot_mapping is not None:
             store_query_cache(q, self.q_cache, context.query_slot_mapping)
+        return self.attend(q, k, v)
+
+    def attend(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
+        """The attention call alone, for callers that wrote the caches already (the fused
+        q/k normalisation + rotation + store launch)."""
+        context = get_context()
+        k_cache, v_cache = self.k_cache, self.v_cache
         if context.is_prefill:
             if context.block_tables is not None:  # prefix cache: keys come from the pages
                 k, v = k_cache, v_cache
