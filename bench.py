@@ -46,11 +46,13 @@ def parse_args():
     ap.add_argument("--kernel-impl", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--also-exact", action="store_true", help="time the exact variant as well")
-    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops", "prefill", "decode_step"],
+    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops", "prefill", "decode_step", "tp_allreduce"],
                     help="compress (default, the headline op), decode (paged decode attention kernel) or "
                          "step_ops (the element-wise ops of a decoder layer step and the sampler) or "
                          "prefill (varlen causal prefill attention, one layer) or decode_step (the decode "
-                         "forward of Qwen3-8B-shaped blocks, launch by launch and as a replayed CUDA graph)")
+                         "forward of Qwen3-8B-shaped blocks, launch by launch and as a replayed CUDA graph) or "
+                         "tp_allreduce (the row-parallel projections' all-reduce + residual + RMSNorm over "
+                         "peer memory against the library collective; needs --gpus >= 2 under torchrun)")
     ap.add_argument("--tokens", type=int, default=32768, help="tokens per call of the step_ops workload")
     return ap.parse_args()
 
@@ -365,6 +367,125 @@ def run_decode_step(args):
     }))
 
 
+def run_tp_allreduce(args):
+    """The all-reduce of a row-parallel projection's output for a 512-sequence decode step of a
+    hidden-4096 model (4 MiB of bf16 per rank) followed by the residual add + RMSNorm of the block:
+    one fused launch over peer memory against dist.all_reduce + the RMSNorm kernel.  A step = one
+    such reduction, `steps` of them replayed as one CUDA graph; times are CUDA events, the maximum
+    over the ranks."""
+    import torch
+    import torch.distributed as dist
+    from zipage_b200.layers.step_ops import rms_norm
+    from zipage_b200.layers.tp_comm import TPCommunicator
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world < 2:
+        print(json.dumps({"metric": "allreduce_add_rms_norm_us", "unavailable": "needs 2, 4 or 8 ranks (torchrun)"}))
+        return
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    rank = dist.get_rank()
+    rows, hidden = args.batch, 4096
+    comm = TPCommunicator(max_bytes=rows * hidden * 2)
+    g = torch.Generator(device=dev).manual_seed(rank)
+    x = torch.randn(rows, hidden, device=dev, generator=g).to(torch.bfloat16)
+    res = torch.randn(rows, hidden, device=dev, generator=g).to(torch.bfloat16)
+    w = torch.ones(hidden, device=dev, dtype=torch.bfloat16)
+    y = x.clone()
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps * 1e3], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def nccl_step():
+        y.copy_(x)
+        dist.all_reduce(y)
+        rms_norm(y, w, 1e-6, res)
+
+    cases = {
+        "fused_auto": lambda: comm.all_reduce_add_rms_norm(x, res, w, 1e-6),
+        "fused_one_shot": lambda: comm.all_reduce_add_rms_norm(x, res, w, 1e-6, algo="one_shot"),
+        "fused_two_shot": lambda: comm.all_reduce_add_rms_norm(x, res, w, 1e-6, algo="two_shot"),
+        "plain_one_shot": lambda: comm.all_reduce(x, out=y, algo="one_shot"),
+        "plain_two_shot": lambda: comm.all_reduce(x, out=y, algo="two_shot"),
+        "nccl_all_reduce": lambda: dist.all_reduce(y),
+        "nccl_all_reduce_then_rms_norm": nccl_step,
+    }
+    # Launch by launch, a 20 us collective is bound by the host's call overhead on both sides of the
+    # comparison; the device time shows when `steps` calls are replayed as one CUDA graph (which is
+    # how a decode step issues them).
+    def graphed(fn):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(); dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(args.steps):
+                fn()
+        return graph
+
+    graphs = {k: graphed(fn) for k, fn in cases.items()}
+
+    def timed_graph(graph):
+        graph.replay()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps * 1e3], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    runs = {k: [] for k in cases}
+    gruns = {k: [] for k in cases}
+    with ClockSampler(dev.index or 0) as clocks:
+        for _ in range(3):            # three rounds over all cases; the median of each is reported
+            for k, fn in cases.items():
+                runs[k].append(timed(fn))
+                gruns[k].append(timed_graph(graphs[k]))
+    t_eager = {k: sorted(v)[1] for k, v in runs.items()}
+    t = {k: sorted(v)[1] for k, v in gruns.items()}
+    del graphs
+    status = comm.status()
+    comm.close()
+    msg = rows * hidden * 2
+    two_shot = world > 2
+    link_bytes = msg * (2 * (world - 1) / world if two_shot else world - 1)   # into each GPU
+    target_us = link_bytes / 770e9 * 1e6
+    if rank == 0:
+        print(json.dumps({
+            "metric": "allreduce_add_rms_norm_us", "value": t["fused_auto"], "unit": "us", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": t["fused_auto"] / 1e3,
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "all-reduce + residual + RMSNorm of one row-parallel projection, decode step",
+                       "rows": rows, "hidden": hidden, "message_bytes": msg,
+                       "l2": "4 MiB messages live in L2 by design; no flush"},
+            "times_us": t, "launch_by_launch_times_us": t_eager, "comm_status": status,
+            "gpu_launches": args.steps * 3 * 5 * 2, "clocks": clocks.summary(),
+            "roofline": {"bound": "nvlink", "kernel": "all_reduce_kernel (fused)", "bytes_into_each_gpu": link_bytes,
+                         "peak": 770.0, "unit": "GB/s", "achieved": link_bytes / (t["fused_auto"] * 1e-6) / 1e9,
+                         "frac": target_us / t["fused_auto"], "peak_source": "measured peer copy, per direction",
+                         "traffic": None},
+        }))
+    dist.destroy_process_group()
+
+
 def run_step_ops(args):
     """The per-step ops of one decoder layer at Qwen3-8B sizes (hidden 4096, intermediate 12288,
     32 query / 8 KV heads of 128) on a prefill-sized batch of tokens, so that every input is larger
@@ -508,6 +629,8 @@ def main():
         return run_step_ops(args)
     if args.workload == "decode_step":
         return run_decode_step(args)
+    if args.workload == "tp_allreduce":
+        return run_tp_allreduce(args)
 
     import torch
     import torch.distributed as dist

@@ -74,15 +74,17 @@ def test_argument_checks():
         lib.zp_comm_destroy(h)
 
 
-def test_all_reduce_on_two_gpus():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_all_reduce_across_gpus(world):
     _gpu()
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
     r = subprocess.run(
-        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-         "--master-addr", "127.0.0.1", "--master-port", "29731", str(ROOT / "tests" / "tp_comm_worker.py")],
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+         "--master-addr", "127.0.0.1", "--master-port", str(29731 + world), str(ROOT / "tests" / "tp_comm_worker.py")],
         capture_output=True, text=True, timeout=420, env=env)
     sys.stdout.write(r.stdout[-3000:])
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert "rank 0 OK" in r.stdout and "rank 1 OK" in r.stdout
+    assert all(f"rank {i} OK" in r.stdout for i in range(world))
+    print([ln for ln in r.stdout.splitlines() if ln.startswith("TPCOMM")])

@@ -10,7 +10,7 @@
 // mapping the caller attaches): [flags | 2 parities x (input area, result area)].  One launch:
 //   1. each block copies its rows of the input into the local input area of this call's parity,
 //   2. meets the same block of every peer (a flag per (phase, source rank, block) written into
-//      the peer's segment with release/system scope, polled locally with acquire/system scope),
+//      the peer's segment with release/system scope, polled locally, then an acquire fence),
 //   3. one-shot: reads its rows from every rank's input area and sums them in fp32 in rank order
 //      (so every rank gets the same bits), rounding to T once;
 //      two-shot: each rank sums only the 512-byte chunks it owns and stores the result into every
@@ -50,11 +50,6 @@ struct Dev {
   int rank, world;
 };
 
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -76,9 +71,17 @@ __device__ __forceinline__ char* area_of(char* const* seg, size_t area_bytes, in
   return seg[owner] + FLAG_BYTES + (size_t)(parity * 2 + which) * area_bytes;
 }
 
-// All threads of the block have issued their stores; meet the same block of every peer.
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// All threads of the block have issued their stores; meet the same block of every peer.  The
+// block barrier orders every thread's stores before the signalling thread's release (which is
+// cumulative), and the signalling thread's acquire fence before every thread's later loads, so
+// only the threads that signal pay for system-scope fences; the poll itself is a relaxed load.
 __device__ __forceinline__ void meet_peers(const Dev& c, char* const* seg, int phase, uint32_t epoch) {
-  __threadfence_system();
   __syncthreads();
   const int t = threadIdx.x;
   if (t < c.world && t != c.rank) {
@@ -86,8 +89,8 @@ __device__ __forceinline__ void meet_peers(const Dev& c, char* const* seg, int p
     const uint32_t* mine = flag_of(seg, c.rank, phase, t, blockIdx.x);
     const long long t0 = now_ns();
     uint32_t spins = 0;
-    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
-      if (++spins > 1024u) {
+    while ((int32_t)(ld_relaxed_sys(mine) - epoch) < 0) {
+      if (++spins > 4096u) {
         __nanosleep(64);
         if ((spins & 63u) == 0 && now_ns() - t0 > c.timeout_ns) {
           atomicCAS(c.state + 2, 0u, (uint32_t)STATUS_TIMEOUT);
@@ -95,6 +98,7 @@ __device__ __forceinline__ void meet_peers(const Dev& c, char* const* seg, int p
         }
       }
     }
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
   }
   __syncthreads();
 }
@@ -162,18 +166,47 @@ all_reduce_kernel(const Dev c, const T* in, T* out, int64_t nvec, int row_vecs, 
     meet_peers(c, seg, 1, epoch);
   }
 
-  const char* my_res = area_of(seg, c.area_bytes, c.rank, parity, 1);
+  // The raw vectors of the block's next row are requested before the current row is summed and
+  // normalised, so that a row's round trip over the link overlaps the previous row's arithmetic.
+  constexpr int NSRC = TWO_SHOT ? 1 : WORLD;
+  const char* src[NSRC];
+#pragma unroll
+  for (int r = 0; r < NSRC; ++r) src[r] = area_of(seg, c.area_bytes, TWO_SHOT ? c.rank : r, parity, TWO_SHOT ? 1 : 0);
+  Pack<T> raw[VPT][NSRC];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+#pragma unroll
+    for (int r = 0; r < NSRC; ++r) raw[i][r].raw = make_int4(0, 0, 0, 0);
+  auto request = [&](int64_t row) {
+    const int64_t v0 = row * row_vecs, v1 = min(v0 + row_vecs, nvec);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int64_t v = v0 + threadIdx.x + i * THREADS;
+      if (v < v1) {
+#pragma unroll
+        for (int r = 0; r < NSRC; ++r) raw[i][r].raw = ld16_l2(src[r] + v * 16);
+      }
+    }
+  };
+  if ((int64_t)blockIdx.x < nrows) request(blockIdx.x);
   for (int64_t row = blockIdx.x; row < nrows; row += gridDim.x) {
     const int64_t v0 = row * row_vecs, v1 = min(v0 + row_vecs, nvec);
     Pack<T> x[VPT];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const int64_t v = v0 + threadIdx.x + i * THREADS;
-      if (v < v1) {
-        if constexpr (TWO_SHOT) x[i].raw = ld16_l2(my_res + v * 16);
-        else x[i].raw = reduce_vector<T, WORLD>(c, seg, parity, v);
+      if constexpr (TWO_SHOT) {
+        x[i] = raw[i][0];
+      } else {   // fp32 sum in rank order, one rounding
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) {
+          float acc = raw[i][0].get(j);
+#pragma unroll
+          for (int r = 1; r < WORLD; ++r) acc += raw[i][r].get(j);
+          x[i].set(j, acc);
+        }
       }
     }
+    if (row + gridDim.x < nrows) request(row + gridDim.x);
     if constexpr (!FUSED) {
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
