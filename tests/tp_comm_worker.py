@@ -79,6 +79,27 @@ def main():
                     assert (d <= 2.0 ** -7 * y0.float().abs().clamp_min(1e-3)).all(), (rows, hidden, algo)
                     assert (d > 0).float().mean() < 0.01, (rows, hidden, algo, (d > 0).float().mean())
 
+    # sampling over a sharded vocabulary == the single-GPU sampler on the concatenated logits
+    # (and the CPU oracle), with given draws and with the built-in generator
+    from oracle import step_ops_oracle as S
+    from zipage_b200.layers.step_ops import sample
+    for dtype, B, Vs in ((torch.bfloat16, 37, 5000), (torch.bfloat16, 300, 1001), (torch.float32, 64, 4096),
+                         (torch.float16, 5, 75968)):
+        torch.manual_seed(3)                                  # replicated inputs
+        V = Vs * world
+        full = (3 * torch.randn(B, V)).to(dtype).to(dev)
+        temps = (0.3 + torch.rand(B)).to(dev)
+        draws = torch.empty(B, V).exponential_(1.0).to(dev)
+        sl = slice(rank * Vs, (rank + 1) * Vs)
+        tok = comm.sample(full[:, sl].contiguous(), temps, noise_shard=draws[:, sl].contiguous())
+        assert torch.equal(tok, sample(full, temps, noise=draws)), (dtype, B, Vs)
+        assert torch.equal(tok.cpu(), S.sample_race(full.cpu(), temps.cpu(), draws.cpu())), (dtype, B, Vs)
+        tok = comm.sample(full[:, sl].contiguous(), temps, seed=11)
+        assert torch.equal(tok, sample(full, temps, seed=11)), (dtype, B, Vs, "generator")
+        gathered = [torch.empty_like(tok) for _ in range(world)]
+        dist.all_gather(gathered, tok)
+        assert all(torch.equal(t, tok) for t in gathered)
+
     # timing of the 4 MiB message of a 512-sequence decode step against the library collective
     x = torch.randn(2 * 1024 * 1024, device=dev, generator=g).to(torch.bfloat16)
     y = x.clone()
@@ -100,6 +121,22 @@ def main():
     small = torch.randn(8 * 4096, device=dev, generator=g).to(torch.bfloat16)
     s1 = timed(lambda: comm.all_reduce(small, algo="one_shot"))
     s3 = timed(lambda: dist.all_reduce(small))
+    # the reference's route for 512 rows of a 151 936-token vocabulary: gather the shards to rank 0,
+    # concatenate, sample there
+    Vs = 151936 // world
+    shard = torch.randn(512, Vs, device=dev, generator=g).to(torch.bfloat16)
+    temps = torch.full((512,), 0.7, device=dev)
+    parts = [torch.empty_like(shard) for _ in range(world)] if rank == 0 else None
+
+    def gather_route():
+        dist.gather(shard, parts, 0)
+        if rank == 0:
+            sample(torch.cat(parts, -1), temps, seed=5)
+
+    g1 = timed(lambda: comm.sample(shard, temps, seed=5), 20)
+    g2 = timed(gather_route, 20)
+    if rank == 0:
+        print(f"TPCOMM world={world} sampler 512 x 151936: sharded {g1:.1f} us, gather + sample on rank 0 {g2:.1f} us", flush=True)
     assert comm.status() == 0
     if rank == 0:
         print(f"TPCOMM world={world} 4MiB: one_shot {t1:.1f} us, two_shot {t2:.1f} us, nccl {t3:.1f} us; "

@@ -263,6 +263,179 @@ all_reduce_kernel(const Dev c, const T* in, T* out, int64_t nvec, int row_vecs, 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Sampler over a vocabulary sharded across the ranks, without gathering the logits.
+// Every rank holds logits[:, rank * Vs : (rank + 1) * Vs].  One launch on every rank:
+//   A. per row: the shard's maximum m_r of logits / t and z_r = sum exp(x / t - m_r); both pushed
+//      into every rank's input area; meeting;
+//   B. per row: M = max m_r, Z = sum z_r exp(m_r - M) (rank order: the same bits everywhere); the
+//      race e_i / q_i over the shard with fast arithmetic, the two best candidates per thread
+//      re-evaluated with the reference's expression (exp(x / t - M) / Z) / q, the shard's winner
+//      (value, global index) pushed into every rank's result area; meeting;
+//   C. per row: the best of the ranks' winners (larger value, then lower index) -> tokens_out.
+// All ranks end with the same tokens.  The draws of the built-in generator are keyed by the
+// global index, so they do not depend on the sharding.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ float exp1_draw(uint64_t seed, uint32_t row, uint32_t i) {   // as zp_sample
+  uint32_t h = mix32(((uint32_t)seed ^ (row * 0x9e3779b9u)) + i * 0x85ebca6bu);
+  h = mix32(h ^ (uint32_t)(seed >> 32) ^ row);
+  const float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
+  return -__logf(u);
+}
+
+constexpr int SAMPLE_THREADS = 1024;
+
+template <typename T, int WORLD>
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_sharded_kernel(const Dev c, const T* __restrict__ logits, const float* __restrict__ temperatures,
+                      const float* __restrict__ noise, int64_t* __restrict__ out, int rows, int Vs,
+                      uint64_t seed) {
+  constexpr int EPV = Pack<T>::N;
+  __shared__ uint32_t s_epoch;
+  __shared__ char* seg[MAX_WORLD];
+  __shared__ float red[32];
+  __shared__ float bval[32];
+  __shared__ int bidx[32];
+  if (threadIdx.x == 0) {
+    s_epoch = *reinterpret_cast<volatile uint32_t*>(c.state) + 1u;
+#pragma unroll
+    for (int r = 0; r < MAX_WORLD; ++r) seg[r] = c.seg[r];
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch, parity = epoch & 1u;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+
+  auto for_each = [&](const T* lr, auto&& fn) {   // a thread sees its elements in ascending order
+    const int nvec = ((uintptr_t)lr % 16 == 0) ? Vs / EPV : 0;
+#pragma unroll 2
+    for (int v = threadIdx.x; v < nvec; v += SAMPLE_THREADS) {
+      Pack<T> a;
+      a.raw = ld16(lr + v * EPV);
+#pragma unroll
+      for (int j = 0; j < EPV; ++j) fn(v * EPV + j, a.get(j));
+    }
+    for (int i = nvec * EPV + threadIdx.x; i < Vs; i += SAMPLE_THREADS) fn(i, Elem<T>::to_f32(lr[i]));
+  };
+
+  // ---- A: shard statistics ----
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* lr = logits + (int64_t)row * Vs;
+    const float t = temperatures[row];
+    float mx = -INFINITY;
+    if (t > 0.f) {   // the correctly rounded quotient is monotonic in the numerator
+      for_each(lr, [&](int, float x) { mx = fmaxf(mx, x); });
+      mx = __fdiv_rn(block_max(mx, red), t);
+    } else {
+      for_each(lr, [&](int, float x) { mx = fmaxf(mx, __fdiv_rn(x, t)); });
+      mx = block_max(mx, red);
+    }
+    const float inv_t = 1.f / t;
+    float z = 0.f;
+    for_each(lr, [&](int, float x) { z += __expf(fmaf(x, inv_t, -mx)); });
+    z = block_sum(z, red);
+    if (threadIdx.x < WORLD)
+      *reinterpret_cast<float2*>(area_of(seg, c.area_bytes, threadIdx.x, parity, 0) +
+                                 ((size_t)c.rank * rows + row) * 8) = make_float2(mx, z);
+    __syncthreads();
+  }
+  meet_peers(c, seg, 0, epoch);
+
+  // ---- B: the race over the shard against the global maximum and sum ----
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* lr = logits + (int64_t)row * Vs;
+    const float t = temperatures[row];
+    float ms[WORLD], zs[WORLD];
+    float m = -INFINITY;
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) {
+      const float2 st = __ldcg(reinterpret_cast<const float2*>(area_of(seg, c.area_bytes, c.rank, parity, 0) +
+                                                                ((size_t)r * rows + row) * 8));
+      ms[r] = st.x; zs[r] = st.y;
+      m = fmaxf(m, st.x);
+    }
+    float zsum = 0.f;
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) zsum += zs[r] * expf(ms[r] - m);
+    const float inv_t = 1.f / t;
+    const int64_t nbase = (int64_t)row * Vs;
+    const uint32_t gbase = (uint32_t)c.rank * (uint32_t)Vs;
+    float r0 = -INFINITY, r1 = -INFINITY, q0 = 1.f, q1 = 1.f;
+    int i0 = 0x7fffffff, i1 = 0x7fffffff;
+    for_each(lr, [&](int i, float x) {
+      const float e = __expf(fmaf(x, inv_t, -m));
+      const float q = fmaxf(noise ? noise[nbase + i] : exp1_draw(seed, row, gbase + i), 1e-10f);
+      const float r = __fdividef(e, q);
+      if (r > r1) {
+        if (r > r0) { r1 = r0; q1 = q0; i1 = i0; r0 = r; q0 = q; i0 = i; }
+        else { r1 = r; q1 = q; i1 = i; }
+      }
+    });
+    auto exact = [&](int i, float q) -> float {   // the reference's value of a candidate
+      if (i == 0x7fffffff) return -INFINITY;
+      const float e = expf(__fdiv_rn(Elem<T>::to_f32(lr[i]), t) - m);
+      return __fdiv_rn(__fdiv_rn(e, zsum), q);
+    };
+    const float v0 = exact(i0, q0), v1 = exact(i1, q1);
+    float best = v0;
+    int besti = i0;
+    if (v1 > best || (v1 == best && i1 < besti)) { best = v1; besti = i1; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+      if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+    }
+    if (lane == 0) { bval[w] = best; bidx[w] = besti; }
+    __syncthreads();
+    if (w == 0) {
+      best = bval[lane]; besti = bidx[lane];   // SAMPLE_THREADS / 32 == 32 warps
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+        if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+      }
+      if (lane < WORLD) {
+        const int gi = besti == 0x7fffffff ? 0x7fffffff : (int)gbase + besti;
+        *reinterpret_cast<float2*>(area_of(seg, c.area_bytes, lane, parity, 1) +
+                                   ((size_t)c.rank * rows + row) * 8) = make_float2(best, __int_as_float(gi));
+      }
+    }
+    __syncthreads();
+  }
+  meet_peers(c, seg, 1, epoch);
+
+  // ---- C: the best of the shards' winners ----
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    if (threadIdx.x == 0) {
+      float best = -INFINITY;
+      int besti = 0x7fffffff;
+#pragma unroll
+      for (int r = 0; r < WORLD; ++r) {
+        const float2 cnd = __ldcg(reinterpret_cast<const float2*>(area_of(seg, c.area_bytes, c.rank, parity, 1) +
+                                                                   ((size_t)r * rows + row) * 8));
+        const int ci = __float_as_int(cnd.y);
+        if (cnd.x > best || (cnd.x == best && ci < besti)) { best = cnd.x; besti = ci; }
+      }
+      out[row] = besti;
+    }
+  }
+
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(c.state + 1, 1u) == gridDim.x - 1) {
+      c.state[1] = 0;
+      c.state[0] = epoch;
+      __threadfence();
+    }
+  }
+}
+
 }}  // namespace zp::coll
 
 struct zp_comm {
@@ -438,4 +611,36 @@ extern "C" int zp_all_reduce_add_rms_norm(zp_comm* c, const void* in, const void
              zp::coll::THREADS * zp::coll::VPT * 16);
   return run(c, algo, true, in, out, rows * (row_bytes / 16), (int)(row_bytes / 16), rows, residual, weight,
              residual_out, eps, dtype, stream, "zp_all_reduce_add_rms_norm");
+}
+
+extern "C" int zp_sample_sharded(zp_comm* c, const void* logits, const float* temperatures, const float* noise,
+                                 int64_t* tokens_out, int n_rows, int vocab_shard, uint64_t seed, int dtype,
+                                 void* stream) {
+  using namespace zp::coll;
+  ZP_REQUIRE(c && c->state, "zp_sample_sharded: null communicator");
+  for (int r = 0; r < c->world; ++r) ZP_REQUIRE(c->seg[r], "zp_sample_sharded: the segment of rank %d is not attached", r);
+  if (n_rows == 0) return ZP_OK;
+  ZP_REQUIRE(logits && temperatures && tokens_out, "zp_sample_sharded: null pointer");
+  ZP_REQUIRE(n_rows > 0 && vocab_shard > 0 && (int64_t)vocab_shard * c->world < 0x7fffffff,
+             "zp_sample_sharded: bad sizes");
+  ZP_REQUIRE((size_t)c->world * n_rows * 8 <= c->area_bytes,
+             "zp_sample_sharded: %d rows need %zu bytes of message area, the communicator has %zu", n_rows,
+             (size_t)c->world * n_rows * 8, c->area_bytes);
+  Dev d;
+  for (int r = 0; r < MAX_WORLD; ++r) d.seg[r] = c->seg[r];
+  d.state = c->state; d.area_bytes = c->area_bytes; d.timeout_ns = c->timeout_ns;
+  d.rank = c->rank; d.world = c->world;
+  const int grid = std::min(n_rows, std::min(c->sms, MAX_BLOCKS));
+  cudaStream_t st = (cudaStream_t)stream;
+#define ZP_SAMPLE_WORLD(W)                                                                              \
+  ZP_DISPATCH_DTYPE(dtype, T, (sample_sharded_kernel<T, W><<<grid, SAMPLE_THREADS, 0, st>>>(            \
+                                  d, (const T*)logits, temperatures, noise, tokens_out, n_rows, vocab_shard, seed)))
+  switch (c->world) {
+    case 2: ZP_SAMPLE_WORLD(2); break;
+    case 4: ZP_SAMPLE_WORLD(4); break;
+    case 8: ZP_SAMPLE_WORLD(8); break;
+    default: zp::set_error("zp_sample_sharded: world size %d", c->world); return ZP_ERR_INVALID_ARGUMENT;
+  }
+#undef ZP_SAMPLE_WORLD
+  return zp::check_launch("zp_sample_sharded");
 }

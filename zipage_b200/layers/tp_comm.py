@@ -70,6 +70,23 @@ class TPCommunicator:
         _count(1)
         return out.view(x.shape), res_out.view(x.shape)
 
+    def sample(self, logits_shard, temperatures, noise_shard=None, seed=0):
+        """tokens [B] int64, the same on every rank, from this rank's vocabulary shard
+        logits_shard [B, V / world] (rank r holds columns r*V/world ..., as ParallelLMHead
+        computes them) — stands where embed_head.py:27-34 gathers the shards to rank 0 and
+        sampler.py:17-31 samples there."""
+        L.require_cuda(logits_shard, temperatures, noise_shard)
+        B, Vs = logits_shard.shape
+        assert logits_shard.is_contiguous() and temperatures.dtype == torch.float32
+        if noise_shard is not None:
+            assert noise_shard.dtype == torch.float32 and noise_shard.is_contiguous() and noise_shard.shape == logits_shard.shape
+        out = torch.empty(B, dtype=torch.int64, device=logits_shard.device)
+        L.check(L.load().zp_sample_sharded(self._h, L.ptr(logits_shard), L.ptr(temperatures), L.ptr(noise_shard),
+                                           L.ptr(out), B, Vs, int(seed), L.dtype_code(logits_shard),
+                                           L.stream_ptr()), "sample_sharded")
+        _count(1)
+        return out
+
     def status(self) -> int:
         """0, or 1 when a device-side wait of an earlier call ran out (synchronises)."""
         code = C.c_int(0)
