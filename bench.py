@@ -53,6 +53,7 @@ def parse_args():
                          "forward of Qwen3-8B-shaped blocks, launch by launch and as a replayed CUDA graph) or "
                          "tp_allreduce (the row-parallel projections' all-reduce + residual + RMSNorm over "
                          "peer memory against the library collective; needs --gpus >= 2 under torchrun)")
+    ap.add_argument("--verbose", action="store_true", help="progress lines on stderr")
     ap.add_argument("--tokens", type=int, default=32768, help="tokens per call of the step_ops workload")
     return ap.parse_args()
 
@@ -278,7 +279,10 @@ def run_decode_step(args):
     over compressed tables (context 2049..2304 tokens in 9 pages), timed launch by launch and as
     one replayed CUDA graph whose inputs are device state only.  `value` is the graph's rate with
     the inputs already in the graph's buffers; `e2e` copies the step's inputs from pinned host
-    memory and reads the hidden states back."""
+    memory and reads the hidden states back.  Under torchrun (N = 2, 4, 8) the blocks are
+    tensor-parallel over the ranks (heads and MLP columns split, the same batch: strong scaling)
+    with every all-reduce fused into the norm that consumes it, over peer memory; the same step on
+    NCCL all-reduce + the RMSNorm kernel is timed beside it."""
     import torch
     from types import SimpleNamespace
     from zipage_b200 import kernel as K
@@ -286,6 +290,21 @@ def run_decode_step(args):
     from zipage_b200.layers.qwen3_block import Qwen3Model
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    comm = lib_comm = None
+    rank = 0
+    if world > 1:
+        import torch.distributed as dist
+        from zipage_b200.layers.tp_comm import LibraryCommunicator, TPCommunicator
+        dist.init_process_group("nccl", device_id=dev)
+        rank = dist.get_rank()
+        comm = TPCommunicator(max_bytes=min(args.batch, 256) * 4096 * 2, timeout_ms=2000)
+        lib_comm = LibraryCommunicator()
+    hkv = HKV // world
+
+    def stage(msg):   # progress on stderr (the JSON line goes to stdout)
+        if args.verbose:
+            print(f"[decode_step rank {rank}] {msg}", file=sys.stderr, flush=True)
     B, Ln, NBs = min(args.batch, 256), min(args.layers, 36), BUDGET + 1
     cfg = SimpleNamespace(hidden_size=4096, num_attention_heads=HQ, num_key_value_heads=HKV, head_dim=D,
                           intermediate_size=12288, hidden_act="silu", rms_norm_eps=1e-6, vocab_size=151936,
@@ -295,12 +314,13 @@ def run_decode_step(args):
     torch.set_default_dtype(torch.bfloat16)
     try:
         with torch.device(dev):
-            model = Qwen3Model(cfg).eval()
+            model = Qwen3Model(cfg, comm).eval()
+            lib_model = Qwen3Model(cfg, lib_comm).eval() if world > 1 else None
     finally:
         torch.set_default_dtype(prev)
     P = B * (NBs + 1)
-    kv = torch.empty((2, Ln, P, BS, HKV, D), dtype=torch.bfloat16, device=dev).normal_()
-    qc = torch.zeros((Ln, B, QCL, HQ, D), dtype=torch.bfloat16, device=dev)
+    kv = torch.empty((2, Ln, P, BS, hkv, D), dtype=torch.bfloat16, device=dev).normal_()
+    qc = torch.zeros((Ln, B, QCL, HQ // world, D), dtype=torch.bfloat16, device=dev)
     model.bind_caches(kv, qc)
     g = torch.Generator(device="cpu").manual_seed(5)
     table = torch.randperm(P, generator=g)[: B * NBs].view(B, NBs).to(torch.int32).pin_memory()
@@ -309,7 +329,7 @@ def run_decode_step(args):
     qid = torch.arange(B, dtype=torch.int32).pin_memory()
     runner = DecodeGraphRunner(model, cfg.hidden_size, max_bs=B, max_num_blocks=NBs + 1, query_cache_len=QCL,
                                device=dev, graph_bs=[B])
-    runner.capture()
+    stage('model built'); runner.capture(); stage('captured')
     host_out = torch.empty((B, cfg.hidden_size), dtype=torch.bfloat16).pin_memory()
     d_args = [x.to(dev) for x in (ids, ntok, table, qid)]
     runner._fill(*d_args)
@@ -318,13 +338,20 @@ def run_decode_step(args):
         for _ in range(args.warmup):
             fn()
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
             fn()
         e1.record()
         torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / args.steps
+        ms = e0.elapsed_time(e1) / args.steps
+        if world > 1:   # the slowest rank
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
 
     def e2e_step():
         out = runner.run(ids.to(dev, non_blocking=True), ntok.to(dev, non_blocking=True),
@@ -338,30 +365,52 @@ def run_decode_step(args):
     per_step = K.LAUNCHES
     with ClockSampler(dev.index or 0) as clocks:
         ms_graph = timed(graph.replay)
+    stage(f'graph {ms_graph:.3f} ms')
     ms_eager = timed(lambda: runner._step(B))
+    stage(f'eager {ms_eager:.3f} ms')
     ms_e2e = timed(e2e_step)
+    stage(f'e2e {ms_e2e:.3f} ms')
+    ms_lib = None
+    if world > 1:
+        # The same step on the library collective + the stand-alone norm kernel, launch by launch
+        # (compare with launch_by_launch_ms_per_step): replaying a captured decode graph that
+        # holds NCCL all-reduces stalled on this software stack, so that route is not captured.
+        lib_model.bind_caches(kv, qc)
+        lib_runner = DecodeGraphRunner(lib_model, cfg.hidden_size, max_bs=B, max_num_blocks=NBs + 1,
+                                       query_cache_len=QCL, device=dev, graph_bs=[B])
+        lib_runner._fill(*d_args)
+        ms_lib = timed(lambda: lib_runner._step(B))
+        stage(f'library route, launch by launch {ms_lib:.3f} ms')
     h2d = ids.numel() * 8 + ntok.numel() * 4 + table.numel() * 4 + qid.numel() * 4
     # bytes a step must read once: every block's weights and the K/V rows of every context token
     wbytes = sum(p.numel() for n, p in model.named_parameters() if "embed" not in n) * 2
-    kvbytes = float(ntok.sum().item()) * HKV * D * 2 * 2 * Ln
+    kvbytes = float(ntok.sum().item()) * hkv * D * 2 * 2 * Ln
     peaks = {}
     pk = ROOT / "MEASURED_PEAKS.json"
     if pk.exists():
         peaks = json.loads(pk.read_text())
     hbm_peak = peaks.get("hbm_gbs", 6650.0)
     ach = (wbytes + kvbytes) / (ms_graph * 1e-3) / 1e9
+    if world > 1:
+        status = comm.status()
+        comm.close()
+        dist.destroy_process_group()
+        if rank != 0:
+            return
     print(json.dumps({
-        "metric": "decode_step_tokens_per_s", "value": B / (ms_graph * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "metric": "decode_step_tokens_per_s", "value": B / (ms_graph * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_graph, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "decode forward, Qwen3-8B-shaped blocks, compressed tables (2049..2304 tokens "
                                "in 9 pages), one CUDA graph replay per step", "sequences": B, "layers": Ln,
+                   "parallelism": f"tp{world}: all-reduce fused into the norms over peer memory" if world > 1 else "none",
                    "l2": "weights + K/V of a step (%.1f GB) far exceed the 126 MB L2" % ((wbytes + kvbytes) / 1e9)},
         "launch_by_launch_ms_per_step": ms_eager, "graph_speedup": ms_eager / ms_graph,
+        "library_collective_launch_by_launch_ms_per_step": ms_lib, "comm_status": status if world > 1 else None,
         "e2e": {"value": B / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": host_out.numel() * 2},
         "gpu_launches": per_step * args.steps, "own_kernels_per_step": per_step, "clocks": clocks.summary(),
-        "roofline": {"bound": "hbm", "kernel": "whole step (weights + K/V read once)", "achieved": ach,
+        "roofline": {"bound": "hbm", "kernel": "whole step (this rank's weights + K/V read once)", "achieved": ach,
                      "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
                      "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback", "traffic": None},
     }))

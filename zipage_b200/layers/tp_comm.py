@@ -100,6 +100,27 @@ class TPCommunicator:
             self._h = C.c_void_p()
 
 
+class LibraryCommunicator:
+    """The same interface on `torch.distributed` collectives (NCCL) and the stand-alone RMSNorm
+    kernel — the reference's route, kept for comparisons and for groups that span nodes."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+
+    def all_reduce(self, x, out=None, algo="auto"):
+        if out is not None:
+            out.copy_(x)
+            x = out
+        dist.all_reduce(x, group=self.group)
+        return x
+
+    def all_reduce_add_rms_norm(self, x, residual, weight, eps, algo="auto"):
+        from .step_ops import rms_norm
+        dist.all_reduce(x, group=self.group)
+        return rms_norm(x, weight, eps, residual)
+
+
 class RowParallelLinear(nn.Module):
     """third_party/nanovllm/layers/linear.py:131-153 with the all-reduce on a TPCommunicator.
     `weight` holds this rank's [output_size, input_size / tp_size] shard."""
