@@ -112,3 +112,47 @@ def prepare_decode(num_tokens, block_tables, query_ids, query_cache_len, block_s
     return (torch.tensor(pos, dtype=torch.int64), torch.tensor(ctx, dtype=torch.int32),
             torch.tensor(slot, dtype=torch.int32), torch.tensor(padded, dtype=torch.int32),
             torch.tensor(trip, dtype=torch.int32).reshape(-1, 3))
+
+
+# ---- the sampler over a vocabulary sharded across ranks -----------------------------------------
+# The reference gathers the shards' logits to rank 0 (zipage/layers/embed_head.py:27-34) and
+# samples there (zipage/layers/sampler.py:17-31).  The three functions below restate the same race
+# shard by shard: softmax statistics per shard, the shard's winner against the global statistics,
+# the best of the winners.  Their composition must give sample_race() of the concatenated logits.
+
+def shard_softmax_stats(logits_shard: torch.Tensor, temperatures: torch.Tensor):
+    """Per row: the shard's maximum of logits / T and the sum of exp(logits / T - maximum)."""
+    lg = logits_shard.float() / temperatures.unsqueeze(1)
+    m = lg.max(dim=-1).values
+    return m, torch.exp(lg - m.unsqueeze(1)).sum(dim=-1)
+
+
+def shard_race_winner(logits_shard, temperatures, noise_shard, m_all, z_all, index_base):
+    """m_all, z_all [world, B] in rank order.  Returns the shard's best value of
+    (exp(l / T - M) / Z) / max(noise, 1e-10) per row and its global index (first on ties)."""
+    M = m_all.max(dim=0).values
+    Z = torch.zeros_like(M)
+    for r in range(m_all.shape[0]):                       # rank order, as every rank sums it
+        Z = Z + z_all[r] * torch.exp(m_all[r] - M)
+    lg = logits_shard.float() / temperatures.unsqueeze(1)
+    val = torch.exp(lg - M.unsqueeze(1)) / Z.unsqueeze(1) / noise_shard.clamp_min(1e-10)
+    best, idx = val.max(dim=-1)
+    return best, idx + index_base
+
+
+def combine_winners(vals: torch.Tensor, idxs: torch.Tensor) -> torch.Tensor:
+    """vals, idxs [world, B]: the larger value wins, then the lower global index."""
+    best, besti = vals[0].clone(), idxs[0].clone()
+    for r in range(1, vals.shape[0]):
+        take = (vals[r] > best) | ((vals[r] == best) & (idxs[r] < besti))
+        best, besti = torch.where(take, vals[r], best), torch.where(take, idxs[r], besti)
+    return besti
+
+
+def all_reduce_rank_order(parts, dtype):
+    """dist.all_reduce(y) of RowParallelLinear.forward (third_party/nanovllm/layers/linear.py:149-153)
+    with the summation order pinned: fp32, rank 0 first, one rounding to the tensor dtype."""
+    acc = parts[0].float()
+    for p in parts[1:]:
+        acc = acc + p.float()
+    return acc.to(dtype)

@@ -151,9 +151,12 @@ def main():
         full = (3 * torch.randn(B, V)).to(dtype).to(dev)
         temps = (0.3 + torch.rand(B)).to(dev)
         draws = torch.empty(B, V).exponential_(1.0).to(dev)
+        full[3, 5] = full[3, Vs + 9] = 40.0               # an exact tie between two shards:
+        draws[3, 5] = draws[3, Vs + 9] = 0.5              # the lower global index must win
         sl = slice(rank * Vs, (rank + 1) * Vs)
         tok = comm.sample(full[:, sl].contiguous(), temps, noise_shard=draws[:, sl].contiguous())
         assert torch.equal(tok, sample(full, temps, noise=draws)), (dtype, B, Vs)
+        assert int(tok[3]) == 5
         assert torch.equal(tok.cpu(), S.sample_race(full.cpu(), temps.cpu(), draws.cpu())), (dtype, B, Vs)
         tok = comm.sample(full[:, sl].contiguous(), temps, seed=11)
         assert torch.equal(tok, sample(full, temps, seed=11)), (dtype, B, Vs, "generator")
