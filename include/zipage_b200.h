@@ -321,8 +321,8 @@ int zp_prepare_decode(const int32_t* num_tokens, const int32_t* block_tables,
  * 28-40, called at third_party/nanovllm/models/qwen3.py:146-152).  The sum is taken in fp32 in rank
  * order and rounded to T once, so every rank holds the same bits.
  *
- * Set-up, once per rank: zp_comm_create allocates this rank's segment (flags + four message areas
- * of max_bytes) with cudaMalloc; the ranks exchange the 64-byte handles of zp_comm_ipc_handle by
+ * Set-up, once per rank: zp_comm_create allocates this rank's segment (flags + 2 x (world + 1)
+ * message areas of max_bytes) with cudaMalloc; the ranks exchange the 64-byte handles of zp_comm_ipc_handle by
  * any host channel and map each other's segment with zp_comm_open_peer (CUDA IPC), or map the
  * segments themselves and pass the pointers to zp_comm_attach_peer.  All ranks must make the same
  * sequence of calls with the same sizes.  Every device-side wait ends after timeout_ms: the call's

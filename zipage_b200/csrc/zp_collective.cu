@@ -7,14 +7,17 @@
 // 28-40; call sites third_party/nanovllm/models/qwen3.py:146-152).
 //
 // Every rank owns one segment of device memory that all ranks of the node map (CUDA IPC, or any
-// mapping the caller attaches): [flags | 2 parities x (input area, result area)].  One launch:
-//   1. each block copies its rows of the input into the local input area of this call's parity,
+// mapping the caller attaches): [flags | 2 parities x (one input slot per source rank, a result
+// area)].  One launch:
+//   1. each block stores its rows of the input into slot `rank` of every rank's segment (one-shot)
+//      or of the segment of the rank that owns each 512-byte chunk (two-shot): posted writes over
+//      the link, no round trip,
 //   2. meets the same block of every peer (a flag per (phase, source rank, block) written into
 //      the peer's segment with release/system scope, polled locally, then an acquire fence),
-//   3. one-shot: reads its rows from every rank's input area and sums them in fp32 in rank order
-//      (so every rank gets the same bits), rounding to T once;
-//      two-shot: each rank sums only the 512-byte chunks it owns and stores the result into every
-//      rank's result area, the blocks meet again, and each reads its rows from its own result area,
+//   3. one-shot: sums its rows over the local slots in fp32 in rank order (so every rank gets the
+//      same bits), rounding to T once;
+//      two-shot: each rank sums only the chunks it owns and stores the result into every rank's
+//      result area, the blocks meet again, and each reads its rows from its own result area,
 //   4. writes the sum, or (fused) adds the residual, writes the new residual, and writes the
 //      RMS-normalised, weighted row — the same arithmetic as the stand-alone RMSNorm kernel.
 // The two parities alternate between calls, so a rank may start the next call while a peer still
@@ -66,9 +69,11 @@ __device__ __forceinline__ int4 ld16_l2(const void* p) {   // L2 only: the line 
 __device__ __forceinline__ uint32_t* flag_of(char* const* seg, int owner, int phase, int src, int blk) {
   return reinterpret_cast<uint32_t*>(seg[owner]) + (phase * MAX_WORLD + src) * MAX_BLOCKS + blk;
 }
-__device__ __forceinline__ char* area_of(char* const* seg, size_t area_bytes, int owner, uint32_t parity,
-                                         int which) {
-  return seg[owner] + FLAG_BYTES + (size_t)(parity * 2 + which) * area_bytes;
+// Area `which` of `owner`'s segment: 0..world-1 = the input slot written by that source rank,
+// world = the result area of the two-shot form.
+__device__ __forceinline__ char* area_of(char* const* seg, size_t area_bytes, int world, int owner,
+                                         uint32_t parity, int which) {
+  return seg[owner] + FLAG_BYTES + (size_t)(parity * (world + 1) + which) * area_bytes;
 }
 
 __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
@@ -110,24 +115,6 @@ template <typename T> struct Pack {
   __device__ __forceinline__ void set(int i, float v) { reinterpret_cast<T*>(&raw)[i] = Elem<T>::from_f32(v); }
 };
 
-// fp32 sum over the ranks, in rank order, of vector `v` of the input areas; rounded to T.
-template <typename T, int WORLD>
-__device__ __forceinline__ int4 reduce_vector(const Dev& c, char* const* seg, uint32_t parity, int64_t v) {
-  constexpr int EPV = Pack<T>::N;
-  Pack<T> x[WORLD];
-#pragma unroll
-  for (int r = 0; r < WORLD; ++r) x[r].raw = ld16_l2(area_of(seg, c.area_bytes, r, parity, 0) + v * 16);
-  Pack<T> o;
-#pragma unroll
-  for (int j = 0; j < EPV; ++j) {
-    float acc = x[0].get(j);
-#pragma unroll
-    for (int r = 1; r < WORLD; ++r) acc += x[r].get(j);
-    o.set(j, acc);
-  }
-  return o.raw;
-}
-
 // Rows of `row_vecs` 16-byte vectors (<= THREADS * VPT); row r belongs to block r % gridDim.x.
 template <typename T, int WORLD, bool TWO_SHOT, bool FUSED>
 __global__ void __launch_bounds__(THREADS)
@@ -144,12 +131,20 @@ all_reduce_kernel(const Dev c, const T* in, T* out, int64_t nvec, int row_vecs, 
   }
   __syncthreads();
   const uint32_t epoch = s_epoch, parity = epoch & 1u;
-  char* my_in = area_of(seg, c.area_bytes, c.rank, parity, 0);
-
+  // Push: the input goes straight into slot `rank` of the ranks that will sum it (one-shot: all of
+  // them; two-shot: the owner of each 512-byte chunk), so that after the meeting every load of the
+  // reduction is local and no round trip over the link is left on the critical path.
   for (int64_t row = blockIdx.x; row < nrows; row += gridDim.x) {
     const int64_t v0 = row * row_vecs, v1 = min(v0 + row_vecs, nvec);
-    for (int64_t v = v0 + threadIdx.x; v < v1; v += THREADS)
-      st16(my_in + v * 16, ld16(reinterpret_cast<const char*>(in) + v * 16));
+    for (int64_t v = v0 + threadIdx.x; v < v1; v += THREADS) {
+      const int4 x = ld16(reinterpret_cast<const char*>(in) + v * 16);
+      if constexpr (TWO_SHOT) {
+        st16(area_of(seg, c.area_bytes, WORLD, (int)((v >> 5) % WORLD), parity, c.rank) + v * 16, x);
+      } else {
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r) st16(area_of(seg, c.area_bytes, WORLD, r, parity, c.rank) + v * 16, x);
+      }
+    }
   }
   meet_peers(c, seg, 0, epoch);
 
@@ -158,20 +153,29 @@ all_reduce_kernel(const Dev c, const T* in, T* out, int64_t nvec, int row_vecs, 
       const int64_t v0 = row * row_vecs, v1 = min(v0 + row_vecs, nvec);
       for (int64_t v = v0 + threadIdx.x; v < v1; v += THREADS) {
         if ((int)((v >> 5) % WORLD) != c.rank) continue;   // 512-byte chunks, dealt round-robin
-        const int4 s = reduce_vector<T, WORLD>(c, seg, parity, v);
+        Pack<T> x[WORLD], o;
 #pragma unroll
-        for (int r = 0; r < WORLD; ++r) st16(area_of(seg, c.area_bytes, r, parity, 1) + v * 16, s);
+        for (int r = 0; r < WORLD; ++r) x[r].raw = ld16_l2(area_of(seg, c.area_bytes, WORLD, c.rank, parity, r) + v * 16);
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) {   // fp32 sum in rank order, one rounding
+          float acc = x[0].get(j);
+#pragma unroll
+          for (int r = 1; r < WORLD; ++r) acc += x[r].get(j);
+          o.set(j, acc);
+        }
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r) st16(area_of(seg, c.area_bytes, WORLD, r, parity, WORLD) + v * 16, o.raw);
       }
     }
     meet_peers(c, seg, 1, epoch);
   }
 
   // The raw vectors of the block's next row are requested before the current row is summed and
-  // normalised, so that a row's round trip over the link overlaps the previous row's arithmetic.
+  // normalised.
   constexpr int NSRC = TWO_SHOT ? 1 : WORLD;
   const char* src[NSRC];
 #pragma unroll
-  for (int r = 0; r < NSRC; ++r) src[r] = area_of(seg, c.area_bytes, TWO_SHOT ? c.rank : r, parity, TWO_SHOT ? 1 : 0);
+  for (int r = 0; r < NSRC; ++r) src[r] = area_of(seg, c.area_bytes, WORLD, c.rank, parity, TWO_SHOT ? WORLD : r);
   Pack<T> raw[VPT][NSRC];
 #pragma unroll
   for (int i = 0; i < VPT; ++i)
@@ -338,7 +342,7 @@ sample_sharded_kernel(const Dev c, const T* __restrict__ logits, const float* __
     for_each(lr, [&](int, float x) { z += __expf(fmaf(x, inv_t, -mx)); });
     z = block_sum(z, red);
     if (threadIdx.x < WORLD)
-      *reinterpret_cast<float2*>(area_of(seg, c.area_bytes, threadIdx.x, parity, 0) +
+      *reinterpret_cast<float2*>(area_of(seg, c.area_bytes, WORLD, threadIdx.x, parity, 0) +
                                  ((size_t)c.rank * rows + row) * 8) = make_float2(mx, z);
     __syncthreads();
   }
@@ -352,7 +356,7 @@ sample_sharded_kernel(const Dev c, const T* __restrict__ logits, const float* __
     float m = -INFINITY;
 #pragma unroll
     for (int r = 0; r < WORLD; ++r) {
-      const float2 st = __ldcg(reinterpret_cast<const float2*>(area_of(seg, c.area_bytes, c.rank, parity, 0) +
+      const float2 st = __ldcg(reinterpret_cast<const float2*>(area_of(seg, c.area_bytes, WORLD, c.rank, parity, 0) +
                                                                 ((size_t)r * rows + row) * 8));
       ms[r] = st.x; zs[r] = st.y;
       m = fmaxf(m, st.x);
@@ -401,7 +405,7 @@ sample_sharded_kernel(const Dev c, const T* __restrict__ logits, const float* __
       }
       if (lane < WORLD) {
         const int gi = besti == 0x7fffffff ? 0x7fffffff : (int)gbase + besti;
-        *reinterpret_cast<float2*>(area_of(seg, c.area_bytes, lane, parity, 1) +
+        *reinterpret_cast<float2*>(area_of(seg, c.area_bytes, WORLD, lane, parity, 1) +
                                    ((size_t)c.rank * rows + row) * 8) = make_float2(best, __int_as_float(gi));
       }
     }
@@ -416,7 +420,7 @@ sample_sharded_kernel(const Dev c, const T* __restrict__ logits, const float* __
       int besti = 0x7fffffff;
 #pragma unroll
       for (int r = 0; r < WORLD; ++r) {
-        const float2 cnd = __ldcg(reinterpret_cast<const float2*>(area_of(seg, c.area_bytes, c.rank, parity, 1) +
+        const float2 cnd = __ldcg(reinterpret_cast<const float2*>(area_of(seg, c.area_bytes, WORLD, c.rank, parity, 1) +
                                                                    ((size_t)r * rows + row) * 8));
         const int ci = __float_as_int(cnd.y);
         if (cnd.x > best || (cnd.x == best && ci < besti)) { best = cnd.x; besti = ci; }
@@ -449,7 +453,9 @@ struct zp_comm {
 
 namespace {
 
-size_t segment_bytes(size_t area_bytes) { return zp::coll::FLAG_BYTES + 4 * area_bytes; }
+size_t segment_bytes(size_t area_bytes, int world) {
+  return zp::coll::FLAG_BYTES + 2 * (size_t)(world + 1) * area_bytes;
+}
 
 template <typename T, int WORLD>
 void launch(const zp_comm* c, bool two_shot, bool fused, const void* in, void* out, int64_t nvec,
@@ -460,8 +466,10 @@ void launch(const zp_comm* c, bool two_shot, bool fused, const void* in, void* o
   for (int r = 0; r < MAX_WORLD; ++r) d.seg[r] = c->seg[r];
   d.state = c->state; d.area_bytes = c->area_bytes; d.timeout_ns = c->timeout_ns;
   d.rank = c->rank; d.world = c->world;
-  const int grid = (int)std::min<int64_t>(nrows, std::min(c->sms, MAX_BLOCKS));
   auto go = [&](auto kernel) {
+    // one block per SM: every block of the launch is resident at once (blocks wait for their
+    // peers' blocks), and more blocks only add flags to exchange (256 blocks measured slower)
+    const int grid = (int)std::min<int64_t>(nrows, std::min(c->sms, MAX_BLOCKS));
     kernel<<<grid, THREADS, 0, st>>>(d, (const T*)in, (T*)out, nvec, row_vecs, nrows, (const T*)residual,
                                      (const T*)weight, (T*)residual_out, eps);
   };
@@ -512,7 +520,7 @@ extern "C" int zp_comm_create(int rank, int world, size_t max_bytes, int timeout
   cudaError_t e = cudaGetDevice(&c->device);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&c->sms, cudaDevAttrMultiProcessorCount, c->device);
   void* seg = nullptr; void* state = nullptr;
-  if (e == cudaSuccess) e = cudaMalloc(&seg, segment_bytes(c->area_bytes));
+  if (e == cudaSuccess) e = cudaMalloc(&seg, segment_bytes(c->area_bytes, world));
   if (e == cudaSuccess) e = cudaMemset(seg, 0, FLAG_BYTES);
   if (e == cudaSuccess) e = cudaMalloc(&state, 256);
   if (e == cudaSuccess) e = cudaMemset(state, 0, 256);
@@ -533,7 +541,7 @@ extern "C" int zp_comm_create(int rank, int world, size_t max_bytes, int timeout
 extern "C" int zp_comm_segment(zp_comm* c, void** ptr_out, size_t* bytes_out) {
   ZP_REQUIRE(c && ptr_out && bytes_out, "zp_comm_segment: null pointer");
   *ptr_out = c->seg[c->rank];
-  *bytes_out = segment_bytes(c->area_bytes);
+  *bytes_out = segment_bytes(c->area_bytes, c->world);
   return ZP_OK;
 }
 
