@@ -362,6 +362,25 @@ int zp_sample_sharded(zp_comm* comm, const void* logits, const float* temperatur
                       int64_t* tokens_out, int n_rows, int vocab_shard, uint64_t seed, int dtype,
                       void* stream);
 
+/* Test support, not a serving path: the ranks of a world (2, 4 or 8) as ONE cooperative launch on
+ * one GPU — grid (blocks, world), every block resident, rank r = comms[r] (all created in this
+ * process on the current device, each with the others' segments attached by zp_comm_attach_peer).
+ * Runs the same per-rank code as zp_all_reduce (fused = 0; rows x row_elems elements) or
+ * zp_all_reduce_add_rms_norm (fused = 1), for world sizes with no multi-GPU machine at hand.
+ * ins / outs / residual_outs: one pointer per rank; residual and weight are shared.  algo 1 or 2. */
+int zp_all_reduce_emulated(zp_comm* const* comms, int world, const void* const* ins, void* const* outs,
+                           const void* residual, const void* weight, void* const* residual_outs,
+                           int64_t rows, int row_elems, float eps, int dtype, int algo, int fused,
+                           void* stream);
+
+/* Test support, as zp_all_reduce_emulated: zp_sample_sharded for every rank of a world as one
+ * cooperative launch on one GPU.  logits_shards[r] [n_rows, vocab_shard], noise_shards (NULL, or
+ * one [n_rows, vocab_shard] fp32 pointer per rank), tokens_outs[r] [n_rows] int64. */
+int zp_sample_sharded_emulated(zp_comm* const* comms, int world, const void* const* logits_shards,
+                               const float* temperatures, const float* const* noise_shards,
+                               int64_t* const* tokens_outs, int n_rows, int vocab_shard, uint64_t seed,
+                               int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

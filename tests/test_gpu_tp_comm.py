@@ -88,3 +88,137 @@ def test_all_reduce_across_gpus(world):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert all(f"rank {i} OK" in r.stdout for i in range(world))
     print([ln for ln in r.stdout.splitlines() if ln.startswith("TPCOMM")])
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_world_sizes_as_one_cooperative_launch(world):
+    """Every rank of the world as blocks of one cooperative launch on one GPU (the per-rank code is
+    the multi-GPU kernel's): bit-exact against the fp32 rank-order sum for both algorithms, over
+    consecutive calls, and the fused residual + RMSNorm form against the RMSNorm kernel."""
+    import ctypes as C
+    from zipage_b200 import _lib as L
+    from zipage_b200.layers.step_ops import rms_norm
+    dev = _gpu()
+    lib = L.load()
+    comms = []
+    try:
+        for r in range(world):
+            h = C.c_void_p()
+            L.check(lib.zp_comm_create(r, world, 1 << 20, 2000, C.byref(h)), "create")
+            comms.append(h)
+        segs = []
+        for h in comms:
+            p, n = C.c_void_p(), C.c_size_t()
+            L.check(lib.zp_comm_segment(h, C.byref(p), C.byref(n)), "segment")
+            segs.append(p)
+        for r, h in enumerate(comms):
+            for q in range(world):
+                if q != r:
+                    L.check(lib.zp_comm_attach_peer(h, q, segs[q]), "attach")
+        arr = (C.c_void_p * world)(*[h.value for h in comms])
+        g = torch.Generator(device=dev).manual_seed(world)
+
+        def ptrs(ts):
+            return (C.c_void_p * world)(*[t.data_ptr() for t in ts])
+
+        for dtype in (torch.bfloat16, torch.float32):
+            for rows, elems in ((40, 1024), (3, 4096 if dtype == torch.float32 else 8192), (300, 512)):
+                for algo in (1, 2):
+                    for _ in range(3):      # consecutive calls alternate the areas
+                        xs = [torch.randn(rows, elems, device=dev, generator=g).to(dtype) for _ in range(world)]
+                        outs = [torch.empty_like(x) for x in xs]
+                        L.check(lib.zp_all_reduce_emulated(arr, world, ptrs(xs), ptrs(outs), None, None, None, rows,
+                                                           elems, 0.0, L.dtype_code(xs[0]), algo, 0, L.stream_ptr()),
+                                "emulated")
+                        acc = xs[0].float()
+                        for x in xs[1:]:
+                            acc = acc + x.float()
+                        want = acc.to(dtype)
+                        for o in outs:
+                            assert torch.equal(o, want), (world, dtype, rows, elems, algo)
+                    # fused form
+                    res = torch.randn(rows, elems, device=dev, generator=g).to(dtype)
+                    w = (1 + 0.1 * torch.randn(elems, device=dev, generator=g)).to(dtype)
+                    res_outs = [torch.empty_like(res) for _ in range(world)]
+                    L.check(lib.zp_all_reduce_emulated(arr, world, ptrs(xs), ptrs(outs), L.ptr(res), L.ptr(w),
+                                                       ptrs(res_outs), rows, elems, 1e-6, L.dtype_code(res), algo, 1,
+                                                       L.stream_ptr()), "emulated fused")
+                    y0, r0 = rms_norm(want, w, 1e-6, res)
+                    for o, ro in zip(outs, res_outs):
+                        assert torch.equal(ro, r0)
+                        if dtype == torch.float32:
+                            assert torch.allclose(o, y0, rtol=3e-6, atol=1e-6)
+                        else:
+                            d = (o.float() - y0.float()).abs()
+                            assert (d <= 2.0 ** -7 * y0.float().abs().clamp_min(1e-3)).all()
+                            assert (d > 0).float().mean() < 0.01
+        torch.cuda.synchronize()
+        for h in comms:
+            code = C.c_int(-1)
+            L.check(lib.zp_comm_status(h, C.byref(code)), "status")
+            assert code.value == 0
+    finally:
+        for h in comms:
+            lib.zp_comm_destroy(h)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_sampler_world_sizes_as_one_cooperative_launch(world):
+    """The sharded sampler for every rank of the world in one cooperative launch on one GPU: every
+    rank's tokens == the single-GPU sampler on the concatenated logits == the CPU oracle."""
+    import ctypes as C
+    from oracle import step_ops_oracle as S
+    from zipage_b200 import _lib as L
+    from zipage_b200.layers.step_ops import sample
+    dev = _gpu()
+    lib = L.load()
+    comms = []
+    try:
+        for r in range(world):
+            h = C.c_void_p()
+            L.check(lib.zp_comm_create(r, world, 1 << 16, 2000, C.byref(h)), "create")
+            comms.append(h)
+        segs = []
+        for h in comms:
+            p, n = C.c_void_p(), C.c_size_t()
+            L.check(lib.zp_comm_segment(h, C.byref(p), C.byref(n)), "segment")
+            segs.append(p)
+        for r, h in enumerate(comms):
+            for q in range(world):
+                if q != r:
+                    L.check(lib.zp_comm_attach_peer(h, q, segs[q]), "attach")
+        arr = (C.c_void_p * world)(*[h.value for h in comms])
+        for dtype, B, Vs in ((torch.bfloat16, 37, 2000), (torch.float32, 70, 1001), (torch.float16, 5, 18992)):
+            torch.manual_seed(3 + world)
+            V = Vs * world
+            full = (3 * torch.randn(B, V)).to(dtype).to(dev)
+            temps = (0.3 + torch.rand(B)).to(dev)
+            draws = torch.empty(B, V).exponential_(1.0).to(dev)
+            full[3, 5] = full[3, (world - 1) * Vs + 9] = 40.0     # an exact tie between the first and the last shard
+            draws[3, 5] = draws[3, (world - 1) * Vs + 9] = 0.5
+            shards = [full[:, r * Vs:(r + 1) * Vs].contiguous() for r in range(world)]
+            nshards = [draws[:, r * Vs:(r + 1) * Vs].contiguous() for r in range(world)]
+            outs = [torch.empty(B, dtype=torch.int64, device=dev) for _ in range(world)]
+
+            def ptrs(ts):
+                return (C.c_void_p * world)(*[t.data_ptr() for t in ts])
+
+            L.check(lib.zp_sample_sharded_emulated(arr, world, ptrs(shards), L.ptr(temps), ptrs(nshards), ptrs(outs), B,
+                                                   Vs, 0, L.dtype_code(full), L.stream_ptr()), "emulated sampler")
+            want = sample(full, temps, noise=draws)
+            assert torch.equal(want.cpu(), S.sample_race(full.cpu(), temps.cpu(), draws.cpu()))
+            for o in outs:
+                assert torch.equal(o, want), (world, dtype, B, Vs)
+            assert int(want[3]) == 5
+            L.check(lib.zp_sample_sharded_emulated(arr, world, ptrs(shards), L.ptr(temps), None, ptrs(outs), B, Vs, 11,
+                                                   L.dtype_code(full), L.stream_ptr()), "emulated sampler, generator")
+            want = sample(full, temps, seed=11)
+            for o in outs:
+                assert torch.equal(o, want), (world, dtype, B, Vs, "generator")
+        for h in comms:
+            code = C.c_int(-1)
+            L.check(lib.zp_comm_status(h, C.byref(code)), "status")
+            assert code.value == 0
+    finally:
+        for h in comms:
+            lib.zp_comm_destroy(h)

@@ -85,6 +85,8 @@ SIGNATURES = {
     "zp_comm_destroy": (_I, [_P]),
     "zp_all_reduce": (_I, [_P, _P, _P, _L, _I, _I, _P]),
     "zp_all_reduce_add_rms_norm": (_I, [_P] * 6 + [_L, _I, _F, _I, _I, _P]),
+    "zp_all_reduce_emulated": (_I, [_P, _I, _P, _P, _P, _P, _P, _L, _I, _F, _I, _I, _I, _P]),
+    "zp_sample_sharded_emulated": (_I, [_P, _I, _P, _P, _P, _P, _I, _I, C.c_uint64, _I, _P]),
     "zp_sample_sharded": (_I, [_P, _P, _P, _P, _P, _I, _I, C.c_uint64, _I, _P]),
 }
 

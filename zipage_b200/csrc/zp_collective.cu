@@ -86,12 +86,12 @@ __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
 // block barrier orders every thread's stores before the signalling thread's release (which is
 // cumulative), and the signalling thread's acquire fence before every thread's later loads, so
 // only the threads that signal pay for system-scope fences; the poll itself is a relaxed load.
-__device__ __forceinline__ void meet_peers(const Dev& c, char* const* seg, int phase, uint32_t epoch) {
+__device__ __forceinline__ void meet_peers(const Dev& c, char* const* seg, int phase, uint32_t epoch, int blk) {
   __syncthreads();
   const int t = threadIdx.x;
   if (t < c.world && t != c.rank) {
-    st_release_sys(flag_of(seg, t, phase, c.rank, blockIdx.x), epoch);
-    const uint32_t* mine = flag_of(seg, c.rank, phase, t, blockIdx.x);
+    st_release_sys(flag_of(seg, t, phase, c.rank, blk), epoch);
+    const uint32_t* mine = flag_of(seg, c.rank, phase, t, blk);
     const long long t0 = now_ns();
     uint32_t spins = 0;
     while ((int32_t)(ld_relaxed_sys(mine) - epoch) < 0) {
@@ -116,10 +116,11 @@ template <typename T> struct Pack {
 };
 
 // Rows of `row_vecs` 16-byte vectors (<= THREADS * VPT); row r belongs to block r % gridDim.x.
+// `blk` of `nblk`: this block's index among the rank's blocks (the x dimension of the grid).
 template <typename T, int WORLD, bool TWO_SHOT, bool FUSED>
-__global__ void __launch_bounds__(THREADS)
-all_reduce_kernel(const Dev c, const T* in, T* out, int64_t nvec, int row_vecs, int64_t nrows,
-                  const T* residual, const T* __restrict__ weight, T* residual_out, float eps) {
+__device__ __forceinline__ void
+all_reduce_body(const Dev& c, const int blk, const int nblk, const T* in, T* out, int64_t nvec, int row_vecs,
+                int64_t nrows, const T* residual, const T* __restrict__ weight, T* residual_out, float eps) {
   constexpr int EPV = Pack<T>::N;
   __shared__ uint32_t s_epoch;
   __shared__ float red[32];
@@ -134,7 +135,7 @@ all_reduce_kernel(const Dev c, const T* in, T* out, int64_t nvec, int row_vecs, 
   // Push: the input goes straight into slot `rank` of the ranks that will sum it (one-shot: all of
   // them; two-shot: the owner of each 512-byte chunk), so that after the meeting every load of the
   // reduction is local and no round trip over the link is left on the critical path.
-  for (int64_t row = blockIdx.x; row < nrows; row += gridDim.x) {
+  for (int64_t row = blk; row < nrows; row += nblk) {
     const int64_t v0 = row * row_vecs, v1 = min(v0 + row_vecs, nvec);
     for (int64_t v = v0 + threadIdx.x; v < v1; v += THREADS) {
       const int4 x = ld16(reinterpret_cast<const char*>(in) + v * 16);
@@ -146,10 +147,10 @@ all_reduce_kernel(const Dev c, const T* in, T* out, int64_t nvec, int row_vecs, 
       }
     }
   }
-  meet_peers(c, seg, 0, epoch);
+  meet_peers(c, seg, 0, epoch, blk);
 
   if constexpr (TWO_SHOT) {
-    for (int64_t row = blockIdx.x; row < nrows; row += gridDim.x) {
+    for (int64_t row = blk; row < nrows; row += nblk) {
       const int64_t v0 = row * row_vecs, v1 = min(v0 + row_vecs, nvec);
       for (int64_t v = v0 + threadIdx.x; v < v1; v += THREADS) {
         if ((int)((v >> 5) % WORLD) != c.rank) continue;   // 512-byte chunks, dealt round-robin
@@ -167,7 +168,7 @@ all_reduce_kernel(const Dev c, const T* in, T* out, int64_t nvec, int row_vecs, 
         for (int r = 0; r < WORLD; ++r) st16(area_of(seg, c.area_bytes, WORLD, r, parity, WORLD) + v * 16, o.raw);
       }
     }
-    meet_peers(c, seg, 1, epoch);
+    meet_peers(c, seg, 1, epoch, blk);
   }
 
   // The raw vectors of the block's next row are requested before the current row is summed and
@@ -192,8 +193,8 @@ all_reduce_kernel(const Dev c, const T* in, T* out, int64_t nvec, int row_vecs, 
       }
     }
   };
-  if ((int64_t)blockIdx.x < nrows) request(blockIdx.x);
-  for (int64_t row = blockIdx.x; row < nrows; row += gridDim.x) {
+  if ((int64_t)blk < nrows) request(blk);
+  for (int64_t row = blk; row < nrows; row += nblk) {
     const int64_t v0 = row * row_vecs, v1 = min(v0 + row_vecs, nvec);
     Pack<T> x[VPT];
 #pragma unroll
@@ -210,7 +211,7 @@ all_reduce_kernel(const Dev c, const T* in, T* out, int64_t nvec, int row_vecs, 
         }
       }
     }
-    if (row + gridDim.x < nrows) request(row + gridDim.x);
+    if (row + nblk < nrows) request(row + nblk);
     if constexpr (!FUSED) {
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
@@ -259,12 +260,53 @@ all_reduce_kernel(const Dev c, const T* in, T* out, int64_t nvec, int row_vecs, 
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
-    if (atomicAdd(c.state + 1, 1u) == gridDim.x - 1) {
+    if (atomicAdd(c.state + 1, 1u) == (uint32_t)nblk - 1) {
       c.state[1] = 0;
       c.state[0] = epoch;
       __threadfence();
     }
   }
+}
+
+template <typename T, int WORLD, bool TWO_SHOT, bool FUSED>
+__global__ void __launch_bounds__(THREADS)
+all_reduce_kernel(const Dev c, const T* in, T* out, int64_t nvec, int row_vecs, int64_t nrows,
+                  const T* residual, const T* __restrict__ weight, T* residual_out, float eps) {
+  all_reduce_body<T, WORLD, TWO_SHOT, FUSED>(c, blockIdx.x, gridDim.x, in, out, nvec, row_vecs, nrows, residual,
+                                             weight, residual_out, eps);
+}
+
+// Every rank of a world as one cooperative launch on ONE GPU: blockIdx.y is the rank, all blocks
+// are resident at once, so the ranks' blocks can wait for one another.  Test support for world
+// sizes for which no multi-GPU machine is at hand; the per-rank code is the body above, unchanged.
+struct EmulatedWorld {
+  Dev dev[MAX_WORLD];
+  const void* in[MAX_WORLD];
+  void* out[MAX_WORLD];
+  void* residual_out[MAX_WORLD];
+};
+
+template <typename T, int WORLD, bool TWO_SHOT, bool FUSED>
+__global__ void __launch_bounds__(THREADS)
+all_reduce_emulated_kernel(const EmulatedWorld w, int64_t nvec, int row_vecs, int64_t nrows, const T* residual,
+                           const T* __restrict__ weight, float eps) {
+  __shared__ Dev c;
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r)
+      if (r == (int)blockIdx.y) c = w.dev[r];
+  }
+  __shared__ const void* in;
+  __shared__ void* out;
+  __shared__ void* res_out;
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r)
+      if (r == (int)blockIdx.y) { in = w.in[r]; out = w.out[r]; res_out = w.residual_out[r]; }
+  }
+  __syncthreads();
+  all_reduce_body<T, WORLD, TWO_SHOT, FUSED>(c, blockIdx.x, gridDim.x, (const T*)in, (T*)out, nvec, row_vecs, nrows,
+                                             residual, weight, (T*)res_out, eps);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -294,10 +336,10 @@ __device__ __forceinline__ float exp1_draw(uint64_t seed, uint32_t row, uint32_t
 constexpr int SAMPLE_THREADS = 1024;
 
 template <typename T, int WORLD>
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_sharded_kernel(const Dev c, const T* __restrict__ logits, const float* __restrict__ temperatures,
-                      const float* __restrict__ noise, int64_t* __restrict__ out, int rows, int Vs,
-                      uint64_t seed) {
+__device__ __forceinline__ void
+sample_sharded_body(const Dev& c, const int blk, const int nblk, const T* __restrict__ logits,
+                    const float* __restrict__ temperatures, const float* __restrict__ noise,
+                    int64_t* __restrict__ out, int rows, int Vs, uint64_t seed) {
   constexpr int EPV = Pack<T>::N;
   __shared__ uint32_t s_epoch;
   __shared__ char* seg[MAX_WORLD];
@@ -326,7 +368,7 @@ sample_sharded_kernel(const Dev c, const T* __restrict__ logits, const float* __
   };
 
   // ---- A: shard statistics ----
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  for (int row = blk; row < rows; row += nblk) {
     const T* lr = logits + (int64_t)row * Vs;
     const float t = temperatures[row];
     float mx = -INFINITY;
@@ -346,10 +388,10 @@ sample_sharded_kernel(const Dev c, const T* __restrict__ logits, const float* __
                                  ((size_t)c.rank * rows + row) * 8) = make_float2(mx, z);
     __syncthreads();
   }
-  meet_peers(c, seg, 0, epoch);
+  meet_peers(c, seg, 0, epoch, blk);
 
   // ---- B: the race over the shard against the global maximum and sum ----
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  for (int row = blk; row < rows; row += nblk) {
     const T* lr = logits + (int64_t)row * Vs;
     const float t = temperatures[row];
     float ms[WORLD], zs[WORLD];
@@ -411,10 +453,10 @@ sample_sharded_kernel(const Dev c, const T* __restrict__ logits, const float* __
     }
     __syncthreads();
   }
-  meet_peers(c, seg, 1, epoch);
+  meet_peers(c, seg, 1, epoch, blk);
 
   // ---- C: the best of the shards' winners ----
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  for (int row = blk; row < rows; row += nblk) {
     if (threadIdx.x == 0) {
       float best = -INFINITY;
       int besti = 0x7fffffff;
@@ -432,12 +474,41 @@ sample_sharded_kernel(const Dev c, const T* __restrict__ logits, const float* __
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
-    if (atomicAdd(c.state + 1, 1u) == gridDim.x - 1) {
+    if (atomicAdd(c.state + 1, 1u) == (uint32_t)nblk - 1) {
       c.state[1] = 0;
       c.state[0] = epoch;
       __threadfence();
     }
   }
+}
+
+template <typename T, int WORLD>
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_sharded_kernel(const Dev c, const T* __restrict__ logits, const float* __restrict__ temperatures,
+                      const float* __restrict__ noise, int64_t* __restrict__ out, int rows, int Vs,
+                      uint64_t seed) {
+  sample_sharded_body<T, WORLD>(c, blockIdx.x, gridDim.x, logits, temperatures, noise, out, rows, Vs, seed);
+}
+
+// Every rank as blocks of one cooperative launch on one GPU (test support, as above): rank r reads
+// columns [r * Vs, (r + 1) * Vs) of the full [rows, WORLD * Vs] logits (row stride = full width is
+// not supported by the body, so the shards are separate contiguous tensors).
+template <typename T, int WORLD>
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_sharded_emulated_kernel(const EmulatedWorld w, const float* __restrict__ temperatures, int rows, int Vs,
+                               uint64_t seed) {
+  __shared__ Dev c;
+  __shared__ const void* logits;
+  __shared__ const void* noise;
+  __shared__ void* out;
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r)
+      if (r == (int)blockIdx.y) { c = w.dev[r]; logits = w.in[r]; out = w.out[r]; noise = w.residual_out[r]; }
+  }
+  __syncthreads();
+  sample_sharded_body<T, WORLD>(c, blockIdx.x, gridDim.x, (const T*)logits, temperatures, (const float*)noise,
+                                (int64_t*)out, rows, Vs, seed);
 }
 
 }}  // namespace zp::coll
@@ -651,4 +722,93 @@ extern "C" int zp_sample_sharded(zp_comm* c, const void* logits, const float* te
   }
 #undef ZP_SAMPLE_WORLD
   return zp::check_launch("zp_sample_sharded");
+}
+
+// Test support (see all_reduce_emulated_kernel): `comms[r]` is rank r's communicator, all created
+// in this process on the current device with each other's segments attached by pointer.
+extern "C" int zp_all_reduce_emulated(zp_comm* const* comms, int world, const void* const* ins, void* const* outs,
+                                      const void* residual, const void* weight, void* const* residual_outs,
+                                      int64_t rows, int row_elems, float eps, int dtype, int algo, int fused,
+                                      void* stream) {
+  using namespace zp::coll;
+  ZP_REQUIRE(comms && ins && outs, "zp_all_reduce_emulated: null pointer");
+  ZP_REQUIRE(world == 2 || world == 4 || world == 8, "zp_all_reduce_emulated: world size %d", world);
+  ZP_REQUIRE(algo == 1 || algo == 2, "zp_all_reduce_emulated: algorithm %d (1 one-shot, 2 two-shot)", algo);
+  const int64_t row_bytes = (int64_t)row_elems * (int64_t)zp::dtype_size(dtype);
+  ZP_REQUIRE(rows > 0 && row_elems > 0 && row_bytes % 16 == 0 && row_bytes / 16 <= THREADS * VPT,
+             "zp_all_reduce_emulated: bad row size");
+  ZP_REQUIRE(!fused || (residual && weight && residual_outs), "zp_all_reduce_emulated: fused form needs residual and weight");
+  EmulatedWorld w{};
+  for (int r = 0; r < world; ++r) {
+    const zp_comm* c = comms[r];
+    ZP_REQUIRE(c && c->world == world && c->rank == r, "zp_all_reduce_emulated: communicator %d", r);
+    ZP_REQUIRE((size_t)(rows * row_bytes) <= c->area_bytes, "zp_all_reduce_emulated: message exceeds the areas");
+    for (int q = 0; q < world; ++q) ZP_REQUIRE(c->seg[q], "zp_all_reduce_emulated: rank %d lacks segment %d", r, q);
+    for (int q = 0; q < MAX_WORLD; ++q) w.dev[r].seg[q] = c->seg[q];
+    w.dev[r].state = c->state; w.dev[r].area_bytes = c->area_bytes; w.dev[r].timeout_ns = c->timeout_ns;
+    w.dev[r].rank = r; w.dev[r].world = world;
+    w.in[r] = ins[r]; w.out[r] = outs[r]; w.residual_out[r] = fused ? residual_outs[r] : nullptr;
+  }
+  int64_t nvec = rows * (row_bytes / 16);
+  int row_vecs = (int)(row_bytes / 16);
+  int64_t nrows = rows;
+  const int nblk = (int)std::min<int64_t>(nrows, std::max(1, comms[0]->sms / world));
+  void* args[] = {&w, &nvec, &row_vecs, &nrows, (void*)&residual, (void*)&weight, &eps};
+  const dim3 grid(nblk, world);
+  cudaError_t e = cudaSuccess;
+  auto go = [&](auto kernel) {
+    e = cudaLaunchCooperativeKernel((const void*)kernel, grid, dim3(THREADS), args, 0, (cudaStream_t)stream);
+  };
+#define ZP_EMU(W)                                                                                     \
+  ZP_DISPATCH_DTYPE(dtype, T, {                                                                       \
+    if (algo == 2) { if (fused) go(all_reduce_emulated_kernel<T, W, true, true>); else go(all_reduce_emulated_kernel<T, W, true, false>); } \
+    else           { if (fused) go(all_reduce_emulated_kernel<T, W, false, true>); else go(all_reduce_emulated_kernel<T, W, false, false>); } \
+  })
+  switch (world) {
+    case 2: ZP_EMU(2); break;
+    case 4: ZP_EMU(4); break;
+    default: ZP_EMU(8); break;
+  }
+#undef ZP_EMU
+  if (e != cudaSuccess) { zp::set_error("zp_all_reduce_emulated: %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
+  return zp::check_launch("zp_all_reduce_emulated");
+}
+
+// Test support: zp_sample_sharded for every rank of a world as one cooperative launch on one GPU.
+// logits_shards / noise_shards (or NULL) / tokens_outs: one pointer per rank.
+extern "C" int zp_sample_sharded_emulated(zp_comm* const* comms, int world, const void* const* logits_shards,
+                                          const float* temperatures, const float* const* noise_shards,
+                                          int64_t* const* tokens_outs, int n_rows, int vocab_shard, uint64_t seed,
+                                          int dtype, void* stream) {
+  using namespace zp::coll;
+  ZP_REQUIRE(comms && logits_shards && temperatures && tokens_outs, "zp_sample_sharded_emulated: null pointer");
+  ZP_REQUIRE(world == 2 || world == 4 || world == 8, "zp_sample_sharded_emulated: world size %d", world);
+  ZP_REQUIRE(n_rows > 0 && vocab_shard > 0, "zp_sample_sharded_emulated: bad sizes");
+  EmulatedWorld w{};
+  for (int r = 0; r < world; ++r) {
+    const zp_comm* c = comms[r];
+    ZP_REQUIRE(c && c->world == world && c->rank == r, "zp_sample_sharded_emulated: communicator %d", r);
+    ZP_REQUIRE((size_t)world * n_rows * 8 <= c->area_bytes, "zp_sample_sharded_emulated: too many rows for the areas");
+    for (int q = 0; q < world; ++q) ZP_REQUIRE(c->seg[q], "zp_sample_sharded_emulated: rank %d lacks segment %d", r, q);
+    for (int q = 0; q < MAX_WORLD; ++q) w.dev[r].seg[q] = c->seg[q];
+    w.dev[r].state = c->state; w.dev[r].area_bytes = c->area_bytes; w.dev[r].timeout_ns = c->timeout_ns;
+    w.dev[r].rank = r; w.dev[r].world = world;
+    w.in[r] = logits_shards[r]; w.out[r] = tokens_outs[r];
+    w.residual_out[r] = noise_shards ? (void*)noise_shards[r] : nullptr;
+  }
+  // 1024-thread blocks: one per SM; the ranks share the SMs
+  const int nblk = std::min(n_rows, std::max(1, comms[0]->sms / world));
+  void* args[] = {&w, (void*)&temperatures, &n_rows, &vocab_shard, &seed};
+  const dim3 grid(nblk, world);
+  cudaError_t e = cudaSuccess;
+  auto go = [&](auto kernel) {
+    e = cudaLaunchCooperativeKernel((const void*)kernel, grid, dim3(SAMPLE_THREADS), args, 0, (cudaStream_t)stream);
+  };
+  switch (world) {
+    case 2: ZP_DISPATCH_DTYPE(dtype, T, go(sample_sharded_emulated_kernel<T, 2>)); break;
+    case 4: ZP_DISPATCH_DTYPE(dtype, T, go(sample_sharded_emulated_kernel<T, 4>)); break;
+    default: ZP_DISPATCH_DTYPE(dtype, T, go(sample_sharded_emulated_kernel<T, 8>)); break;
+  }
+  if (e != cudaSuccess) { zp::set_error("zp_sample_sharded_emulated: %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
+  return zp::check_launch("zp_sample_sharded_emulated");
 }
