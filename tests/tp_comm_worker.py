@@ -144,7 +144,7 @@ def main():
     # (and the CPU oracle), with given draws and with the built-in generator
     from oracle import step_ops_oracle as S
     from zipage_b200.layers.step_ops import sample
-    for dtype, B, Vs in ((torch.bfloat16, 37, 5000), (torch.bfloat16, 300, 1001), (torch.float32, 64, 4096),
+    for dtype, B, Vs in ((torch.bfloat16, 37, 5000), (torch.bfloat16, 300, 1001), (torch.bfloat16, 700, 520), (torch.float32, 64, 4096),
                          (torch.float16, 5, 75968)):
         torch.manual_seed(3)                                  # replicated inputs
         V = Vs * world

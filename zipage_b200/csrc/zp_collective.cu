@@ -312,12 +312,12 @@ all_reduce_emulated_kernel(const EmulatedWorld w, int64_t nvec, int row_vecs, in
 // ---------------------------------------------------------------------------------------------
 // Sampler over a vocabulary sharded across the ranks, without gathering the logits.
 // Every rank holds logits[:, rank * Vs : (rank + 1) * Vs].  One launch on every rank:
-//   A. per row: the shard's maximum m_r of logits / t and z_r = sum exp(x / t - m_r); both pushed
-//      into every rank's input area; meeting;
+//   A. per row: the shard's maximum m_r of logits / t, then in one pass z_r = sum exp(x / t - m_r)
+//      and the race e_i / q_i with fast arithmetic (the two best candidates per thread are kept in
+//      shared memory); (m_r, z_r) pushed into every rank's segment; meeting;
 //   B. per row: M = max m_r, Z = sum z_r exp(m_r - M) (rank order: the same bits everywhere); the
-//      race e_i / q_i over the shard with fast arithmetic, the two best candidates per thread
-//      re-evaluated with the reference's expression (exp(x / t - M) / Z) / q, the shard's winner
-//      (value, global index) pushed into every rank's result area; meeting;
+//      kept candidates re-evaluated with the reference's expression (exp(x / t - M) / Z) / q, the
+//      shard's winner (value, global index) pushed into every rank's segment; meeting;
 //   C. per row: the best of the ranks' winners (larger value, then lower index) -> tokens_out.
 // All ranks end with the same tokens.  The draws of the built-in generator are keyed by the
 // global index, so they do not depend on the sharding.
@@ -334,12 +334,19 @@ __device__ __forceinline__ float exp1_draw(uint64_t seed, uint32_t row, uint32_t
 }
 
 constexpr int SAMPLE_THREADS = 1024;
+constexpr int SAMPLE_ROWS_PER_BLOCK = 4;
+constexpr int SAMPLE_SMEM = SAMPLE_ROWS_PER_BLOCK * 2 * SAMPLE_THREADS * (int)sizeof(int2);   // 64 KB
 
 template <typename T, int WORLD>
 __device__ __forceinline__ void
 sample_sharded_body(const Dev& c, const int blk, const int nblk, const T* __restrict__ logits,
                     const float* __restrict__ temperatures, const float* __restrict__ noise,
-                    int64_t* __restrict__ out, int rows, int Vs, uint64_t seed) {
+                    int64_t* __restrict__ out, int rows, int Vs, uint64_t seed, uint32_t row0) {
+  // (index, draw) of the two best candidates per thread for each of the block's rows
+  // (at most SAMPLE_ROWS_PER_BLOCK; `row0`: the first row's index in the caller's batch, which
+  // keys the generator)
+  extern __shared__ __align__(16) unsigned char sample_smem[];
+  int2* cand = reinterpret_cast<int2*>(sample_smem);
   constexpr int EPV = Pack<T>::N;
   __shared__ uint32_t s_epoch;
   __shared__ char* seg[MAX_WORLD];
@@ -367,8 +374,11 @@ sample_sharded_body(const Dev& c, const int blk, const int nblk, const T* __rest
     for (int i = nvec * EPV + threadIdx.x; i < Vs; i += SAMPLE_THREADS) fn(i, Elem<T>::to_f32(lr[i]));
   };
 
-  // ---- A: shard statistics ----
-  for (int row = blk; row < rows; row += nblk) {
+  // ---- A: shard statistics, and the race against the shard's own maximum ----
+  // (the order of the candidates does not depend on which maximum is subtracted; the two best per
+  // thread wait in shared memory for the global statistics)
+  int slot = 0;
+  for (int row = blk; row < rows; row += nblk, ++slot) {
     const T* lr = logits + (int64_t)row * Vs;
     const float t = temperatures[row];
     float mx = -INFINITY;
@@ -380,9 +390,24 @@ sample_sharded_body(const Dev& c, const int blk, const int nblk, const T* __rest
       mx = block_max(mx, red);
     }
     const float inv_t = 1.f / t;
+    const int64_t nbase = (int64_t)row * Vs;
+    const uint32_t gbase = (uint32_t)c.rank * (uint32_t)Vs;
     float z = 0.f;
-    for_each(lr, [&](int, float x) { z += __expf(fmaf(x, inv_t, -mx)); });
+    float r0 = -INFINITY, r1 = -INFINITY, q0 = 1.f, q1 = 1.f;
+    int i0 = 0x7fffffff, i1 = 0x7fffffff;
+    for_each(lr, [&](int i, float x) {
+      const float e = __expf(fmaf(x, inv_t, -mx));
+      z += e;
+      const float q = fmaxf(noise ? noise[nbase + i] : exp1_draw(seed, row0 + row, gbase + i), 1e-10f);
+      const float r = __fdividef(e, q);
+      if (r > r1) {
+        if (r > r0) { r1 = r0; q1 = q0; i1 = i0; r0 = r; q0 = q; i0 = i; }
+        else { r1 = r; q1 = q; i1 = i; }
+      }
+    });
     z = block_sum(z, red);
+    cand[(slot * 2 + 0) * SAMPLE_THREADS + threadIdx.x] = make_int2(i0, __float_as_int(q0));
+    cand[(slot * 2 + 1) * SAMPLE_THREADS + threadIdx.x] = make_int2(i1, __float_as_int(q1));
     if (threadIdx.x < WORLD)
       *reinterpret_cast<float2*>(area_of(seg, c.area_bytes, WORLD, threadIdx.x, parity, 0) +
                                  ((size_t)c.rank * rows + row) * 8) = make_float2(mx, z);
@@ -390,8 +415,9 @@ sample_sharded_body(const Dev& c, const int blk, const int nblk, const T* __rest
   }
   meet_peers(c, seg, 0, epoch, blk);
 
-  // ---- B: the race over the shard against the global maximum and sum ----
-  for (int row = blk; row < rows; row += nblk) {
+  // ---- B: the candidates' exact values against the global maximum and sum ----
+  slot = 0;
+  for (int row = blk; row < rows; row += nblk, ++slot) {
     const T* lr = logits + (int64_t)row * Vs;
     const float t = temperatures[row];
     float ms[WORLD], zs[WORLD];
@@ -406,29 +432,18 @@ sample_sharded_body(const Dev& c, const int blk, const int nblk, const T* __rest
     float zsum = 0.f;
 #pragma unroll
     for (int r = 0; r < WORLD; ++r) zsum += zs[r] * expf(ms[r] - m);
-    const float inv_t = 1.f / t;
-    const int64_t nbase = (int64_t)row * Vs;
     const uint32_t gbase = (uint32_t)c.rank * (uint32_t)Vs;
-    float r0 = -INFINITY, r1 = -INFINITY, q0 = 1.f, q1 = 1.f;
-    int i0 = 0x7fffffff, i1 = 0x7fffffff;
-    for_each(lr, [&](int i, float x) {
-      const float e = __expf(fmaf(x, inv_t, -m));
-      const float q = fmaxf(noise ? noise[nbase + i] : exp1_draw(seed, row, gbase + i), 1e-10f);
-      const float r = __fdividef(e, q);
-      if (r > r1) {
-        if (r > r0) { r1 = r0; q1 = q0; i1 = i0; r0 = r; q0 = q; i0 = i; }
-        else { r1 = r; q1 = q; i1 = i; }
-      }
-    });
-    auto exact = [&](int i, float q) -> float {   // the reference's value of a candidate
-      if (i == 0x7fffffff) return -INFINITY;
-      const float e = expf(__fdiv_rn(Elem<T>::to_f32(lr[i]), t) - m);
-      return __fdiv_rn(__fdiv_rn(e, zsum), q);
+    auto exact = [&](int2 cd) -> float {   // the reference's value of a candidate
+      if (cd.x == 0x7fffffff) return -INFINITY;
+      const float e = expf(__fdiv_rn(Elem<T>::to_f32(lr[cd.x]), t) - m);
+      return __fdiv_rn(__fdiv_rn(e, zsum), __int_as_float(cd.y));
     };
-    const float v0 = exact(i0, q0), v1 = exact(i1, q1);
+    const int2 c0 = cand[(slot * 2 + 0) * SAMPLE_THREADS + threadIdx.x];
+    const int2 c1 = cand[(slot * 2 + 1) * SAMPLE_THREADS + threadIdx.x];
+    const float v0 = exact(c0), v1 = exact(c1);
     float best = v0;
-    int besti = i0;
-    if (v1 > best || (v1 == best && i1 < besti)) { best = v1; besti = i1; }
+    int besti = c0.x;
+    if (v1 > best || (v1 == best && c1.x < besti)) { best = v1; besti = c1.x; }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -486,8 +501,8 @@ template <typename T, int WORLD>
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_sharded_kernel(const Dev c, const T* __restrict__ logits, const float* __restrict__ temperatures,
                       const float* __restrict__ noise, int64_t* __restrict__ out, int rows, int Vs,
-                      uint64_t seed) {
-  sample_sharded_body<T, WORLD>(c, blockIdx.x, gridDim.x, logits, temperatures, noise, out, rows, Vs, seed);
+                      uint64_t seed, uint32_t row0) {
+  sample_sharded_body<T, WORLD>(c, blockIdx.x, gridDim.x, logits, temperatures, noise, out, rows, Vs, seed, row0);
 }
 
 // Every rank as blocks of one cooperative launch on one GPU (test support, as above): rank r reads
@@ -508,7 +523,7 @@ sample_sharded_emulated_kernel(const EmulatedWorld w, const float* __restrict__ 
   }
   __syncthreads();
   sample_sharded_body<T, WORLD>(c, blockIdx.x, gridDim.x, (const T*)logits, temperatures, (const float*)noise,
-                                (int64_t*)out, rows, Vs, seed);
+                                (int64_t*)out, rows, Vs, seed, 0u);
 }
 
 }}  // namespace zp::coll
@@ -709,18 +724,30 @@ extern "C" int zp_sample_sharded(zp_comm* c, const void* logits, const float* te
   for (int r = 0; r < MAX_WORLD; ++r) d.seg[r] = c->seg[r];
   d.state = c->state; d.area_bytes = c->area_bytes; d.timeout_ns = c->timeout_ns;
   d.rank = c->rank; d.world = c->world;
-  const int grid = std::min(n_rows, std::min(c->sms, MAX_BLOCKS));
   cudaStream_t st = (cudaStream_t)stream;
-#define ZP_SAMPLE_WORLD(W)                                                                              \
-  ZP_DISPATCH_DTYPE(dtype, T, (sample_sharded_kernel<T, W><<<grid, SAMPLE_THREADS, 0, st>>>(            \
-                                  d, (const T*)logits, temperatures, noise, tokens_out, n_rows, vocab_shard, seed)))
-  switch (c->world) {
-    case 2: ZP_SAMPLE_WORLD(2); break;
-    case 4: ZP_SAMPLE_WORLD(4); break;
-    case 8: ZP_SAMPLE_WORLD(8); break;
-    default: zp::set_error("zp_sample_sharded: world size %d", c->world); return ZP_ERR_INVALID_ARGUMENT;
-  }
+  const int es = (int)zp::dtype_size(dtype);
+  const int max_grid = std::min(c->sms, MAX_BLOCKS);
+  // a block keeps the candidates of at most SAMPLE_ROWS_PER_BLOCK rows: larger batches take
+  // several launches (each a complete exchange)
+  for (int row0 = 0; row0 < n_rows; row0 += SAMPLE_ROWS_PER_BLOCK * max_grid) {
+    const int rows = std::min(n_rows - row0, SAMPLE_ROWS_PER_BLOCK * max_grid);
+    const int grid = std::min(rows, max_grid);
+    const char* lg = (const char*)logits + (size_t)row0 * vocab_shard * es;
+    const float* nz = noise ? noise + (size_t)row0 * vocab_shard : nullptr;
+#define ZP_SAMPLE_WORLD(W)                                                                               \
+  ZP_DISPATCH_DTYPE(dtype, T, {                                                                          \
+    cudaFuncSetAttribute(sample_sharded_kernel<T, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, SAMPLE_SMEM); \
+    sample_sharded_kernel<T, W><<<grid, SAMPLE_THREADS, SAMPLE_SMEM, st>>>(                              \
+        d, (const T*)lg, temperatures + row0, nz, tokens_out + row0, rows, vocab_shard, seed, (uint32_t)row0); \
+  })
+    switch (c->world) {
+      case 2: ZP_SAMPLE_WORLD(2); break;
+      case 4: ZP_SAMPLE_WORLD(4); break;
+      case 8: ZP_SAMPLE_WORLD(8); break;
+      default: zp::set_error("zp_sample_sharded: world size %d", c->world); return ZP_ERR_INVALID_ARGUMENT;
+    }
 #undef ZP_SAMPLE_WORLD
+  }
   return zp::check_launch("zp_sample_sharded");
 }
 
@@ -798,11 +825,15 @@ extern "C" int zp_sample_sharded_emulated(zp_comm* const* comms, int world, cons
   }
   // 1024-thread blocks: one per SM; the ranks share the SMs
   const int nblk = std::min(n_rows, std::max(1, comms[0]->sms / world));
+  ZP_REQUIRE(n_rows <= SAMPLE_ROWS_PER_BLOCK * nblk, "zp_sample_sharded_emulated: at most %d rows at this world size",
+             SAMPLE_ROWS_PER_BLOCK * nblk);
   void* args[] = {&w, (void*)&temperatures, &n_rows, &vocab_shard, &seed};
   const dim3 grid(nblk, world);
   cudaError_t e = cudaSuccess;
   auto go = [&](auto kernel) {
-    e = cudaLaunchCooperativeKernel((const void*)kernel, grid, dim3(SAMPLE_THREADS), args, 0, (cudaStream_t)stream);
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SAMPLE_SMEM);
+    e = cudaLaunchCooperativeKernel((const void*)kernel, grid, dim3(SAMPLE_THREADS), args, SAMPLE_SMEM,
+                                    (cudaStream_t)stream);
   };
   switch (world) {
     case 2: ZP_DISPATCH_DTYPE(dtype, T, go(sample_sharded_emulated_kernel<T, 2>)); break;
