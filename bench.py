@@ -279,7 +279,7 @@ def run_decode_step(args):
     over compressed tables (context 2049..2304 tokens in 9 pages), timed launch by launch and as
     one replayed CUDA graph whose inputs are device state only.  `value` is the graph's rate with
     the inputs already in the graph's buffers; `e2e` copies the step's inputs from pinned host
-    memory and reads the hidden states back.  Under torchrun (N = 2, 4, 8) the blocks are
+    memory, adds the LM head and the sampler, and reads the tokens back.  Under torchrun (N = 2, 4, 8) the blocks are
     tensor-parallel over the ranks (heads and MLP columns split, the same batch: strong scaling)
     with every all-reduce fused into the norm that consumes it, over peer memory; the same step on
     NCCL all-reduce + the RMSNorm kernel is timed beside it."""
@@ -330,7 +330,14 @@ def run_decode_step(args):
     runner = DecodeGraphRunner(model, cfg.hidden_size, max_bs=B, max_num_blocks=NBs + 1, query_cache_len=QCL,
                                device=dev, graph_bs=[B])
     stage('model built'); runner.capture(); stage('captured')
-    host_out = torch.empty((B, cfg.hidden_size), dtype=torch.bfloat16).pin_memory()
+    # the rest of ModelRunner.run for the end-to-end figure: LM head on this rank's vocabulary
+    # shard (cuBLAS), the sampler (sharded over the ranks when there are several), tokens to the host
+    from zipage_b200.layers.step_ops import sample
+    vs = cfg.vocab_size // world
+    lm_head = torch.empty((vs, cfg.hidden_size), dtype=torch.bfloat16, device=dev).normal_(0, 0.02)
+    temps = torch.full((B,), 0.7, device=dev)
+    host_out = torch.empty(B, dtype=torch.int64).pin_memory()
+    step_no = [0]
     d_args = [x.to(dev) for x in (ids, ntok, table, qid)]
     runner._fill(*d_args)
 
@@ -356,7 +363,10 @@ def run_decode_step(args):
     def e2e_step():
         out = runner.run(ids.to(dev, non_blocking=True), ntok.to(dev, non_blocking=True),
                          table.to(dev, non_blocking=True), qid.to(dev, non_blocking=True))
-        host_out.copy_(out, non_blocking=True)
+        logits = torch.nn.functional.linear(out, lm_head)
+        step_no[0] += 1
+        tok = comm.sample(logits, temps, seed=step_no[0]) if world > 1 else sample(logits, temps, seed=step_no[0])
+        host_out.copy_(tok, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     graph = runner.graphs[B]
@@ -408,7 +418,8 @@ def run_decode_step(args):
         "launch_by_launch_ms_per_step": ms_eager, "graph_speedup": ms_eager / ms_graph,
         "library_collective_launch_by_launch_ms_per_step": ms_lib, "comm_status": status if world > 1 else None,
         "e2e": {"value": B / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": host_out.numel() * 2},
+                "d2h_bytes_per_step": host_out.numel() * 8,
+                "includes": "LM head (cuBLAS) + sampler" + (" over the sharded vocabulary" if world > 1 else "")},
         "gpu_launches": per_step * args.steps, "own_kernels_per_step": per_step, "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "kernel": "whole step (this rank's weights + K/V read once)", "achieved": ach,
                      "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
