@@ -467,6 +467,8 @@ def run_tp_allreduce(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    flagged_ok = rows * hidden * 2 <= (2 << 20)
+
     def nccl_step():
         y.copy_(x)
         dist.all_reduce(y)
@@ -478,6 +480,8 @@ def run_tp_allreduce(args):
         "fused_two_shot": lambda: comm.all_reduce_add_rms_norm(x, res, w, 1e-6, algo="two_shot"),
         "plain_one_shot": lambda: comm.all_reduce(x, out=y, algo="one_shot"),
         "plain_two_shot": lambda: comm.all_reduce(x, out=y, algo="two_shot"),
+        "plain_flagged_lines": (lambda: comm.all_reduce(x, out=y, algo="flagged_lines")) if flagged_ok else None,
+        "fused_flagged_lines": (lambda: comm.all_reduce_add_rms_norm(x, res, w, 1e-6, algo="flagged_lines")) if flagged_ok else None,
         "nccl_all_reduce": lambda: dist.all_reduce(y),
         "nccl_all_reduce_then_rms_norm": nccl_step,
     }
@@ -498,7 +502,7 @@ def run_tp_allreduce(args):
                 fn()
         return graph
 
-    graphs = {k: graphed(fn) for k, fn in cases.items()}
+    graphs = {k: graphed(fn) for k, fn in cases.items() if fn is not None}
 
     def timed_graph(graph):
         graph.replay()
@@ -511,6 +515,7 @@ def run_tp_allreduce(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    cases = {k: v for k, v in cases.items() if v is not None}
     runs = {k: [] for k in cases}
     gruns = {k: [] for k in cases}
     with ClockSampler(dev.index or 0) as clocks:

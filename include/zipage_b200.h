@@ -339,8 +339,10 @@ int zp_comm_attach_peer(zp_comm* comm, int peer, void* segment);
 int zp_comm_status(zp_comm* comm, int* status_out);   /* synchronous 4-byte read */
 int zp_comm_destroy(zp_comm* comm);
 /* out[i] = T(sum over ranks of in[i]); count elements, count * sizeof(T) a multiple of 16 and at
- * most max_bytes; in == out allowed.  algo: 0 = by size and world, 1 = one-shot (every rank reads
- * all inputs), 2 = two-shot (reduce-scatter into every rank's result area, then a local read). */
+ * most max_bytes; in == out allowed.  algo: 0 = by size and world, 1 = one-shot (every rank gets
+ * all inputs, one meeting), 2 = two-shot (reduce-scatter into every rank's result area, then a
+ * local read; two meetings), 3 = flagged lines (one-shot with the epoch stored beside every
+ * payload word instead of a meeting; at most 2 MiB; the default up to 512 KiB). */
 int zp_all_reduce(zp_comm* comm, const void* in, void* out, int64_t count, int dtype, int algo,
                   void* stream);
 /* x = all-reduce(in) [rows, hidden]; s = x + residual; residual_out = T(s);

@@ -123,7 +123,7 @@ def test_world_sizes_as_one_cooperative_launch(world):
 
         for dtype in (torch.bfloat16, torch.float32):
             for rows, elems in ((40, 1024), (3, 4096 if dtype == torch.float32 else 8192), (300, 512)):
-                for algo in (1, 2):
+                for algo in (1, 2, 3):
                     for _ in range(3):      # consecutive calls alternate the areas
                         xs = [torch.randn(rows, elems, device=dev, generator=g).to(dtype) for _ in range(world)]
                         outs = [torch.empty_like(x) for x in xs]

@@ -99,7 +99,9 @@ def main():
     for dtype in (torch.bfloat16, torch.float16, torch.float32):
         per = 16 // torch.empty((), dtype=dtype).element_size()
         for n in (per, 4096, 1000 * per + 3 * per, 256 * 4096, 2 * 1024 * 1024):
-            for algo in ("one_shot", "two_shot", "auto"):
+            for algo in ("one_shot", "two_shot", "auto", "flagged_lines"):
+                if algo == "flagged_lines" and n * (16 // per) > (2 << 20):
+                    continue                                  # that form carries at most 2 MiB
                 x = torch.randn(n, device=dev, generator=g).to(dtype)
                 want = expected(x, dtype)
                 got = comm.all_reduce(x.clone(), algo=algo)
@@ -114,7 +116,7 @@ def main():
     wants = [expected(x, torch.bfloat16) for x in xs]
     torch.cuda.synchronize()
     dist.barrier()
-    for algo in ("one_shot", "two_shot"):
+    for algo in ("one_shot", "two_shot", "auto"):   # auto: flagged lines up to 2 MiB, meetings above
         outs = [comm.all_reduce(x, out=torch.empty_like(x), algo=algo) for x in xs]
         torch.cuda.synchronize()
         for o, w in zip(outs, wants):
@@ -127,7 +129,9 @@ def main():
             torch.manual_seed(7)   # residual and weight are replicated across the ranks
             res = torch.randn(rows, hidden).to(dtype).to(dev)
             w = (1 + 0.1 * torch.randn(hidden)).to(dtype).to(dev)
-            for algo in ("one_shot", "two_shot"):
+            for algo in ("one_shot", "two_shot", "flagged_lines"):
+                if algo == "flagged_lines" and x.numel() * x.element_size() > (2 << 20):
+                    continue
                 y0, r0 = rms_norm(comm.all_reduce(x.clone(), algo=algo), w, 1e-6, res)
                 y1, r1 = comm.all_reduce_add_rms_norm(x, res, w, 1e-6, algo=algo)
                 assert torch.equal(r0, r1), (dtype, rows, hidden, algo)
@@ -186,6 +190,7 @@ def main():
     t3 = timed(lambda: dist.all_reduce(y))
     small = torch.randn(8 * 4096, device=dev, generator=g).to(torch.bfloat16)
     s1 = timed(lambda: comm.all_reduce(small, algo="one_shot"))
+    s2 = timed(lambda: comm.all_reduce(small, algo="flagged_lines"))
     s3 = timed(lambda: dist.all_reduce(small))
     # the reference's route for 512 rows of a 151 936-token vocabulary: gather the shards to rank 0,
     # concatenate, sample there
@@ -206,7 +211,7 @@ def main():
     assert comm.status() == 0
     if rank == 0:
         print(f"TPCOMM world={world} 4MiB: one_shot {t1:.1f} us, two_shot {t2:.1f} us, nccl {t3:.1f} us; "
-              f"64KiB: one_shot {s1:.1f} us, nccl {s3:.1f} us", flush=True)
+              f"64KiB: one_shot {s1:.1f} us, flagged lines {s2:.1f} us, nccl {s3:.1f} us", flush=True)
     comm.close()
     dist.destroy_process_group()
     print(f"rank {rank} OK", flush=True)

@@ -49,6 +49,7 @@ struct Dev {
   char* seg[MAX_WORLD];     // every rank's segment as mapped here (seg[rank] is the local one)
   uint32_t* state;          // local only: [0] epoch, [1] blocks done, [2] status
   size_t area_bytes;
+  size_t ll_bytes;          // payload capacity of one flagged-line slot (0: none)
   long long timeout_ns;
   int rank, world;
 };
@@ -74,6 +75,39 @@ __device__ __forceinline__ uint32_t* flag_of(char* const* seg, int owner, int ph
 __device__ __forceinline__ char* area_of(char* const* seg, size_t area_bytes, int world, int owner,
                                          uint32_t parity, int which) {
   return seg[owner] + FLAG_BYTES + (size_t)(parity * (world + 1) + which) * area_bytes;
+}
+
+// Flagged lines (mode 2): a 16-byte store carries two 4-byte payload words, each followed by the
+// call's epoch, so the data announces itself — no fence, no separate flag, no meeting; it relies on
+// 8-byte stores arriving whole.  A payload vector of 16 bytes becomes two such lines.  Slot
+// (parity, source rank) of `owner`'s segment, after the areas:
+__device__ __forceinline__ char* ll_of(char* const* seg, size_t area_bytes, size_t ll_bytes, int world, int owner,
+                                       uint32_t parity, int src) {
+  return seg[owner] + FLAG_BYTES + 2 * (size_t)(world + 1) * area_bytes +
+         (size_t)(parity * world + src) * 2 * ll_bytes;
+}
+__device__ __forceinline__ uint4 ld_volatile16(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+// Wait (bounded) for the two lines of payload vector `v` of a slot; returns the 16 payload bytes.
+__device__ __forceinline__ int4 ll_read(const Dev& c, const char* slot, int64_t v, uint32_t epoch) {
+  const char* p = slot + v * 32;
+  uint4 a = ld_volatile16(p), b = ld_volatile16(p + 16);
+  if (a.y != epoch || a.w != epoch || b.y != epoch || b.w != epoch) {
+    const long long t0 = now_ns();
+    uint32_t spins = 0;
+    do {
+      a = ld_volatile16(p); b = ld_volatile16(p + 16);
+      if ((++spins & 255u) == 0 && now_ns() - t0 > c.timeout_ns) {
+        atomicCAS(c.state + 2, 0u, (uint32_t)STATUS_TIMEOUT);
+        break;
+      }
+    } while (a.y != epoch || a.w != epoch || b.y != epoch || b.w != epoch);
+  }
+  return make_int4((int)a.x, (int)a.z, (int)b.x, (int)b.z);
 }
 
 __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
@@ -117,11 +151,13 @@ template <typename T> struct Pack {
 
 // Rows of `row_vecs` 16-byte vectors (<= THREADS * VPT); row r belongs to block r % gridDim.x.
 // `blk` of `nblk`: this block's index among the rank's blocks (the x dimension of the grid).
-template <typename T, int WORLD, bool TWO_SHOT, bool FUSED>
+// MODE 0: one-shot, 1: two-shot, 2: flagged lines (one-shot without a meeting).
+template <typename T, int WORLD, int MODE, bool FUSED>
 __device__ __forceinline__ void
 all_reduce_body(const Dev& c, const int blk, const int nblk, const T* in, T* out, int64_t nvec, int row_vecs,
                 int64_t nrows, const T* residual, const T* __restrict__ weight, T* residual_out, float eps) {
   constexpr int EPV = Pack<T>::N;
+  constexpr bool TWO_SHOT = MODE == 1, LL = MODE == 2;
   __shared__ uint32_t s_epoch;
   __shared__ float red[32];
   __shared__ char* seg[MAX_WORLD];
@@ -139,7 +175,15 @@ all_reduce_body(const Dev& c, const int blk, const int nblk, const T* in, T* out
     const int64_t v0 = row * row_vecs, v1 = min(v0 + row_vecs, nvec);
     for (int64_t v = v0 + threadIdx.x; v < v1; v += THREADS) {
       const int4 x = ld16(reinterpret_cast<const char*>(in) + v * 16);
-      if constexpr (TWO_SHOT) {
+      if constexpr (LL) {
+        const int4 la = make_int4(x.x, (int)epoch, x.y, (int)epoch), lb = make_int4(x.z, (int)epoch, x.w, (int)epoch);
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r) {
+          char* dst = ll_of(seg, c.area_bytes, c.ll_bytes, WORLD, r, parity, c.rank) + v * 32;
+          st16(dst, la);
+          st16(dst + 16, lb);
+        }
+      } else if constexpr (TWO_SHOT) {
         st16(area_of(seg, c.area_bytes, WORLD, (int)((v >> 5) % WORLD), parity, c.rank) + v * 16, x);
       } else {
 #pragma unroll
@@ -147,7 +191,7 @@ all_reduce_body(const Dev& c, const int blk, const int nblk, const T* in, T* out
       }
     }
   }
-  meet_peers(c, seg, 0, epoch, blk);
+  if constexpr (!LL) meet_peers(c, seg, 0, epoch, blk);
 
   if constexpr (TWO_SHOT) {
     for (int64_t row = blk; row < nrows; row += nblk) {
@@ -176,7 +220,9 @@ all_reduce_body(const Dev& c, const int blk, const int nblk, const T* in, T* out
   constexpr int NSRC = TWO_SHOT ? 1 : WORLD;
   const char* src[NSRC];
 #pragma unroll
-  for (int r = 0; r < NSRC; ++r) src[r] = area_of(seg, c.area_bytes, WORLD, c.rank, parity, TWO_SHOT ? WORLD : r);
+  for (int r = 0; r < NSRC; ++r)
+    src[r] = LL ? ll_of(seg, c.area_bytes, c.ll_bytes, WORLD, c.rank, parity, r)
+                : area_of(seg, c.area_bytes, WORLD, c.rank, parity, TWO_SHOT ? WORLD : r);
   Pack<T> raw[VPT][NSRC];
 #pragma unroll
   for (int i = 0; i < VPT; ++i)
@@ -189,7 +235,8 @@ all_reduce_body(const Dev& c, const int blk, const int nblk, const T* in, T* out
       const int64_t v = v0 + threadIdx.x + i * THREADS;
       if (v < v1) {
 #pragma unroll
-        for (int r = 0; r < NSRC; ++r) raw[i][r].raw = ld16_l2(src[r] + v * 16);
+        for (int r = 0; r < NSRC; ++r)
+          raw[i][r].raw = LL ? ll_read(c, src[r], v, epoch) : ld16_l2(src[r] + v * 16);
       }
     }
   };
@@ -268,11 +315,12 @@ all_reduce_body(const Dev& c, const int blk, const int nblk, const T* in, T* out
   }
 }
 
-template <typename T, int WORLD, bool TWO_SHOT, bool FUSED>
+// MODE 0: one-shot, 1: two-shot, 2: flagged lines (one-shot without a meeting).
+template <typename T, int WORLD, int MODE, bool FUSED>
 __global__ void __launch_bounds__(THREADS)
 all_reduce_kernel(const Dev c, const T* in, T* out, int64_t nvec, int row_vecs, int64_t nrows,
                   const T* residual, const T* __restrict__ weight, T* residual_out, float eps) {
-  all_reduce_body<T, WORLD, TWO_SHOT, FUSED>(c, blockIdx.x, gridDim.x, in, out, nvec, row_vecs, nrows, residual,
+  all_reduce_body<T, WORLD, MODE, FUSED>(c, blockIdx.x, gridDim.x, in, out, nvec, row_vecs, nrows, residual,
                                              weight, residual_out, eps);
 }
 
@@ -286,7 +334,7 @@ struct EmulatedWorld {
   void* residual_out[MAX_WORLD];
 };
 
-template <typename T, int WORLD, bool TWO_SHOT, bool FUSED>
+template <typename T, int WORLD, int MODE, bool FUSED>
 __global__ void __launch_bounds__(THREADS)
 all_reduce_emulated_kernel(const EmulatedWorld w, int64_t nvec, int row_vecs, int64_t nrows, const T* residual,
                            const T* __restrict__ weight, float eps) {
@@ -305,7 +353,7 @@ all_reduce_emulated_kernel(const EmulatedWorld w, int64_t nvec, int row_vecs, in
       if (r == (int)blockIdx.y) { in = w.in[r]; out = w.out[r]; res_out = w.residual_out[r]; }
   }
   __syncthreads();
-  all_reduce_body<T, WORLD, TWO_SHOT, FUSED>(c, blockIdx.x, gridDim.x, (const T*)in, (T*)out, nvec, row_vecs, nrows,
+  all_reduce_body<T, WORLD, MODE, FUSED>(c, blockIdx.x, gridDim.x, (const T*)in, (T*)out, nvec, row_vecs, nrows,
                                              residual, weight, (T*)res_out, eps);
 }
 
@@ -531,6 +579,7 @@ sample_sharded_emulated_kernel(const EmulatedWorld w, const float* __restrict__ 
 struct zp_comm {
   int rank = 0, world = 0, device = 0, sms = 0;
   size_t area_bytes = 0;
+  size_t ll_bytes = 0;
   char* seg[zp::coll::MAX_WORLD] = {};
   bool ipc_opened[zp::coll::MAX_WORLD] = {};
   uint32_t* state = nullptr;
@@ -539,18 +588,25 @@ struct zp_comm {
 
 namespace {
 
+constexpr size_t LL_MAX_BYTES = 2u << 20;   // largest message sent as flagged lines
+// ... and the largest for which they are the default: measured on 2 GPUs, 64 KiB 7 us against
+// 10.4 us for the one-shot form with a meeting, 2 MiB 17.5 us against 15.7 us
+constexpr size_t LL_AUTO_BYTES = 512u << 10;
+
+size_t ll_bytes_for(size_t area_bytes) { return std::min(area_bytes, LL_MAX_BYTES); }
 size_t segment_bytes(size_t area_bytes, int world) {
-  return zp::coll::FLAG_BYTES + 2 * (size_t)(world + 1) * area_bytes;
+  return zp::coll::FLAG_BYTES + 2 * (size_t)(world + 1) * area_bytes +
+         2 * (size_t)world * 2 * ll_bytes_for(area_bytes);
 }
 
 template <typename T, int WORLD>
-void launch(const zp_comm* c, bool two_shot, bool fused, const void* in, void* out, int64_t nvec,
+void launch(const zp_comm* c, int mode, bool fused, const void* in, void* out, int64_t nvec,
             int row_vecs, int64_t nrows, const void* residual, const void* weight, void* residual_out,
             float eps, cudaStream_t st) {
   using namespace zp::coll;
   Dev d;
   for (int r = 0; r < MAX_WORLD; ++r) d.seg[r] = c->seg[r];
-  d.state = c->state; d.area_bytes = c->area_bytes; d.timeout_ns = c->timeout_ns;
+  d.state = c->state; d.area_bytes = c->area_bytes; d.ll_bytes = c->ll_bytes; d.timeout_ns = c->timeout_ns;
   d.rank = c->rank; d.world = c->world;
   auto go = [&](auto kernel) {
     // one block per SM: every block of the launch is resident at once (blocks wait for their
@@ -559,8 +615,9 @@ void launch(const zp_comm* c, bool two_shot, bool fused, const void* in, void* o
     kernel<<<grid, THREADS, 0, st>>>(d, (const T*)in, (T*)out, nvec, row_vecs, nrows, (const T*)residual,
                                      (const T*)weight, (T*)residual_out, eps);
   };
-  if (two_shot) { if (fused) go(all_reduce_kernel<T, WORLD, true, true>); else go(all_reduce_kernel<T, WORLD, true, false>); }
-  else          { if (fused) go(all_reduce_kernel<T, WORLD, false, true>); else go(all_reduce_kernel<T, WORLD, false, false>); }
+  if (mode == 2)      { if (fused) go(all_reduce_kernel<T, WORLD, 2, true>); else go(all_reduce_kernel<T, WORLD, 2, false>); }
+  else if (mode == 1) { if (fused) go(all_reduce_kernel<T, WORLD, 1, true>); else go(all_reduce_kernel<T, WORLD, 1, false>); }
+  else                { if (fused) go(all_reduce_kernel<T, WORLD, 0, true>); else go(all_reduce_kernel<T, WORLD, 0, false>); }
 }
 
 int run(zp_comm* c, int algo, bool fused, const void* in, void* out, int64_t nvec, int row_vecs,
@@ -569,17 +626,23 @@ int run(zp_comm* c, int algo, bool fused, const void* in, void* out, int64_t nve
   using namespace zp::coll;
   ZP_REQUIRE(c && c->state, "%s: null communicator", what);
   for (int r = 0; r < c->world; ++r) ZP_REQUIRE(c->seg[r], "%s: the segment of rank %d is not attached", what, r);
-  ZP_REQUIRE(algo >= 0 && algo <= 2, "%s: algorithm %d (0 auto, 1 one-shot, 2 two-shot)", what, algo);
+  ZP_REQUIRE(algo >= 0 && algo <= 3, "%s: algorithm %d (0 auto, 1 one-shot, 2 two-shot, 3 flagged lines)", what, algo);
+  ZP_REQUIRE(algo != 3 || (size_t)nvec * 16 <= c->ll_bytes, "%s: flagged lines carry at most %zu bytes", what, c->ll_bytes);
   ZP_REQUIRE((size_t)nvec * 16 <= c->area_bytes, "%s: %lld bytes exceed the communicator's %zu", what,
              (long long)nvec * 16, c->area_bytes);
   ZP_REQUIRE(((uintptr_t)in | (uintptr_t)out | (uintptr_t)residual | (uintptr_t)weight | (uintptr_t)residual_out) % 16 == 0,
              "%s: pointers must be 16-byte aligned", what);
   if (nvec == 0) return ZP_OK;
   // one-shot moves (world-1) x the message into every GPU, two-shot 2 x (world-1)/world of it
-  const bool two_shot = algo == 2 || (algo == 0 && c->world > 2 && (size_t)nvec * 16 >= (512u << 10));
+  // small messages go as flagged lines (twice the bytes on the link, but no fence and no
+  // meeting: a decode step's messages are latency-bound); above that one-shot moves (world-1) x
+  // the message into every GPU, two-shot 2 x (world-1)/world of it
+  int mode;
+  if (algo == 0) mode = (size_t)nvec * 16 <= std::min(c->ll_bytes, LL_AUTO_BYTES) ? 2 : (c->world > 2 ? 1 : 0);
+  else mode = algo - 1;
   cudaStream_t st = (cudaStream_t)stream;
 #define ZP_COLL_WORLD(W) \
-  ZP_DISPATCH_DTYPE(dtype, T, (launch<T, W>(c, two_shot, fused, in, out, nvec, row_vecs, nrows, residual, weight, residual_out, eps, st)))
+  ZP_DISPATCH_DTYPE(dtype, T, (launch<T, W>(c, mode, fused, in, out, nvec, row_vecs, nrows, residual, weight, residual_out, eps, st)))
   switch (c->world) {
     case 2: ZP_COLL_WORLD(2); break;
     case 4: ZP_COLL_WORLD(4); break;
@@ -602,12 +665,16 @@ extern "C" int zp_comm_create(int rank, int world, size_t max_bytes, int timeout
   ZP_REQUIRE(c, "zp_comm_create: out of host memory");
   c->rank = rank; c->world = world;
   c->area_bytes = (max_bytes + 255) / 256 * 256;
+  c->ll_bytes = ll_bytes_for(c->area_bytes);
   c->timeout_ns = (long long)timeout_ms * 1000000ll;
   cudaError_t e = cudaGetDevice(&c->device);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&c->sms, cudaDevAttrMultiProcessorCount, c->device);
   void* seg = nullptr; void* state = nullptr;
   if (e == cudaSuccess) e = cudaMalloc(&seg, segment_bytes(c->area_bytes, world));
   if (e == cudaSuccess) e = cudaMemset(seg, 0, FLAG_BYTES);
+  if (e == cudaSuccess)   // no line of the flagged-line slots may carry a future epoch
+    e = cudaMemset((char*)seg + FLAG_BYTES + 2 * (size_t)(world + 1) * c->area_bytes, 0,
+                   2 * (size_t)world * 2 * c->ll_bytes);
   if (e == cudaSuccess) e = cudaMalloc(&state, 256);
   if (e == cudaSuccess) e = cudaMemset(state, 0, 256);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
@@ -722,7 +789,7 @@ extern "C" int zp_sample_sharded(zp_comm* c, const void* logits, const float* te
              (size_t)c->world * n_rows * 8, c->area_bytes);
   Dev d;
   for (int r = 0; r < MAX_WORLD; ++r) d.seg[r] = c->seg[r];
-  d.state = c->state; d.area_bytes = c->area_bytes; d.timeout_ns = c->timeout_ns;
+  d.state = c->state; d.area_bytes = c->area_bytes; d.ll_bytes = c->ll_bytes; d.timeout_ns = c->timeout_ns;
   d.rank = c->rank; d.world = c->world;
   cudaStream_t st = (cudaStream_t)stream;
   const int es = (int)zp::dtype_size(dtype);
@@ -760,7 +827,7 @@ extern "C" int zp_all_reduce_emulated(zp_comm* const* comms, int world, const vo
   using namespace zp::coll;
   ZP_REQUIRE(comms && ins && outs, "zp_all_reduce_emulated: null pointer");
   ZP_REQUIRE(world == 2 || world == 4 || world == 8, "zp_all_reduce_emulated: world size %d", world);
-  ZP_REQUIRE(algo == 1 || algo == 2, "zp_all_reduce_emulated: algorithm %d (1 one-shot, 2 two-shot)", algo);
+  ZP_REQUIRE(algo >= 1 && algo <= 3, "zp_all_reduce_emulated: algorithm %d (1 one-shot, 2 two-shot, 3 flagged lines)", algo);
   const int64_t row_bytes = (int64_t)row_elems * (int64_t)zp::dtype_size(dtype);
   ZP_REQUIRE(rows > 0 && row_elems > 0 && row_bytes % 16 == 0 && row_bytes / 16 <= THREADS * VPT,
              "zp_all_reduce_emulated: bad row size");
@@ -769,10 +836,12 @@ extern "C" int zp_all_reduce_emulated(zp_comm* const* comms, int world, const vo
   for (int r = 0; r < world; ++r) {
     const zp_comm* c = comms[r];
     ZP_REQUIRE(c && c->world == world && c->rank == r, "zp_all_reduce_emulated: communicator %d", r);
-    ZP_REQUIRE((size_t)(rows * row_bytes) <= c->area_bytes, "zp_all_reduce_emulated: message exceeds the areas");
+    ZP_REQUIRE((size_t)(rows * row_bytes) <= (algo == 3 ? c->ll_bytes : c->area_bytes),
+               "zp_all_reduce_emulated: message exceeds the areas");
     for (int q = 0; q < world; ++q) ZP_REQUIRE(c->seg[q], "zp_all_reduce_emulated: rank %d lacks segment %d", r, q);
     for (int q = 0; q < MAX_WORLD; ++q) w.dev[r].seg[q] = c->seg[q];
-    w.dev[r].state = c->state; w.dev[r].area_bytes = c->area_bytes; w.dev[r].timeout_ns = c->timeout_ns;
+    w.dev[r].state = c->state; w.dev[r].area_bytes = c->area_bytes; w.dev[r].ll_bytes = c->ll_bytes;
+    w.dev[r].timeout_ns = c->timeout_ns;
     w.dev[r].rank = r; w.dev[r].world = world;
     w.in[r] = ins[r]; w.out[r] = outs[r]; w.residual_out[r] = fused ? residual_outs[r] : nullptr;
   }
@@ -788,8 +857,9 @@ extern "C" int zp_all_reduce_emulated(zp_comm* const* comms, int world, const vo
   };
 #define ZP_EMU(W)                                                                                     \
   ZP_DISPATCH_DTYPE(dtype, T, {                                                                       \
-    if (algo == 2) { if (fused) go(all_reduce_emulated_kernel<T, W, true, true>); else go(all_reduce_emulated_kernel<T, W, true, false>); } \
-    else           { if (fused) go(all_reduce_emulated_kernel<T, W, false, true>); else go(all_reduce_emulated_kernel<T, W, false, false>); } \
+    if (algo == 3)      { if (fused) go(all_reduce_emulated_kernel<T, W, 2, true>); else go(all_reduce_emulated_kernel<T, W, 2, false>); } \
+    else if (algo == 2) { if (fused) go(all_reduce_emulated_kernel<T, W, 1, true>); else go(all_reduce_emulated_kernel<T, W, 1, false>); } \
+    else                { if (fused) go(all_reduce_emulated_kernel<T, W, 0, true>); else go(all_reduce_emulated_kernel<T, W, 0, false>); } \
   })
   switch (world) {
     case 2: ZP_EMU(2); break;
@@ -818,7 +888,8 @@ extern "C" int zp_sample_sharded_emulated(zp_comm* const* comms, int world, cons
     ZP_REQUIRE((size_t)world * n_rows * 8 <= c->area_bytes, "zp_sample_sharded_emulated: too many rows for the areas");
     for (int q = 0; q < world; ++q) ZP_REQUIRE(c->seg[q], "zp_sample_sharded_emulated: rank %d lacks segment %d", r, q);
     for (int q = 0; q < MAX_WORLD; ++q) w.dev[r].seg[q] = c->seg[q];
-    w.dev[r].state = c->state; w.dev[r].area_bytes = c->area_bytes; w.dev[r].timeout_ns = c->timeout_ns;
+    w.dev[r].state = c->state; w.dev[r].area_bytes = c->area_bytes; w.dev[r].ll_bytes = c->ll_bytes;
+    w.dev[r].timeout_ns = c->timeout_ns;
     w.dev[r].rank = r; w.dev[r].world = world;
     w.in[r] = logits_shards[r]; w.out[r] = tokens_outs[r];
     w.residual_out[r] = noise_shards ? (void*)noise_shards[r] : nullptr;

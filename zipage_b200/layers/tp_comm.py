@@ -18,7 +18,7 @@ from torch import nn
 from .. import _lib as L
 from ..kernel import _count
 
-ALGO = {"auto": 0, "one_shot": 1, "two_shot": 2}
+ALGO = {"auto": 0, "one_shot": 1, "two_shot": 2, "flagged_lines": 3}
 
 
 class TPCommunicator:
