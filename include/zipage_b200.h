@@ -355,11 +355,12 @@ int zp_all_reduce_add_rms_norm(zp_comm* comm, const void* in, const void* residu
 /* Replaces ParallelLMHead's gather of the vocabulary shards to rank 0 (zipage/layers/embed_head.py:
  * 27-34: dist.gather + torch.cat) followed by Sampler.forward on rank 0 (zipage/layers/sampler.py:
  * 17-31): every rank runs the exponential race on its own shard logits[:, rank*Vs:(rank+1)*Vs]
- * and the ranks exchange, per row, 8 bytes of softmax statistics and 8 bytes of (value, index) —
+ * and the ranks exchange, per row, 8 bytes of softmax statistics and 8 bytes of (value, index)
+ * (each as one 16-byte line that carries the call's epoch beside the payload: no meeting) —
  * one launch per rank, no library collective, every rank ends with the same tokens_out [n_rows].
  * noise: this rank's shard [n_rows, Vs] of the Exp(1) draws, or NULL for the generator of
  * zp_sample (keyed by the global index: the same draws whatever the sharding).
- * comm's max_bytes must be at least world * n_rows * 8. */
+ * comm's max_bytes must be at least 16 * min(n_rows, 4 * SM count). */
 int zp_sample_sharded(zp_comm* comm, const void* logits, const float* temperatures, const float* noise,
                       int64_t* tokens_out, int n_rows, int vocab_shard, uint64_t seed, int dtype,
                       void* stream);

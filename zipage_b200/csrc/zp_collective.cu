@@ -110,6 +110,23 @@ __device__ __forceinline__ int4 ll_read(const Dev& c, const char* slot, int64_t 
   return make_int4((int)a.x, (int)a.z, (int)b.x, (int)b.z);
 }
 
+// Wait (bounded) for one line {a, epoch, b, epoch}; returns (a, b).
+__device__ __forceinline__ uint2 ll_read_line(const Dev& c, const char* p, uint32_t epoch) {
+  uint4 a = ld_volatile16(p);
+  if (a.y != epoch || a.w != epoch) {
+    const long long t0 = now_ns();
+    uint32_t spins = 0;
+    do {
+      a = ld_volatile16(p);
+      if ((++spins & 255u) == 0 && now_ns() - t0 > c.timeout_ns) {
+        atomicCAS(c.state + 2, 0u, (uint32_t)STATUS_TIMEOUT);
+        break;
+      }
+    } while (a.y != epoch || a.w != epoch);
+  }
+  return make_uint2(a.x, a.z);
+}
+
 __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -362,10 +379,10 @@ all_reduce_emulated_kernel(const EmulatedWorld w, int64_t nvec, int row_vecs, in
 // Every rank holds logits[:, rank * Vs : (rank + 1) * Vs].  One launch on every rank:
 //   A. per row: the shard's maximum m_r of logits / t, then in one pass z_r = sum exp(x / t - m_r)
 //      and the race e_i / q_i with fast arithmetic (the two best candidates per thread are kept in
-//      shared memory); (m_r, z_r) pushed into every rank's segment; meeting;
+//      shared memory); (m_r, z_r) pushed into every rank's segment as a flagged line;
 //   B. per row: M = max m_r, Z = sum z_r exp(m_r - M) (rank order: the same bits everywhere); the
 //      kept candidates re-evaluated with the reference's expression (exp(x / t - M) / Z) / q, the
-//      shard's winner (value, global index) pushed into every rank's segment; meeting;
+//      shard's winner (value, global index) pushed into every rank's segment as a flagged line;
 //   C. per row: the best of the ranks' winners (larger value, then lower index) -> tokens_out.
 // All ranks end with the same tokens.  The draws of the built-in generator are keyed by the
 // global index, so they do not depend on the sharding.
@@ -456,12 +473,11 @@ sample_sharded_body(const Dev& c, const int blk, const int nblk, const T* __rest
     z = block_sum(z, red);
     cand[(slot * 2 + 0) * SAMPLE_THREADS + threadIdx.x] = make_int2(i0, __float_as_int(q0));
     cand[(slot * 2 + 1) * SAMPLE_THREADS + threadIdx.x] = make_int2(i1, __float_as_int(q1));
-    if (threadIdx.x < WORLD)
-      *reinterpret_cast<float2*>(area_of(seg, c.area_bytes, WORLD, threadIdx.x, parity, 0) +
-                                 ((size_t)c.rank * rows + row) * 8) = make_float2(mx, z);
+    if (threadIdx.x < WORLD)   // one flagged line per row and peer: {m, epoch, z, epoch}
+      st16(ll_of(seg, c.area_bytes, c.ll_bytes, WORLD, threadIdx.x, parity, c.rank) + (size_t)row * 16,
+           make_int4(__float_as_int(mx), (int)epoch, __float_as_int(z), (int)epoch));
     __syncthreads();
   }
-  meet_peers(c, seg, 0, epoch, blk);
 
   // ---- B: the candidates' exact values against the global maximum and sum ----
   slot = 0;
@@ -471,11 +487,11 @@ sample_sharded_body(const Dev& c, const int blk, const int nblk, const T* __rest
     float ms[WORLD], zs[WORLD];
     float m = -INFINITY;
 #pragma unroll
-    for (int r = 0; r < WORLD; ++r) {
-      const float2 st = __ldcg(reinterpret_cast<const float2*>(area_of(seg, c.area_bytes, WORLD, c.rank, parity, 0) +
-                                                                ((size_t)r * rows + row) * 8));
-      ms[r] = st.x; zs[r] = st.y;
-      m = fmaxf(m, st.x);
+    for (int r = 0; r < WORLD; ++r) {   // every thread polls the same lines (broadcast loads)
+      const uint2 st = ll_read_line(c, ll_of(seg, c.area_bytes, c.ll_bytes, WORLD, c.rank, parity, r) + (size_t)row * 16,
+                                    epoch);
+      ms[r] = __uint_as_float(st.x); zs[r] = __uint_as_float(st.y);
+      m = fmaxf(m, ms[r]);
     }
     float zsum = 0.f;
 #pragma unroll
@@ -510,13 +526,12 @@ sample_sharded_body(const Dev& c, const int blk, const int nblk, const T* __rest
       }
       if (lane < WORLD) {
         const int gi = besti == 0x7fffffff ? 0x7fffffff : (int)gbase + besti;
-        *reinterpret_cast<float2*>(area_of(seg, c.area_bytes, WORLD, lane, parity, 1) +
-                                   ((size_t)c.rank * rows + row) * 8) = make_float2(best, __int_as_float(gi));
+        st16(ll_of(seg, c.area_bytes, c.ll_bytes, WORLD, lane, parity, c.rank) + ((size_t)rows + row) * 16,
+             make_int4(__float_as_int(best), (int)epoch, gi, (int)epoch));
       }
     }
     __syncthreads();
   }
-  meet_peers(c, seg, 1, epoch, blk);
 
   // ---- C: the best of the shards' winners ----
   for (int row = blk; row < rows; row += nblk) {
@@ -525,10 +540,11 @@ sample_sharded_body(const Dev& c, const int blk, const int nblk, const T* __rest
       int besti = 0x7fffffff;
 #pragma unroll
       for (int r = 0; r < WORLD; ++r) {
-        const float2 cnd = __ldcg(reinterpret_cast<const float2*>(area_of(seg, c.area_bytes, WORLD, c.rank, parity, 1) +
-                                                                   ((size_t)r * rows + row) * 8));
-        const int ci = __float_as_int(cnd.y);
-        if (cnd.x > best || (cnd.x == best && ci < besti)) { best = cnd.x; besti = ci; }
+        const uint2 cnd = ll_read_line(c, ll_of(seg, c.area_bytes, c.ll_bytes, WORLD, c.rank, parity, r) +
+                                              ((size_t)rows + row) * 16, epoch);
+        const float cv = __uint_as_float(cnd.x);
+        const int ci = (int)cnd.y;
+        if (cv > best || (cv == best && ci < besti)) { best = cv; besti = ci; }
       }
       out[row] = besti;
     }
@@ -784,9 +800,9 @@ extern "C" int zp_sample_sharded(zp_comm* c, const void* logits, const float* te
   ZP_REQUIRE(logits && temperatures && tokens_out, "zp_sample_sharded: null pointer");
   ZP_REQUIRE(n_rows > 0 && vocab_shard > 0 && (int64_t)vocab_shard * c->world < 0x7fffffff,
              "zp_sample_sharded: bad sizes");
-  ZP_REQUIRE((size_t)c->world * n_rows * 8 <= c->area_bytes,
-             "zp_sample_sharded: %d rows need %zu bytes of message area, the communicator has %zu", n_rows,
-             (size_t)c->world * n_rows * 8, c->area_bytes);
+  ZP_REQUIRE((size_t)std::min(n_rows, SAMPLE_ROWS_PER_BLOCK * std::min(c->sms, MAX_BLOCKS)) * 16 <= c->ll_bytes,
+             "zp_sample_sharded: the communicator's message area (%zu bytes) is too small for %d rows",
+             c->area_bytes, n_rows);
   Dev d;
   for (int r = 0; r < MAX_WORLD; ++r) d.seg[r] = c->seg[r];
   d.state = c->state; d.area_bytes = c->area_bytes; d.ll_bytes = c->ll_bytes; d.timeout_ns = c->timeout_ns;
@@ -885,7 +901,7 @@ extern "C" int zp_sample_sharded_emulated(zp_comm* const* comms, int world, cons
   for (int r = 0; r < world; ++r) {
     const zp_comm* c = comms[r];
     ZP_REQUIRE(c && c->world == world && c->rank == r, "zp_sample_sharded_emulated: communicator %d", r);
-    ZP_REQUIRE((size_t)world * n_rows * 8 <= c->area_bytes, "zp_sample_sharded_emulated: too many rows for the areas");
+    ZP_REQUIRE((size_t)n_rows * 16 <= c->ll_bytes, "zp_sample_sharded_emulated: too many rows for the areas");
     for (int q = 0; q < world; ++q) ZP_REQUIRE(c->seg[q], "zp_sample_sharded_emulated: rank %d lacks segment %d", r, q);
     for (int q = 0; q < MAX_WORLD; ++q) w.dev[r].seg[q] = c->seg[q];
     w.dev[r].state = c->state; w.dev[r].area_bytes = c->area_bytes; w.dev[r].ll_bytes = c->ll_bytes;
