@@ -342,7 +342,7 @@ int zp_comm_destroy(zp_comm* comm);
  * most max_bytes; in == out allowed.  algo: 0 = by size and world, 1 = one-shot (every rank gets
  * all inputs, one meeting), 2 = two-shot (reduce-scatter into every rank's result area, then a
  * local read; two meetings), 3 = flagged lines (one-shot with the epoch stored beside every
- * payload word instead of a meeting; at most 2 MiB; the default up to 512 KiB). */
+ * payload word instead of a meeting; at most 2 MiB; the default up to 512 KiB on up to 4 ranks). */
 int zp_all_reduce(zp_comm* comm, const void* in, void* out, int64_t count, int dtype, int algo,
                   void* stream);
 /* x = all-reduce(in) [rows, hidden]; s = x + residual; residual_out = T(s);

@@ -654,7 +654,12 @@ int run(zp_comm* c, int algo, bool fused, const void* in, void* out, int64_t nve
   // meeting: a decode step's messages are latency-bound); above that one-shot moves (world-1) x
   // the message into every GPU, two-shot 2 x (world-1)/world of it
   int mode;
-  if (algo == 0) mode = (size_t)nvec * 16 <= std::min(c->ll_bytes, LL_AUTO_BYTES) ? 2 : (c->world > 2 ? 1 : 0);
+  if (algo == 0) {
+    // flagged lines by default only up to 4 ranks: with 8, the 64 KiB message measured 23 us
+    // against 16 us for the one-shot form (seven peers' worth of doubled stores and polls)
+    const bool lines = c->world <= 4 && (size_t)nvec * 16 <= std::min(c->ll_bytes, LL_AUTO_BYTES);
+    mode = lines ? 2 : (c->world > 2 && (size_t)nvec * 16 >= (512u << 10) ? 1 : 0);
+  }
   else mode = algo - 1;
   cudaStream_t st = (cudaStream_t)stream;
 #define ZP_COLL_WORLD(W) \
