@@ -52,6 +52,78 @@ def test_wait_for_an_absent_peer_times_out_and_reports():
     assert torch.allclose(y.float(), torch.ones(4, 256, device=dev), atol=1e-2)
 
 
+def _absent_peer_comm(lib, L, C, dev, max_bytes, timeout_ms):
+    """A world-2 communicator on one GPU whose peer is a zeroed buffer that nothing ever writes."""
+    h = C.c_void_p()
+    L.check(lib.zp_comm_create(0, 2, max_bytes, timeout_ms, C.byref(h)), "create")
+    p, n = C.c_void_p(), C.c_size_t()
+    L.check(lib.zp_comm_segment(h, C.byref(p), C.byref(n)), "segment")
+    absent = torch.zeros(n.value, dtype=torch.uint8, device=dev)
+    L.check(lib.zp_comm_attach_peer(h, 1, C.c_void_p(absent.data_ptr())), "attach")
+    return h, absent
+
+
+def _status(lib, L, C, h):
+    code = C.c_int(-1)
+    L.check(lib.zp_comm_status(h, C.byref(code)), "status")
+    return code.value
+
+
+@pytest.mark.parametrize("form", ["flagged_lines", "two_shot", "fused_flagged", "sampler"])
+def test_absent_peer_costs_about_one_time_limit(form):
+    """Host-injected failure (a peer that never launches), 50 ms limit, for the forms with many
+    waits per thread: flagged lines (one wait per 16-byte vector and peer), the two meetings of
+    the two-shot form, and the two exchange phases of the sharded sampler.  The first wait that
+    runs out makes the failure sticky, so the whole call — and five more calls after it, as a
+    replayed decode graph would issue — ends within a small multiple of ONE limit."""
+    import ctypes as C
+    import time
+    from zipage_b200 import _lib as L
+    dev = _gpu()
+    lib = L.load()
+    h, absent = _absent_peer_comm(lib, L, C, dev, 1 << 20, 50)
+    try:
+        rows, hidden = 64, 4096
+        x = torch.ones(rows, hidden, dtype=torch.bfloat16, device=dev)
+        res = torch.ones_like(x)
+        wgt = torch.ones(hidden, dtype=torch.bfloat16, device=dev)
+        logits = torch.randn(48, 3000, device=dev).to(torch.bfloat16)
+        temps = torch.ones(48, device=dev)
+        toks = torch.empty(48, dtype=torch.int64, device=dev)
+
+        def call():
+            if form == "flagged_lines":
+                L.check(lib.zp_all_reduce(h, L.ptr(x), L.ptr(x), x.numel(), L.dtype_code(x), 3, L.stream_ptr()), form)
+            elif form == "two_shot":
+                L.check(lib.zp_all_reduce(h, L.ptr(x), L.ptr(x), x.numel(), L.dtype_code(x), 2, L.stream_ptr()), form)
+            elif form == "fused_flagged":
+                L.check(lib.zp_all_reduce_add_rms_norm(h, L.ptr(x), L.ptr(res), L.ptr(wgt), L.ptr(x), L.ptr(res), rows,
+                                                       hidden, 1e-6, L.dtype_code(x), 3, L.stream_ptr()), form)
+            else:
+                L.check(lib.zp_sample_sharded(h, L.ptr(logits), L.ptr(temps), None, L.ptr(toks), 48, 3000, 7,
+                                              L.dtype_code(logits), L.stream_ptr()), form)
+
+        assert _status(lib, L, C, h) == 0
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        call()
+        torch.cuda.synchronize()
+        first = time.perf_counter() - t0
+        assert _status(lib, L, C, h) == 1          # ZP_COMM_TIMEOUT
+        assert 0.04 < first < 0.5, first            # one limit, not one per wait
+        t0 = time.perf_counter()
+        for _ in range(5):
+            call()
+        torch.cuda.synchronize()
+        later = time.perf_counter() - t0
+        assert later < 0.05, later                  # the failure is sticky: no further waiting
+        assert _status(lib, L, C, h) == 1
+    finally:
+        lib.zp_comm_destroy(h)
+    y = torch.ones(8, device=dev) * 2              # the context keeps working
+    assert float(y.sum()) == 16.0
+
+
 def test_argument_checks():
     import ctypes as C
     from zipage_b200 import _lib as L

@@ -25,7 +25,10 @@
 // call between, by which time the peer's earlier kernel has ended.
 //
 // Every wait is bounded (wall-clock limit given at creation): when it runs out the kernel records
-// ZP_COMM_TIMEOUT in the communicator's status word and finishes without waiting further; the
+// ZP_COMM_TIMEOUT in the communicator's status word and finishes without waiting further.  The
+// failure is sticky: every wait looks at the status word first and from time to time while it
+// polls, so the other waits of that launch and all waits of later launches return at once (a lost
+// peer costs about one time limit in total, not one per wait).  The
 // result of that call is undefined and the communicator must be destroyed and built again, but
 // the context stays usable.  Blocks only ever wait for the block of the same index on the peers,
 // and a launch has at most one block per SM, so on a GPU otherwise free of spinning kernels every
@@ -62,6 +65,13 @@ __device__ __forceinline__ long long now_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
+// The communicator's status word, read past the caches.  Once a wait has run out it stays non-zero
+// until the communicator is destroyed: every later wait, in this launch and in every launch that
+// follows (a replayed decode graph issues dozens), gives up at its first look instead of spending
+// its own time limit, so a lost peer costs about one limit in total.
+__device__ __forceinline__ bool comm_failed(const uint32_t* state) {
+  return *reinterpret_cast<const volatile uint32_t*>(state + 2) != 0u;
+}
 __device__ __forceinline__ int4 ld16_l2(const void* p) {   // L2 only: the line may be a peer's write
   return __ldcg(reinterpret_cast<const int4*>(p));
 }
@@ -97,13 +107,17 @@ __device__ __forceinline__ int4 ll_read(const Dev& c, const char* slot, int64_t 
   const char* p = slot + v * 32;
   uint4 a = ld_volatile16(p), b = ld_volatile16(p + 16);
   if (a.y != epoch || a.w != epoch || b.y != epoch || b.w != epoch) {
+    if (comm_failed(c.state)) return make_int4((int)a.x, (int)a.z, (int)b.x, (int)b.z);
     const long long t0 = now_ns();
     uint32_t spins = 0;
     do {
       a = ld_volatile16(p); b = ld_volatile16(p + 16);
-      if ((++spins & 255u) == 0 && now_ns() - t0 > c.timeout_ns) {
-        atomicCAS(c.state + 2, 0u, (uint32_t)STATUS_TIMEOUT);
-        break;
+      if ((++spins & 255u) == 0) {
+        if (comm_failed(c.state)) break;
+        if (now_ns() - t0 > c.timeout_ns) {
+          atomicCAS(c.state + 2, 0u, (uint32_t)STATUS_TIMEOUT);
+          break;
+        }
       }
     } while (a.y != epoch || a.w != epoch || b.y != epoch || b.w != epoch);
   }
@@ -114,13 +128,17 @@ __device__ __forceinline__ int4 ll_read(const Dev& c, const char* slot, int64_t 
 __device__ __forceinline__ uint2 ll_read_line(const Dev& c, const char* p, uint32_t epoch) {
   uint4 a = ld_volatile16(p);
   if (a.y != epoch || a.w != epoch) {
+    if (comm_failed(c.state)) return make_uint2(a.x, a.z);
     const long long t0 = now_ns();
     uint32_t spins = 0;
     do {
       a = ld_volatile16(p);
-      if ((++spins & 255u) == 0 && now_ns() - t0 > c.timeout_ns) {
-        atomicCAS(c.state + 2, 0u, (uint32_t)STATUS_TIMEOUT);
-        break;
+      if ((++spins & 255u) == 0) {
+        if (comm_failed(c.state)) break;
+        if (now_ns() - t0 > c.timeout_ns) {
+          atomicCAS(c.state + 2, 0u, (uint32_t)STATUS_TIMEOUT);
+          break;
+        }
       }
     } while (a.y != epoch || a.w != epoch);
   }
@@ -146,7 +164,8 @@ __device__ __forceinline__ void meet_peers(const Dev& c, char* const* seg, int p
     const long long t0 = now_ns();
     uint32_t spins = 0;
     while ((int32_t)(ld_relaxed_sys(mine) - epoch) < 0) {
-      if (++spins > 4096u) {
+      if ((++spins & 1023u) == 1u && comm_failed(c.state)) break;   // first look, then every 1024th
+      if (spins > 4096u) {
         __nanosleep(64);
         if ((spins & 63u) == 0 && now_ns() - t0 > c.timeout_ns) {
           atomicCAS(c.state + 2, 0u, (uint32_t)STATUS_TIMEOUT);

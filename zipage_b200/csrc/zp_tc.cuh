@@ -48,15 +48,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when the block is aborting (this wait ran out, or another role's did).
-// BACKOFF: sleep between polls — for the single-thread producer / MMA roles, whose polling would
-// otherwise take issue slots from the epilogue warps that share their scheduler.
-template <bool BACKOFF = false>
+// SLEEP_NS > 0: sleep that long between polls, so that a waiting warp leaves the issue slots of
+// its scheduler to the warps that have work (a poll is several instructions).  `true` = 64 ns.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* error_word, int where) {
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (BACKOFF) __nanosleep(64);
+    if (SLEEP_NS > 0) __nanosleep(SLEEP_NS == 1 ? 64 : SLEEP_NS);
   }
   *abort_flag = 1;
   atomicCAS(error_word, 0, where);
@@ -75,6 +75,13 @@ __device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
       "r"(c2), "r"(c3), "r"(c4)
       : "memory");
+}
+
+// Hint: bring a tile into L2 ahead of the load that will ask for it (no shared memory, no barrier).
+__device__ __forceinline__ void tma_prefetch_l2_5d(const CUtensorMap* m, int c0, int c1, int c2, int c3, int c4) {
+  asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global.tile [%0, {%1, %2, %3, %4, %5}];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+               : "memory");
 }
 
 // ---- tcgen05 ------------------------------------------------------------------------------------

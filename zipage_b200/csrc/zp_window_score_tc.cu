@@ -1,24 +1,28 @@
 // Window-masked attention scoring on tcgen05 tensor cores (16-bit caches, head_dim 128, page
-// size 256, G*QCL <= 128 window rows, G a power of two).
+// size 256, G*QCL <= 128 window rows per pass, G a power of two).
 //
 // Persistent blocks (one per SM) walk over the units (layer, sequence, kv head) with a fixed
 // stride, so the TMA/MMA pipeline never drains between units.  A unit's window queries (row
-// r = i*G + g) are loaded once by TMA (double-buffered across units); its key pages stream through
-// a ring of 64 KB swizzled tiles.
+// r = i*G + g) are loaded once by TMA; its key pages stream through a ring of three 64 KB
+// swizzled tiles.
 // Three sweeps over the pages recompute the logits on the tensor cores instead of storing them:
 //   sweep 0: D[row][key]  = Q K^T (M = 128 rows, N = 256 keys)   -> row maximum
 //   sweep 1: same product                                         -> row sum of exp
 //   sweep 2: D[key][row]  = K Q^T (2 x (M = 128 keys, N = 128 rows)) -> probabilities; each thread
 //            owns one key and sees all window rows, so the max over the query heads of the group
 //            and the mean/max over the window are register-local.
-// Rounding points are the reference's: logits, shifted logits and probabilities are rounded to T
-// (attention_score.py:129-130 and the torch ops at :220-243) — done two at a time with packed
-// 16-bit instructions; exp uses ex2.approx.
+// Rounding points are the reference's: logits and shifted logits are rounded to T
+// (attention_score.py:129-130 and the torch ops at :220-243) two at a time with packed 16-bit
+// instructions; exp uses ex2.approx.  In sweep 2 the probability of a (key, window row) pair is
+// needed only for the query head of the group that maximises it; rounding to T and exp are both
+// monotonic, so max_g T(exp(x_g) / Z_g) = T(exp(max_g (x_g - ln Z_g))): one exp and one rounding
+// per group instead of one per query head.
 // Roles (576 threads): warp 0 = TMA producer + TMEM owner, warp 1 = MMA issuer, warps 2-17 =
-// epilogue.  The four epilogue warps of a TMEM lane quadrant split the 256 columns of a tile in
-// four groups of 64 (sweeps 0/1: key slots; sweep 2: group g owns keys (g/2)*128.. and window-row
-// columns (g%2)*64.., the two partial sums of a key meet in shared memory).  Four warps per
-// scheduler hide the latency of the TMEM loads and of the dependent maths.
+// epilogue.  Sweeps 0/1: the four epilogue warps of a TMEM lane quadrant split the 256 key
+// columns of a tile in four groups of 64.  Sweep 2: the epilogue warps form two teams of eight,
+// team b takes the tiles that land in accumulator buffer b; inside a team a warp owns 32 keys
+// and all window rows, so no partial sums cross warps and a key's score is written straight
+// from registers.
 #include "zp_tc.cuh"
 
 namespace zp {
@@ -29,7 +33,7 @@ constexpr int WT_THREADS = 576;
 constexpr int WT_PAGE_BYTES = 65536;
 constexpr int WT_BLOCK_BYTES = 32768;
 constexpr int WT_QBLOCK_BYTES = 16384;  // 128 rows x 128 bytes
-constexpr int WT_NS = 2;
+constexpr int WT_NS = 3;
 
 struct WtParams {
   const int32_t* seq_idx;
@@ -45,17 +49,19 @@ struct WtParams {
   // ([pass][unit][NB*256] fp32) and a small kernel adds the passes and rounds.
   int i0, qcl_pass, pass;
   float* partial;
+  int smem_bytes;
 };
 
 struct __align__(16) WtShared {
-  uint64_t full[WT_NS], empty[WT_NS], tfull[2], tempty[2], qfull[2], qempty[2], stats_bar;
+  uint64_t full[WT_NS], empty[WT_NS], tfull[2], tempty[2], qfull, qempty, stats_bar;
   alignas(16) uint32_t colm[64];   // sweep 2, per pair of window rows: packed row maxima (T)
-  alignas(16) float colrz[128];    // sweep 2, per window row: 1 / row sum of exp
+  alignas(16) float collz[128];    // sweep 2, per window row: ln(row sum of exp)
   float part[4][128];              // per column-group partial row maximum / row sum
-  float acc[2][256];               // sweep 2: per key, sum (or max) over window rows; by tile parity
   uint32_t tmem_base;
   int abort_flag;
 };
+constexpr size_t WT_SMEM_BYTES = WT_NS * WT_PAGE_BYTES + 2 * WT_QBLOCK_BYTES + sizeof(WtShared);
+static_assert(WT_SMEM_BYTES <= 232448, "window-score kernel: shared memory budget");
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -63,40 +69,127 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-// Reduce 32 columns held as 16 packed pairs: max over each group of G adjacent columns, then
-// sum (or max) over the groups.  Columns >= ncols are ignored.
-// FULL: all 32 columns are window rows (no per-column test).
-template <typename T, int G, bool FULL>
-__device__ __forceinline__ float group_reduce(const typename Pair<T>::V (&pp)[16], int ncols, bool use_max,
-                                              float acc) {
+// a - c in fp32 with a a 16-bit value: one instruction, no separate widening of a (sm_100)
+template <typename T> struct MixedSub;
+template <> struct MixedSub<__nv_bfloat16> {
+  static __device__ __forceinline__ float sub(__nv_bfloat16 a, float c) {
+    float d;
+    asm("sub.rn.f32.bf16 %0, %1, %2;" : "=f"(d) : "h"(__bfloat16_as_ushort(a)), "f"(c));
+    return d;
+  }
+};
+template <> struct MixedSub<__half> {
+  static __device__ __forceinline__ float sub(__half a, float c) {
+    float d;
+    asm("sub.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(__half_as_ushort(a)), "f"(c));
+    return d;
+  }
+};
+
+// two 32-column TMEM loads in flight, one wait: uses of `b` are ordered after the wait by the
+// empty statement that names its registers
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&a)[32], uint32_t (&b)[32]) {
+  tmem_ld32_issue(taddr, a);
+  tmem_ld32_issue(taddr + 32, b);
+  tmem_ld32_wait(a);
+  asm volatile(""
+      : "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]),
+        "+r"(b[8]), "+r"(b[9]), "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]), "+r"(b[14]), "+r"(b[15]),
+        "+r"(b[16]), "+r"(b[17]), "+r"(b[18]), "+r"(b[19]), "+r"(b[20]), "+r"(b[21]), "+r"(b[22]), "+r"(b[23]),
+        "+r"(b[24]), "+r"(b[25]), "+r"(b[26]), "+r"(b[27]), "+r"(b[28]), "+r"(b[29]), "+r"(b[30]), "+r"(b[31])
+      :
+      : "memory");
+}
+
+// Sweep 0 on 32 raw logits: running maximum (four independent chains).
+__device__ __forceinline__ float s0_chunk(const uint32_t (&raw)[32], float m) {
+  float m0 = m, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    m0 = fmaxf(m0, __uint_as_float(raw[j]));
+    m1 = fmaxf(m1, __uint_as_float(raw[j + 1]));
+    m2 = fmaxf(m2, __uint_as_float(raw[j + 2]));
+    m3 = fmaxf(m3, __uint_as_float(raw[j + 3]));
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+// Sweep 1 on 32 raw logits: sum of exp(T(T(raw * scale) - m)).
+template <typename T>
+__device__ __forceinline__ float2 s1_chunk(const uint32_t (&raw)[32], typename Pair<T>::V m2, float2 scale2,
+                                           float2 z) {
   using V = typename Pair<T>::V;
-  constexpr int PG = G >= 2 ? G / 2 : 1;  // packed pairs per group
+  const float2 log2e2 = make_float2(1.4426950408889634f, 1.4426950408889634f);
+  float2 z1 = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float2 xa = __fmul2_rn(make_float2(__uint_as_float(raw[j]), __uint_as_float(raw[j + 1])), scale2);
+    const float2 xb = __fmul2_rn(make_float2(__uint_as_float(raw[j + 2]), __uint_as_float(raw[j + 3])), scale2);
+    const V la = Pair<T>::pack(xa.x, xa.y), lb = Pair<T>::pack(xb.x, xb.y);
+    const float2 da = __fmul2_rn(Pair<T>::unpack(__hsub2(la, m2)), log2e2);
+    const float2 db = __fmul2_rn(Pair<T>::unpack(__hsub2(lb, m2)), log2e2);
+    z = __fadd2_rn(z, make_float2(ex2_approx(da.x), ex2_approx(da.y)));
+    z1 = __fadd2_rn(z1, make_float2(ex2_approx(db.x), ex2_approx(db.y)));
+  }
+  return __fadd2_rn(z, z1);
+}
+
+// Sweep 2 on 32 columns (window rows col0 .. col0+31 of this thread's key): per group of G
+// columns max_g (x_g - ln Z_g), one exp, rounded to T, then summed (or maximised) over the groups.
+// Groups starting at a column >= nvalid_cols are not window rows; groups starting below `jmask`
+// cannot see this key (last page) and count as probability 0.
+template <typename T, int G>
+__device__ __forceinline__ float s2_chunk(const uint32_t (&raw)[32], const uint32_t* colm_pairs,
+                                          const float* collz, int nvalid_cols, int jmask_rel, float2 scale2,
+                                          bool use_max, float acc) {
+  using V = typename Pair<T>::V;
+  float b[32];
+  const uint4* cm4 = reinterpret_cast<const uint4*>(colm_pairs);
+  const float4* lz4 = reinterpret_cast<const float4*>(collz);
+#pragma unroll
+  for (int j4 = 0; j4 < 4; ++j4) {   // 8 columns per step
+    const uint4 cm = cm4[j4];
+    const uint32_t cmv[4] = {cm.x, cm.y, cm.z, cm.w};
+    const float4 lza = lz4[2 * j4], lzb = lz4[2 * j4 + 1];
+    const float lzv[8] = {lza.x, lza.y, lza.z, lza.w, lzb.x, lzb.y, lzb.z, lzb.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int j = 8 * j4 + 2 * k;
+      const float2 x = __fmul2_rn(make_float2(__uint_as_float(raw[j]), __uint_as_float(raw[j + 1])), scale2);
+      const V xs = __hsub2(Pair<T>::pack(x.x, x.y), *reinterpret_cast<const V*>(&cmv[k]));
+      b[j] = MixedSub<T>::sub(xs.x, lzv[2 * k]);
+      b[j + 1] = MixedSub<T>::sub(xs.y, lzv[2 * k + 1]);
+    }
+  }
   constexpr int NG = 32 / G;
-  float part[NG];
-  if constexpr (G == 1) {
+  float e[NG];
 #pragma unroll
-    for (int jp = 0; jp < 16; ++jp) {
-      const float2 f = Pair<T>::unpack(pp[jp]);
-      part[2 * jp] = f.x; part[2 * jp + 1] = f.y;
+  for (int g = 0; g < NG; ++g) {
+    float m;
+    if constexpr (G == 1) m = b[g];
+    else if constexpr (G == 2) m = fmaxf(b[2 * g], b[2 * g + 1]);
+    else {
+      m = fmaxf(fmaxf(b[g * G], b[g * G + 1]), fmaxf(b[g * G + 2], b[g * G + 3]));
+#pragma unroll
+      for (int k = 4; k < G; k += 4)
+        m = fmaxf(fmaxf(m, b[g * G + k]), fmaxf(fmaxf(b[g * G + k + 1], b[g * G + k + 2]), b[g * G + k + 3]));
     }
+    e[g] = ex2_approx(m * 1.4426950408889634f);
+    if (g * G >= nvalid_cols || g * G < jmask_rel) e[g] = 0.f;
+  }
+  if constexpr (NG == 1) {
+    const float f = Elem<T>::to_f32(Elem<T>::from_f32(e[0]));
+    return use_max ? fmaxf(acc, f) : acc + f;
   } else {
+    float2 a2 = make_float2(acc, use_max ? acc : 0.f);
 #pragma unroll
-    for (int jp = 0; jp < 16; jp += PG) {
-      V m = pp[jp];
-#pragma unroll
-      for (int k = 1; k < PG; ++k) m = __hmax2(m, pp[jp + k]);
-      const float2 f = Pair<T>::unpack(m);
-      part[jp / PG] = fmaxf(f.x, f.y);
+    for (int g = 0; g < NG; g += 2) {
+      const float2 f = Pair<T>::unpack(Pair<T>::pack(e[g], e[g + 1]));
+      if (use_max) { a2.x = fmaxf(a2.x, f.x); a2.y = fmaxf(a2.y, f.y); }
+      else a2 = __fadd2_rn(a2, f);
     }
+    return use_max ? fmaxf(a2.x, a2.y) : a2.x + a2.y;
   }
-  if (use_max) {
-#pragma unroll
-    for (int g = 0; g < NG; ++g) if (FULL || g * G < ncols) acc = fmaxf(acc, part[g]);
-  } else {
-#pragma unroll
-    for (int g = 0; g < NG; ++g) if (FULL || g * G < ncols) acc += part[g];
-  }
-  return acc;
 }
 
 template <typename T, int G>
@@ -104,25 +197,27 @@ __global__ void __launch_bounds__(WT_THREADS, 1)
 window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmQ,
                        const WtParams p) {
   using V = typename Pair<T>::V;
-  extern __shared__ unsigned char smem_raw[];
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* bufs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* qbufs = bufs + WT_NS * WT_PAGE_BYTES;   // two query buffers of 2 x 16 KB
-  WtShared& sh = *reinterpret_cast<WtShared*>(qbufs + 4 * WT_QBLOCK_BYTES);
+  unsigned char* qbuf = bufs + WT_NS * WT_PAGE_BYTES;    // the unit's queries: 2 x 16 KB
+  WtShared& sh = *reinterpret_cast<WtShared*>(qbuf + 2 * WT_QBLOCK_BYTES);
+  if (reinterpret_cast<unsigned char*>(&sh + 1) > smem_raw + p.smem_bytes) {
+    // the tiles need 1024-byte alignment and the budget has no room for a misaligned base
+    if (threadIdx.x == 0) atomicCAS(p.error_word, 0, 100);
+    return;
+  }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int R = G * p.qcl_pass;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < WT_NS; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 16);
-      mbar_init(&sh.qfull[i], 1); mbar_init(&sh.qempty[i], 1);
-    }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sh.tfull[i], 1); mbar_init(&sh.tempty[i], 16); }
+    mbar_init(&sh.qfull, 1); mbar_init(&sh.qempty, 1);
     mbar_init(&sh.stats_bar, 16);  // one arrival per epilogue warp
     sh.abort_flag = 0;
     fence_mbar_init();
   }
-  if (threadIdx.x < 512) (&sh.acc[0][0])[threadIdx.x] = 0.f;
   if (warp == 0) {
     tmem_alloc(&sh.tmem_base, 512);
     tmem_relinquish();
@@ -134,42 +229,16 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   volatile int* abortp = &sh.abort_flag;
 
   // Tile order within a unit: sweeps 0 and 2 walk the table forwards, sweep 1 backwards (the pages
-  // it starts with are the ones sweep 0 touched last, still in L2).  Each role keeps a cursor, so
-  // finding the next valid table position costs one (cached) load instead of a scan of the table.
-  struct TileCursor {
-    // The table entry of the tile after the current one is loaded one call ahead, so its latency
-    // is hidden behind the current tile's work.
-    const int32_t* table; int NB, nvalid, pg, nxt_pg, nxt_entry;
-    __device__ __forceinline__ void probe(int from, int step) {   // next valid position from `from`
-      int q = from;
-      int e = table[q];
-      while (e == -1) { q += step; e = table[q]; }
-      nxt_pg = q; nxt_entry = e;
-    }
-    __device__ __forceinline__ void start() { probe(0, 1); }
-    // returns the table position of tile tt and its (encoded) entry
-    __device__ __forceinline__ int next(int tt, int ntiles, int& entry) {
-      pg = nxt_pg; entry = nxt_entry;
-      const int t2 = tt + 1;
-      if (t2 < ntiles) {
-        const int sweep = t2 / nvalid;
-        if (t2 % nvalid == 0) { if (sweep == 1) probe(NB - 1, -1); else probe(0, 1); }
-        else if (sweep == 1) probe(pg - 1, -1);
-        else probe(pg + 1, 1);
-      }
-      return pg;
-    }
-  };
-  // Every role walks the same sequence of units and tiles; `gt` counts tiles since kernel start
-  // (it selects the shared-memory stage and the TMEM buffer), `n` counts this block's units.
+  // it starts with are the ones sweep 0 touched last, still in L2).  Every role walks the same
+  // sequence of units, sweeps and tiles with counters only (no division in a per-tile path);
+  // `gt` counts tiles since kernel start (it selects the TMEM buffer), `n` counts the block's units.
   struct Unit {
-    int h, b, l, nvalid, ntiles; const int32_t* table;
+    int h, b, l, nvalid; const int32_t* table;
     __device__ __forceinline__ Unit(const WtParams& p, int unit) {
       h = unit % p.Hkv; b = (unit / p.Hkv) % p.B; l = unit / (p.Hkv * p.B);
       table = p.block_table + (int64_t)b * p.NB;
       nvalid = 0;
       for (int pg = 0; pg < p.NB; ++pg) nvalid += table[pg] != -1;
-      ntiles = 3 * nvalid;
     }
   };
 
@@ -177,29 +246,34 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     if (lane == 0) {
       prefetch_tensormap(&tmK);
       prefetch_tensormap(&tmQ);
-      int gt = 0, n = 0;  // n counts the units that have tiles (query buffer n & 1)
+      int s = 0, sph = 0, n = 0;  // ring stage and its phase; n counts the units that have tiles
       bool ok = true;
       for (int unit = blockIdx.x; ok && unit < p.total_units; unit += gridDim.x) {
         const Unit un(p, unit);
-        if (un.ntiles == 0) continue;
-        const int qb = n & 1;
-        if (!mbar_wait<true>(&sh.qempty[qb], ((n >> 1) & 1) ^ 1, abortp, p.error_word, 110)) break;
-        mbar_arrive_expect_tx(&sh.qfull[qb], (uint32_t)(2 * R * 128));
-        const int qid = p.seq_idx[un.b];
-        unsigned char* qbuf = qbufs + qb * 2 * WT_QBLOCK_BYTES;
-        tma_load_5d(qbuf, &tmQ, &sh.qfull[qb], 0, un.h * G, p.i0, qid, un.l);
-        tma_load_5d(qbuf + WT_QBLOCK_BYTES, &tmQ, &sh.qfull[qb], 64, un.h * G, p.i0, qid, un.l);
-        TileCursor cur{un.table, p.NB, un.nvalid, 0, 0, 0};
-        cur.start();
-        for (int tt = 0; tt < un.ntiles; ++tt, ++gt) {
-          int entry;
-          cur.next(tt, un.ntiles, entry);
-          const int s = gt % WT_NS, k = gt / WT_NS;
-          if (!mbar_wait<true>(&sh.empty[s], (k & 1) ^ 1, abortp, p.error_word, 111)) { ok = false; break; }
-          const int id = decode_page(entry).id;
-          mbar_arrive_expect_tx(&sh.full[s], WT_PAGE_BYTES);
-          tma_load_5d(bufs + s * WT_PAGE_BYTES, &tmK, &sh.full[s], 0, un.h, 0, id, un.l);
-          tma_load_5d(bufs + s * WT_PAGE_BYTES + WT_BLOCK_BYTES, &tmK, &sh.full[s], 64, un.h, 0, id, un.l);
+        if (un.nvalid == 0) continue;
+        for (int sweep = 0; ok && sweep < 3; ++sweep) {
+          const int dir = sweep == 1 ? -1 : 1;
+          int pos = sweep == 1 ? p.NB - 1 : 0;
+          for (int j = 0; j < un.nvalid; ++j) {
+            int entry = un.table[pos];
+            while (entry == -1) { pos += dir; entry = un.table[pos]; }
+            pos += dir;
+            if (!mbar_wait<64>(&sh.empty[s], sph ^ 1, abortp, p.error_word, 111)) { ok = false; break; }
+            const int id = decode_page(entry).id;
+            mbar_arrive_expect_tx(&sh.full[s], WT_PAGE_BYTES);
+            tma_load_5d(bufs + s * WT_PAGE_BYTES, &tmK, &sh.full[s], 0, un.h, 0, id, un.l);
+            tma_load_5d(bufs + s * WT_PAGE_BYTES + WT_BLOCK_BYTES, &tmK, &sh.full[s], 64, un.h, 0, id, un.l);
+            if (++s == WT_NS) { s = 0; sph ^= 1; }
+            if (sweep == 0 && j == 0) {
+              // The single query buffer is free once the previous unit's last product has been
+              // read; the first key page of this unit is already on its way.
+              if (!mbar_wait<64>(&sh.qempty, (n & 1) ^ 1, abortp, p.error_word, 110)) { ok = false; break; }
+              mbar_arrive_expect_tx(&sh.qfull, (uint32_t)(2 * R * 128));
+              const int qid = p.seq_idx[un.b];
+              tma_load_5d(qbuf, &tmQ, &sh.qfull, 0, un.h * G, p.i0, qid, un.l);
+              tma_load_5d(qbuf + WT_QBLOCK_BYTES, &tmQ, &sh.qfull, 64, un.h * G, p.i0, qid, un.l);
+            }
+          }
         }
         ++n;
       }
@@ -208,42 +282,42 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     if (lane == 0) {
       constexpr uint32_t IDESC_QK = idesc_f16(UmmaFmt<T>::fmt, 128, 256);
       constexpr uint32_t IDESC_KQ = idesc_f16(UmmaFmt<T>::fmt, 128, 128);
-      int gt = 0, n = 0;
+      int gt = 0, n = 0, s = 0, sph = 0;
       bool ok = true;
+      const uint32_t q_addr = smem_u32(qbuf);
       for (int unit = blockIdx.x; ok && unit < p.total_units; unit += gridDim.x) {
         const Unit un(p, unit);
-        if (un.ntiles == 0) continue;
-        const int qb = n & 1;
-        if (!mbar_wait<true>(&sh.qfull[qb], (n >> 1) & 1, abortp, p.error_word, 211)) break;
-        const uint32_t q_addr = smem_u32(qbufs + qb * 2 * WT_QBLOCK_BYTES);
-        for (int tt = 0; tt < un.ntiles; ++tt, ++gt) {
-          const int sweep = tt / un.nvalid;
-          const int s = gt % WT_NS, k = gt / WT_NS, buf = gt & 1, u = gt >> 1;
-          if (!mbar_wait<true>(&sh.full[s], k & 1, abortp, p.error_word, 212)) { ok = false; break; }
-          if (!mbar_wait<true>(&sh.tempty[buf], (u & 1) ^ 1, abortp, p.error_word, 213)) { ok = false; break; }
-          fence_after_sync();
-          const uint32_t k_addr = smem_u32(bufs + s * WT_PAGE_BYTES);
-          const uint32_t d = tmem_base + buf * 256;
-          if (sweep < 2) {
-            umma_k128(d, q_addr, WT_QBLOCK_BYTES, k_addr, WT_BLOCK_BYTES, IDESC_QK);
-          } else {
-            umma_k128(d, k_addr, WT_BLOCK_BYTES, q_addr, WT_QBLOCK_BYTES, IDESC_KQ);
-            umma_k128(d + 128, k_addr + 16384, WT_BLOCK_BYTES, q_addr, WT_QBLOCK_BYTES, IDESC_KQ);
+        if (un.nvalid == 0) continue;
+        if (!mbar_wait<64>(&sh.qfull, n & 1, abortp, p.error_word, 211)) break;
+        for (int sweep = 0; ok && sweep < 3; ++sweep) {
+          for (int j = 0; j < un.nvalid; ++j, ++gt) {
+            const int buf = gt & 1, u = gt >> 1;
+            if (!mbar_wait<64>(&sh.full[s], sph, abortp, p.error_word, 212)) { ok = false; break; }
+            if (!mbar_wait<64>(&sh.tempty[buf], (u & 1) ^ 1, abortp, p.error_word, 213)) { ok = false; break; }
+            fence_after_sync();
+            const uint32_t k_addr = smem_u32(bufs + s * WT_PAGE_BYTES);
+            const uint32_t d = tmem_base + buf * 256;
+            if (sweep < 2) {
+              umma_k128(d, q_addr, WT_QBLOCK_BYTES, k_addr, WT_BLOCK_BYTES, IDESC_QK);
+            } else {
+              umma_k128(d, k_addr, WT_BLOCK_BYTES, q_addr, WT_QBLOCK_BYTES, IDESC_KQ);
+              umma_k128(d + 128, k_addr + 16384, WT_BLOCK_BYTES, q_addr, WT_QBLOCK_BYTES, IDESC_KQ);
+            }
+            umma_commit(&sh.tfull[buf]);
+            umma_commit(&sh.empty[s]);
+            if (++s == WT_NS) { s = 0; sph ^= 1; }
           }
-          umma_commit(&sh.tfull[buf]);
-          umma_commit(&sh.empty[s]);
         }
-        if (ok) umma_commit(&sh.qempty[qb]);  // the unit's queries are no longer read
+        if (ok) umma_commit(&sh.qempty);  // the unit's queries are no longer read
         ++n;
       }
     }
   } else {
     // ---------------- epilogue ----------------
     const int q = warp & 3;               // TMEM lane quadrant
-    const int grp = (warp - 2) >> 2;      // column group 0..3 (64 columns each)
+    const int grp = (warp - 2) >> 2;      // sweeps 0/1: column group 0..3 (64 key columns each)
     const int r = q * 32 + lane;          // TMEM lane: window row (sweeps 0/1) or key (sweep 2)
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + grp * 64;
-    const float2 log2e2 = make_float2(1.4426950408889634f, 1.4426950408889634f);
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     const float2 scale2 = make_float2(p.scale, p.scale);
     const int my_i = r / G;
     const bool use_max = p.reduce_mode != 0;
@@ -251,166 +325,132 @@ window_score_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     auto sync_epilogue = [&](int where) -> bool {
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh.stats_bar);
-      const bool ok_ = mbar_wait(&sh.stats_bar, ph & 1, abortp, p.error_word, where);
+      const bool ok_ = mbar_wait<0>(&sh.stats_bar, ph & 1, abortp, p.error_word, where);
       ++ph;
       return ok_;
     };
-    // sweep 2: this thread's key and the window-row columns it covers
-    const int hh = grp >> 1, cbase = (grp & 1) * 64;
+    auto release_tmem = [&](int buf) {    // this warp has read what it needs of the accumulator
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.tempty[buf]);
+    };
+    // sweep 2: team = accumulator buffer, hh = key half of the page, slot = this thread's key
+    const int team = grp >> 1, hh = grp & 1;
     const int slot = hh * 128 + r;
 
     int gt = 0;
     bool ok = true;
     for (int unit = blockIdx.x; ok && unit < p.total_units; unit += gridDim.x) {
-    const Unit un(p, unit);
-    const int32_t* table = un.table;
-    const int nvalid = un.nvalid, ntiles = un.ntiles;
-    float row_max = -INFINITY, row_z = 0.f;
-    V m2 = Pair<T>::pack(0.f, 0.f);       // this row's maximum, twice
-    T* out = reinterpret_cast<T*>(p.scores_out) + (int64_t)unit * p.NB * 256;
-    if (grp < 2)
-      for (int pg = 0; pg < p.NB; ++pg)   // padded pages score exactly 0
-        if (table[pg] == -1) {
-          if (p.partial) p.partial[((int64_t)p.pass * p.total_units + unit) * p.NB * 256 + pg * 256 + grp * 128 + r] = 0.f;
-          else out[pg * 256 + grp * 128 + r] = Elem<T>::from_f32(0.f);
+      const int b = (unit / p.Hkv) % p.B;
+      const int32_t* table = p.block_table + (int64_t)b * p.NB;
+      float row_max = -INFINITY;
+      float2 row_z = make_float2(0.f, 0.f);
+      V m2 = Pair<T>::pack(0.f, 0.f);       // this row's maximum, twice
+      T* out = reinterpret_cast<T*>(p.scores_out) + (int64_t)unit * p.NB * 256;
+      float* pout = p.partial ? p.partial + ((int64_t)p.pass * p.total_units + unit) * p.NB * 256 : nullptr;
+      bool any = false;
+      for (int sweep = 0; ok && sweep < 3; ++sweep) {
+        if (sweep == 1 && any) {  // row maximum: combine the four column groups
+          sh.part[grp][r] = row_max;
+          if (!sync_epilogue(311)) { ok = false; break; }
+          const float m = fmaxf(fmaxf(sh.part[0][r], sh.part[1][r]), fmaxf(sh.part[2][r], sh.part[3][r])) * p.scale;
+          m2 = Pair<T>::pack(m, m);
+          if (!sync_epilogue(312)) { ok = false; break; }  // everyone has read `part` before it is reused
         }
-    TileCursor cur{table, p.NB, nvalid, 0, 0, 0};
-    if (ntiles > 0) cur.start();
-    for (int tt = 0; tt < ntiles; ++tt, ++gt) {
-      int entry;
-      const int pg = cur.next(tt, ntiles, entry);
-      const int sweep = tt / nvalid;
-      const bool last = entry < -1;
-      const int buf = gt & 1, u = gt >> 1;
-      if (tt == nvalid) {  // row maximum: combine the four column groups
-        sh.part[grp][r] = row_max;
-        if (!sync_epilogue(311)) { ok = false; break; }
-        const float m = fmaxf(fmaxf(sh.part[0][r], sh.part[1][r]), fmaxf(sh.part[2][r], sh.part[3][r])) * p.scale;
-        m2 = Pair<T>::pack(m, m);
-        if (!sync_epilogue(312)) { ok = false; break; }  // everyone has read `part` before it is reused
-      }
-      if (tt == 2 * nvalid) {  // row sum: combine, publish per-column statistics for sweep 2
-        sh.part[grp][r] = row_z;
-        if (!sync_epilogue(313)) { ok = false; break; }
-        if (grp == 0) {
-          const float z = (sh.part[0][r] + sh.part[1][r]) + (sh.part[2][r] + sh.part[3][r]);
-          reinterpret_cast<T*>(sh.colm)[r] = reinterpret_cast<const T*>(&m2)[0];
-          sh.colrz[r] = 1.f / z;
+        if (sweep == 2 && any) {  // row sum: combine, publish per-column statistics for sweep 2
+          sh.part[grp][r] = row_z.x + row_z.y;
+          if (!sync_epilogue(313)) { ok = false; break; }
+          if (grp == 0) {
+            const float z = (sh.part[0][r] + sh.part[1][r]) + (sh.part[2][r] + sh.part[3][r]);
+            reinterpret_cast<T*>(sh.colm)[r] = reinterpret_cast<const T*>(&m2)[0];
+            sh.collz[r] = logf(z);
+          }
+          if (!sync_epilogue(314)) { ok = false; break; }
         }
-        if (!sync_epilogue(314)) { ok = false; break; }
-      }
-      if (!mbar_wait(&sh.tfull[buf], u & 1, abortp, p.error_word, 315)) { ok = false; break; }
-      fence_after_sync();
+        // The table is read 32 entries at a time (one per lane); ballots give the positions of
+        // the real pages and of the page that holds the window.
+        const int nwords = (p.NB + 31) >> 5;
+        for (int wi = 0; ok && wi < nwords; ++wi) {
+          const int w = sweep == 1 ? nwords - 1 - wi : wi;
+          const int idx = w * 32 + lane;
+          const int e = idx < p.NB ? table[idx] : -1;
+          uint32_t vmask = __ballot_sync(0xffffffffu, e != -1);
+          const uint32_t lmask = __ballot_sync(0xffffffffu, e < -1);
+          if (sweep == 0 && grp < 2 && q == 0 && idx < p.NB && e == -1) {   // padded pages score exactly 0
+            for (int k = 0; k < 128; ++k) {
+              if (pout) pout[idx * 256 + grp * 128 + k] = 0.f;
+              else out[idx * 256 + grp * 128 + k] = Elem<T>::from_f32(0.f);
+            }
+          }
+          while (vmask) {
+            const int bit = sweep == 1 ? 31 - __clz(vmask) : __ffs(vmask) - 1;
+            vmask &= ~(1u << bit);
+            const int pg = w * 32 + bit;
+            const bool last = (lmask >> bit) & 1u;
+            const int buf = gt & 1, u = gt >> 1;
+            ++gt;
+            any = true;
+            if (!mbar_wait<32>(&sh.tfull[buf], u & 1, abortp, p.error_word, 315)) { ok = false; break; }
+            fence_after_sync();
 
-      if (sweep < 2) {
-        // columns = key slots grp*64 ..; row r sees slot <= smax inside the last page
-        const uint32_t tbase = lane_base + buf * 256;
-        const int smax = last ? 256 - p.QCL + p.i0 + my_i : 256;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t raw[32];
-          tmem_ld32_issue(tbase + c * 32, raw);
-          tmem_ld32_wait(raw);
-          if (c == 1) {  // all TMEM reads of this tile have landed in registers
-            fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh.tempty[buf]);
-          }
-          const int s0 = grp * 64 + c * 32;
-          if (s0 + 31 > smax) {  // masked key slots (last page only)
+            if (sweep < 2) {
+              // columns = key slots grp*64 ..; row r sees slot <= smax inside the last page
+              uint32_t ra[32], rb[32];
+              tmem_ld64(lane_addr + buf * 256 + grp * 64, ra, rb);
+              release_tmem(buf);
+              const int smax = last ? 256 - p.QCL + p.i0 + my_i : 256;
+              const int s0 = grp * 64;
+              if (s0 + 63 > smax) {  // masked key slots (last page only)
 #pragma unroll
-            for (int j = 0; j < 32; ++j) if (s0 + j > smax) raw[j] = 0xff800000u;  // -inf
-          }
-          if (sweep == 0) {
-            float m0 = -INFINITY, m1 = -INFINITY, m2_ = -INFINITY, m3 = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              m0 = fmaxf(m0, __uint_as_float(raw[j])); m1 = fmaxf(m1, __uint_as_float(raw[j + 1]));
-              m2_ = fmaxf(m2_, __uint_as_float(raw[j + 2])); m3 = fmaxf(m3, __uint_as_float(raw[j + 3]));
-            }
-            row_max = fmaxf(row_max, fmaxf(fmaxf(m0, m1), fmaxf(m2_, m3)));
-          } else {
-            float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const float2 xa = fmul2(make_float2(__uint_as_float(raw[j]), __uint_as_float(raw[j + 1])), scale2);
-              const float2 xb = fmul2(make_float2(__uint_as_float(raw[j + 2]), __uint_as_float(raw[j + 3])), scale2);
-              const V la = Pair<T>::pack(xa.x, xa.y), lb = Pair<T>::pack(xb.x, xb.y);
-              const float2 da = fmul2(Pair<T>::unpack(__hsub2(la, m2)), log2e2);
-              const float2 db = fmul2(Pair<T>::unpack(__hsub2(lb, m2)), log2e2);
-              z0 += ex2_approx(da.x); z1 += ex2_approx(da.y);
-              z2 += ex2_approx(db.x); z3 += ex2_approx(db.y);
-            }
-            row_z += (z0 + z1) + (z2 + z3);
-          }
-        }
-      } else {
-        // rows of D = keys; columns = window rows j = i*G + g; key `slot` is hidden from columns < jmask
-        const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * 256 + hh * 128 + cbase;
-        const int jmask = last ? max(0, slot - (256 - p.QCL) - p.i0) * G : 0;
-        float acc2 = use_max ? -INFINITY : 0.f;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          const int col0 = cbase + c * 32;
-          if (col0 >= R) {  // no window rows in this chunk (R < 128)
-            if (c == 1) { fence_before_sync(); __syncwarp(); if (lane == 0) mbar_arrive(&sh.tempty[buf]); }
-            continue;
-          }
-          uint32_t raw[32];
-          tmem_ld32_issue(tbase + c * 32, raw);
-          tmem_ld32_wait(raw);
-          if (c == 1) {
-            fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh.tempty[buf]);
-          }
-          V pp[16];
-          const uint4* cm4 = reinterpret_cast<const uint4*>(&sh.colm[col0 >> 1]);
-          const float4* rz4 = reinterpret_cast<const float4*>(&sh.colrz[col0]);
-#pragma unroll
-          for (int j4 = 0; j4 < 4; ++j4) {   // 4 pairs (8 columns) per step
-            const uint4 cm = cm4[j4];
-            const uint32_t cmv[4] = {cm.x, cm.y, cm.z, cm.w};
-            const float4 rza = rz4[2 * j4], rzb = rz4[2 * j4 + 1];
-            const float rzv[8] = {rza.x, rza.y, rza.z, rza.w, rzb.x, rzb.y, rzb.z, rzb.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const int jp = 4 * j4 + k;
-              const float2 x = fmul2(make_float2(__uint_as_float(raw[2 * jp]), __uint_as_float(raw[2 * jp + 1])), scale2);
-              const V lg = Pair<T>::pack(x.x, x.y);
-              const float2 d = fmul2(Pair<T>::unpack(__hsub2(lg, *reinterpret_cast<const V*>(&cmv[k]))), log2e2);
-              const float2 e = fmul2(make_float2(ex2_approx(d.x), ex2_approx(d.y)),
-                                     make_float2(rzv[2 * k], rzv[2 * k + 1]));
-              pp[jp] = Pair<T>::pack(e.x, e.y);
+                for (int j = 0; j < 32; ++j) {
+                  if (s0 + j > smax) ra[j] = 0xff800000u;  // -inf
+                  if (s0 + 32 + j > smax) rb[j] = 0xff800000u;
+                }
+              }
+              if (sweep == 0) {
+                row_max = s0_chunk(rb, s0_chunk(ra, row_max));
+              } else {
+                row_z = s1_chunk<T>(ra, m2, scale2, row_z);
+                row_z = s1_chunk<T>(rb, m2, scale2, row_z);
+              }
+            } else if (team != buf) {
+              release_tmem(buf);   // the other team's tile (the barrier counts every epilogue warp)
+            } else {
+              // rows of D = keys; columns = window rows j = i*G + g; key `slot` is hidden from columns < jmask
+              const uint32_t tb = lane_addr + buf * 256 + hh * 128;
+              const int jmask = last ? max(0, slot - (256 - p.QCL) - p.i0) * G : 0;
+              float acc2 = 0.f;   // probabilities are >= 0: the neutral element of both reductions
+              uint32_t ra[32], rb[32];
+              if (R > 64) {
+                tmem_ld64(tb, ra, rb);
+                acc2 = s2_chunk<T, G>(ra, &sh.colm[0], &sh.collz[0], R, jmask, scale2, use_max, acc2);
+                acc2 = s2_chunk<T, G>(rb, &sh.colm[16], &sh.collz[32], R - 32, jmask - 32, scale2, use_max, acc2);
+                if (R > 96) {
+                  tmem_ld64(tb + 64, ra, rb);
+                  release_tmem(buf);
+                  acc2 = s2_chunk<T, G>(ra, &sh.colm[32], &sh.collz[64], R - 64, jmask - 64, scale2, use_max, acc2);
+                  acc2 = s2_chunk<T, G>(rb, &sh.colm[48], &sh.collz[96], R - 96, jmask - 96, scale2, use_max, acc2);
+                } else {
+                  tmem_ld32(tb + 64, reinterpret_cast<float(&)[32]>(ra));
+                  release_tmem(buf);
+                  acc2 = s2_chunk<T, G>(ra, &sh.colm[32], &sh.collz[64], R - 64, jmask - 64, scale2, use_max, acc2);
+                }
+              } else if (R > 32) {
+                tmem_ld64(tb, ra, rb);
+                release_tmem(buf);
+                acc2 = s2_chunk<T, G>(ra, &sh.colm[0], &sh.collz[0], R, jmask, scale2, use_max, acc2);
+                acc2 = s2_chunk<T, G>(rb, &sh.colm[16], &sh.collz[32], R - 32, jmask - 32, scale2, use_max, acc2);
+              } else {
+                tmem_ld32(tb, reinterpret_cast<float(&)[32]>(ra));
+                release_tmem(buf);
+                acc2 = s2_chunk<T, G>(ra, &sh.colm[0], &sh.collz[0], R, jmask, scale2, use_max, acc2);
+              }
+              if (pout) pout[pg * 256 + slot] = acc2;
+              else out[pg * 256 + slot] = Elem<T>::from_f32(use_max ? acc2 : acc2 / (float)p.QCL);
             }
           }
-          if (jmask > col0) {  // some of this chunk's window rows cannot see this key (last page only)
-            const T zero = Elem<T>::from_f32(0.f);
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < jmask) reinterpret_cast<T*>(pp)[j] = zero;
-          }
-          const int ncols = R - col0;
-          acc2 = ncols >= 32 ? group_reduce<T, G, true>(pp, ncols, use_max, acc2)
-                             : group_reduce<T, G, false>(pp, ncols, use_max, acc2);
-        }
-        // the two column halves of a key meet in shared memory (two addends: order cannot matter)
-        float* accbuf = sh.acc[tt & 1];
-        if (cbase < R) {
-          if (use_max) atomicMax(reinterpret_cast<int*>(&accbuf[slot]), __float_as_int(fmaxf(acc2, 0.f)));
-          else atomicAdd(&accbuf[slot], acc2);
-        }
-        if (!sync_epilogue(316)) { ok = false; break; }
-        if ((grp & 1) == 0) {
-          const float a = accbuf[slot];
-          accbuf[slot] = 0.f;
-          if (p.partial)
-            p.partial[((int64_t)p.pass * p.total_units + unit) * p.NB * 256 + pg * 256 + slot] = a;
-          else
-            out[pg * 256 + slot] = Elem<T>::from_f32(use_max ? a : a / (float)p.QCL);
         }
       }
-    }
     }  // units
   }
   fence_before_sync();
@@ -445,7 +485,7 @@ static int launch_window_tc(const void* k_cache, const void* q_cache, const WtPa
     int rc = make_tensor_map_5d(&tmQ, UmmaFmt<T>::tm, q_cache, dims, strides, box, sizeof(T));
     if (rc) return rc;
   }
-  const size_t smem = WT_NS * WT_PAGE_BYTES + 4 * WT_QBLOCK_BYTES + sizeof(WtShared) + 1024;
+  const size_t smem = 232448;  // all of it: the tiles take 224 KB, the rest is barriers and statistics
   void (*kern)(const CUtensorMap, const CUtensorMap, const WtParams) = nullptr;
   switch (G) {
     case 1: kern = window_score_tc_kernel<T, 1>; break;
@@ -461,7 +501,9 @@ static int launch_window_tc(const void* k_cache, const void* q_cache, const WtPa
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = p.total_units < sms ? p.total_units : sms;
-  kern<<<grid, WT_THREADS, smem, st>>>(tmK, tmQ, p);
+  WtParams pl = p;
+  pl.smem_bytes = (int)smem;
+  kern<<<grid, WT_THREADS, smem, st>>>(tmK, tmQ, pl);
   return check_launch("zp_window_score(tcgen05)");
 }
 
@@ -536,3 +578,4 @@ int window_score_tc(const void* k_cache, const void* q_cache, const int32_t* seq
 }
 
 }  // namespace zp
+
