@@ -570,11 +570,14 @@ class CompressConfig:
         del self.__dict__["self"]
 
 
-def compress_scores(k_cache, query_cache, score_cache, query_ids, block_tables, compressed, cfg):
+def compress_scores(k_cache, query_cache, score_cache, query_ids, block_tables, compressed, cfg,
+                    parts=None):
     """Stages attention_score .. pad mask of zipage/engine/model_runner.py:471-593.
 
     Returns the final selection scores [L,B,Hkv,NB,BS] (cache dtype) and
-    updates score_cache in place when the global score is on.
+    updates score_cache in place when the global score is on.  `parts`, if a
+    dict, receives the two terms of the combination (`score_term`, `red_term`;
+    model_runner.py:559-561) for the kept-set boundary check.
     """
     scores = attention_score(k_cache, query_cache, query_ids, block_tables)
     if cfg.use_global_score:
@@ -588,7 +591,13 @@ def compress_scores(k_cache, query_cache, score_cache, query_ids, block_tables, 
         red = fn(k_cache, block_tables, temperature=cfg.redudancy_temperature)
         if cfg.use_global_score and cfg.max_norm:
             red = max_norm_(red.contiguous())
+        if parts is not None:
+            parts["score_term"] = (scores * cfg.redudancy_lambda).clone()
+            parts["red_term"] = (red * (1 - cfg.redudancy_lambda)).clone()
         scores = combine_scores(scores, red, cfg.redudancy_lambda)
+    elif parts is not None:
+        parts["score_term"] = scores.clone()
+        parts["red_term"] = None
     scores = scores.contiguous()
     if cfg.use_attention_sink:
         attention_sink_(scores, cfg.sink_len)
@@ -598,7 +607,7 @@ def compress_scores(k_cache, query_cache, score_cache, query_ids, block_tables, 
 
 
 def compress(k_cache, v_cache, query_cache, score_cache, query_ids, block_tables,
-             target_block_tables, compressed, cfg):
+             target_block_tables, compressed, cfg, parts=None):
     """One chunk of `ModelRunner.compress` (zipage/engine/model_runner.py:466-622).
 
     k_cache/v_cache [L,P,BS,Hkv,D], query_cache [L,C,QCL,Hq,D], score_cache
@@ -608,7 +617,7 @@ def compress(k_cache, v_cache, query_cache, score_cache, query_ids, block_tables
     L, _, BS, Hkv, D = k_cache.shape
     B, NB = block_tables.shape
     scores = compress_scores(k_cache, query_cache, score_cache, query_ids, block_tables,
-                             compressed, cfg)
+                             compressed, cfg, parts=parts)
     keep = topk_mask(scores.view(L, B, Hkv, -1), BS * cfg.budget_blocks).view(L, B, Hkv, NB, BS)
     compress_kv(k_cache, v_cache, keep, block_tables, target_block_tables)
     if cfg.use_global_score:

@@ -51,9 +51,10 @@ def _run_oracle(case, inp, dtype):
     k, v, q = (inp[n].to(dtype).clone() for n in ("k", "v", "q"))
     sc = inp["score_cache"].to(dtype).clone() if ocfg.use_global_score else None
     att = O.attention_score(k, q, inp["query_ids"], inp["block_tables"])
+    parts = {}
     final, keep = O.compress(k, v, q, sc, inp["query_ids"], inp["block_tables"], inp["targets"],
-                             inp["compressed"], ocfg)
-    return dict(att=att, final=final, keep=keep, k=k, v=v, sc=sc)
+                             inp["compressed"], ocfg, parts=parts)
+    return dict(att=att, final=final, keep=keep, k=k, v=v, sc=sc, parts=parts)
 
 
 FP32_CASES = [n for n in CASES if CASES[n]["dtype"] == "float32"]
@@ -98,8 +99,13 @@ def test_16bit_matches_oracle(name, dtype):
     fin = torch.isfinite(fb)
     assert torch.equal(fa[~fin], fb[~fin])
     assert (fa[fin] - fb[fin]).abs().max() <= 2e-2 * fb[fin].abs().max()
-    mismatch = (out["keep"] ^ ref["keep"]).float().mean().item()
-    assert mismatch < 1e-2, mismatch
+    # kept sets may differ only on indices whose score sits within one rounding step of the cut
+    from oracle.boundary import kept_set_report
+    L, B, Hkv = ref["keep"].shape[:3]
+    rep = kept_set_report(ref["final"].reshape(L, B, Hkv, -1), ref["keep"].reshape(L, B, Hkv, -1),
+                          out["keep"].reshape(L, B, Hkv, -1), BS * case["cfg"]["budget_blocks"], dtype,
+                          ref["parts"])
+    assert rep["outside"] == 0 and rep["mismatch"] < 1e-2, rep
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
