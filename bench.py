@@ -152,7 +152,7 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.sm)}
 
 
-def cpu_baseline_sample(variant, global_score, threads):
+def cpu_baseline_sample(variant, global_score, threads, keep_sample=False):
     """The oracle (CPU restatement of the reference's PyTorch formulation) on a bounded sample of
     the same workload: L=2 layers, B=16 sequences of 9 pages, 8 KV heads, bf16 (256 units)."""
     import torch
@@ -168,19 +168,106 @@ def cpu_baseline_sample(variant, global_score, threads):
                             continues_pooling=True, pooling_size=POOL)
     times = []
     moved = None
+    sample = None
     for it in range(3):
         k, v = w.kv_cache[0].clone(), w.kv_cache[1].clone()
         sc = w.score_cache.clone() if w.score_cache is not None else None
+        parts = {} if (keep_sample and it == 0) else None
         t0 = time.perf_counter()
-        _, keep = O.compress(k, v, w.query_cache, sc, w.query_ids, w.block_tables, w.target_tables,
-                             w.compressed, ocfg)
+        final, keep = O.compress(k, v, w.query_cache, sc, w.query_ids, w.block_tables, w.target_tables,
+                                 w.compressed, ocfg, parts=parts)
         times.append(time.perf_counter() - t0)
         if moved is None:
             moved = moved_rows_per_unit(keep)
+            if keep_sample:
+                sample = dict(w=w, final=final, keep=keep, parts=parts, k_after=k, v_after=v)
     t = statistics.median(times[1:]) if len(times) > 1 else times[0]
     units = Ls * Bs * HKV
     st = algorithmic_bytes_per_unit(BUDGET + 1, D, QCL, HQ // HKV, 2, variant != "none", global_score, moved)
+    if keep_sample:
+        return sum(st.values()) * units / t / 1e9, t, units, sample
     return sum(st.values()) * units / t / 1e9, t, units
+
+
+def parity_on_sample(sample, cfg, kernel_impl, dev):
+    """The CUDA path on the inputs of the CPU-baseline sample, checked against what the oracle just
+    computed there: fraction of differing keep flags, how many of them lie farther than one
+    rounding step from the top-k cut (must be 0), and whether the compaction given the oracle's
+    flags is bit-identical."""
+    import torch
+    from oracle.boundary import kept_set_report
+    from zipage_b200 import kernel as K
+    from zipage_b200.compress import compress_chunk
+    w = sample["w"]
+    kv = w.kv_cache.to(dev)
+    q, qid, bt, tt, cp = (t.to(dev) for t in (w.query_cache, w.query_ids, w.block_tables,
+                                               w.target_tables, w.compressed))
+    sc = w.score_cache.to(dev) if w.score_cache is not None else None
+    k2, v2 = kv[0].clone(), kv[1].clone()
+    K.compress_kv(k2, v2, sample["keep"].to(dev), bt, tt)
+    compaction_exact = bool(torch.equal(k2.cpu(), sample["k_after"]) and torch.equal(v2.cpu(), sample["v_after"]))
+    dbg = compress_chunk(kv[0], kv[1], q, sc, qid, bt, tt, cp, cfg, impl=kernel_impl, return_debug=True)
+    torch.cuda.synchronize()
+    keep = dbg["keep"].cpu()
+    L, B, Hkv = keep.shape[:3]
+    rep = kept_set_report(sample["final"].reshape(L, B, Hkv, -1), sample["keep"].reshape(L, B, Hkv, -1),
+                          keep.reshape(L, B, Hkv, -1), BS * BUDGET, torch.bfloat16, sample["parts"])
+    fa, fb = dbg["final"].float().cpu(), sample["final"].float()
+    fin = torch.isfinite(fb)
+    return {"sample_units": L * B * Hkv, "kept_mismatch": rep["mismatch"], "differing_flags": rep["differing"],
+            "outside_boundary": rep["outside"], "worst_gap_steps": rep["worst"],
+            "score_max_rel_err": float((fa[fin] - fb[fin]).abs().max() / fb[fin].abs().max()),
+            "compaction_bit_exact_given_flags": compaction_exact}
+
+
+def reference_gpu_stage_times(sample, dev):
+    """The reference's own Triton kernels (unmodified, from baseline/_ref when it is there) on the
+    CPU-baseline sample's inputs, on this GPU: per-stage milliseconds, scaled nowhere.  This is the
+    on-box bar for the kernels; the CPU arm stays the reported baseline.  None when the reference or
+    Triton cannot be imported."""
+    import torch
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "zipage" / "kernel").is_dir():
+        return None
+    try:
+        sys.path.insert(0, str(ref))
+        from zipage.kernel.attention_score import attention_score as r_att
+        from zipage.kernel.compress_kv import compress_kv as r_ckv
+        from zipage.kernel.lightning_redudancy_score import lightning_redudancy_score as r_light
+        from zipage.kernel.raw_redudancy_score import raw_redudancy_score as r_raw
+        from zipage_b200 import kernel as K
+        w = sample["w"]
+        kv = w.kv_cache.to(dev)
+        q, qid, bt, tt = (t.to(dev) for t in (w.query_cache, w.query_ids, w.block_tables, w.target_tables))
+        keep = sample["keep"].to(dev)
+
+        def t_ms(fn, n=3):
+            fn(); torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record(); torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n
+        out = {"units": kv.shape[1] * bt.shape[0] * kv.shape[4]}
+        pairs = {
+            "attention_score": (lambda: r_att(kv[0], q, qid, bt), lambda: K.attention_score(kv[0], q, qid, bt)),
+            "lightning_redudancy_score": (lambda: r_light(kv[0], bt, temperature=TEMP),
+                                          lambda: K.lightning_redudancy_score(kv[0], bt, temperature=TEMP)),
+            "raw_redudancy_score": (lambda: r_raw(kv[0], bt, temperature=TEMP),
+                                    lambda: K.raw_redudancy_score(kv[0], bt, temperature=TEMP)),
+        }
+        for name, (rf, of) in pairs.items():
+            out[name] = {"reference_triton_ms": t_ms(rf), "this_library_ms": t_ms(of)}
+        k1, v1, k2, v2 = kv[0].clone(), kv[1].clone(), kv[0].clone(), kv[1].clone()
+        out["compress_kv"] = {"reference_triton_ms": t_ms(lambda: r_ckv(k1, v1, keep, bt, tt), n=1),
+                              "this_library_ms": t_ms(lambda: K.compress_kv(k2, v2, keep, bt, tt), n=1)}
+        return out
+    except Exception as e:  # the reference is optional here
+        return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    finally:
+        if str(ref) in sys.path:
+            sys.path.remove(str(ref))
 
 
 def moved_rows_per_unit(keep):
@@ -730,18 +817,66 @@ def main():
     chunk = args.layer_chunk or L
     comp = Compressor(w.kv_cache, w.query_cache, w.score_cache, cfg, layer_stride=chunk,
                       impl=args.kernel_impl)
+    if args.variant == "exact":
+        comp._ensure_workspace(B, BUDGET + 1)
     seq_tables = w.tables_plain.cpu().tolist()
     seq_targets = w.target_tables.cpu().tolist()
     seq_qids = w.query_ids.cpu().tolist()
     seq_comp = w.compressed.cpu().tolist()
 
-    def device_step():
+    nb_last = BUDGET   # table position of the page that is appended to between compressions
+    last_pages = w.tables_plain[:, nb_last].long()
+    fresh = torch.empty((B, BS, hkv, D), dtype=torch.bfloat16, device=dev)
+    rgen = torch.Generator(device=dev).manual_seed(99 + rank)
+
+    def refresh():
+        """Between steps, outside every timed event: the engine's steady state.  A compression leaves
+        8 compacted pages and the page new tokens are appended to; 256 decode steps later that page
+        is full of new keys and the window holds new queries.  Refilling both makes every step the
+        same work on fresh data instead of a recompression of its own output."""
+        for t in range(2):
+            for l in range(L):
+                fresh.normal_(generator=rgen)
+                w.kv_cache[t, l].index_copy_(0, last_pages, fresh)
+        w.query_cache.normal_(generator=rgen)
+
+    class StageTimers:
+        """Per-stage CUDA events of one step, on the stream the kernels are launched on."""
+        def __init__(self):
+            self.events = []
+
+        def __call__(self, name):
+            outer = self
+
+            class _Ctx:
+                def __enter__(self_):
+                    self_.st = torch.cuda.Event(enable_timing=True)
+                    self_.ed = torch.cuda.Event(enable_timing=True)
+                    self_.st.record()
+
+                def __exit__(self_, *a):
+                    self_.ed.record()
+                    outer.events.append((name, self_.st, self_.ed))
+                    return False
+            return _Ctx()
+
+        def totals(self):
+            out = {}
+            for name, st, ed in self.events:
+                out[name] = out.get(name, 0.0) + st.elapsed_time(ed)
+            return out
+
+    def device_step(timers=None, want_keep=False):
+        moved = []
         for l0 in range(0, L, chunk):
             sl = slice(l0, min(L, l0 + chunk))
-            compress_chunk(w.kv_cache[0, sl], w.kv_cache[1, sl], w.query_cache[sl],
-                           None if w.score_cache is None else w.score_cache[sl], w.query_ids,
-                           w.block_tables, w.target_tables, w.compressed, cfg, impl=args.kernel_impl,
-                           workspace=comp.workspace)
+            keep = compress_chunk(w.kv_cache[0, sl], w.kv_cache[1, sl], w.query_cache[sl],
+                                  None if w.score_cache is None else w.score_cache[sl], w.query_ids,
+                                  w.block_tables, w.target_tables, w.compressed, cfg, impl=args.kernel_impl,
+                                  workspace=comp.workspace, timers=timers, return_keep=want_keep)
+            if want_keep:
+                moved.append((keep, sl.stop - sl.start))
+        return moved
 
     def barrier():
         if world > 1:
@@ -749,39 +884,74 @@ def main():
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
+        refresh()
         device_step()
     barrier()
     K.LAUNCHES = 0
+    step_ms, stage_sums, moved_steps = [], {}, []
+    region0 = time.perf_counter()
     with ClockSampler(local) as clocks:
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record()
         for _ in range(args.steps):
-            device_step()
-        ev1.record()
+            refresh()
+            torch.cuda.synchronize()
+            timers = StageTimers()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            kept = device_step(timers, want_keep=True)
+            ev1.record()
+            torch.cuda.synchronize()
+            step_ms.append(ev0.elapsed_time(ev1))
+            for name, ms in timers.totals().items():
+                stage_sums[name] = stage_sums.get(name, 0.0) + ms
+            # moved rows of THIS step, every layer (a device-side reduction, outside the events)
+            tot = sum(moved_rows_per_unit(k) * n for k, n in kept) / L
+            moved_steps.append(tot)
+            del kept
         barrier()
-        dev_ms = ev0.elapsed_time(ev1)
+    region_s = time.perf_counter() - region0
     launches = K.LAUNCHES
-    # stage split (one extra untimed-by-the-headline step with per-stage events)
-    comp.time_record.clear()
-    comp.compress_tables(seq_tables, seq_targets, seq_qids, seq_comp, timed=True)
-    stage_ms = {k: v * 1e3 for k, v in comp.time_record.items() if k.endswith("_sum")}
+    dev_ms = sum(step_ms)
+    stage_ms = {k + "_sum": v / args.steps for k, v in stage_sums.items()}
+    moved = statistics.mean(moved_steps)
 
     # end to end through the host-facing call: host lists -> pinned -> H2D, kernels, sync, D2H
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
+    e2e_times = []
+    for i in range(2 + args.steps):   # two untimed calls first: staging buffers and scratch get allocated
+        refresh()
+        barrier()
+        t0 = time.perf_counter()
         new_tables, ctx_lens = comp.compress_tables(seq_tables, seq_targets, seq_qids, seq_comp)
-    barrier()
-    e2e_s = (time.perf_counter() - t0) / args.steps
+        if i >= 2:
+            e2e_times.append(time.perf_counter() - t0)
+    e2e_s = statistics.mean(e2e_times)
     h2d = comp.last_h2d_bytes
     d2h = comp.last_d2h_bytes
 
-    # algorithmic bytes: moved rows counted from the flags of one more selection pass
-    dbg = compress_chunk(w.kv_cache[0, :1], w.kv_cache[1, :1], w.query_cache[:1],
-                         None if w.score_cache is None else w.score_cache[:1], w.query_ids,
-                         w.block_tables, w.target_tables, w.compressed, cfg, impl=args.kernel_impl,
-                         workspace=comp.workspace, return_debug=True)
-    moved = moved_rows_per_unit(dbg["keep"])
+    # the engine's real call shape: ModelRunner.compress gets at most 600 // table_len sequences per
+    # call (zipage/engine/zipage_engine.py:143-156) and walks the layers 8 at a time (config.py:45)
+    eng = None
+    if world == 1 and not args.no_cpu_baseline:
+        nb_seq = min(B, 600 // (BUDGET + 1))
+        small = Compressor(w.kv_cache, w.query_cache, w.score_cache, cfg, layer_stride=8,
+                           impl=args.kernel_impl)
+        ts = []
+        for i in range(args.warmup + args.steps):
+            refresh()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            small.compress_tables(seq_tables[:nb_seq], seq_targets[:nb_seq], seq_qids[:nb_seq], seq_comp[:nb_seq])
+            if i >= args.warmup:
+                ts.append(time.perf_counter() - t0)
+        for _ in range(2):   # the second call's stage events are free of allocator stalls
+            refresh()
+            torch.cuda.synchronize()
+            small.time_record.clear()
+            small.compress_tables(seq_tables[:nb_seq], seq_targets[:nb_seq], seq_qids[:nb_seq],
+                                  seq_comp[:nb_seq], timed=True)
+        kern_ms = sum(v for k, v in small.time_record.items() if k.endswith("_sum")) * 1e3
+        eng = {"sequences": nb_seq, "layer_stride": 8, "ms_per_call": statistics.mean(ts) * 1e3,
+               "kernel_ms_per_call": kern_ms, "units_per_call": nb_seq * L * hkv}
+
     stages = algorithmic_bytes_per_unit(BUDGET + 1, D, QCL, hq // hkv, itemsize,
                                         args.variant != "none", args.global_score, moved)
     units = L * B * hkv
@@ -795,23 +965,46 @@ def main():
     value = bytes_step * world / (ms_step * 1e-3) / 1e9
     e2e_val = bytes_step * world / (e2e_ms * 1e-3) / 1e9
 
+    exact = None
+    if rank == 0 and world == 1 and args.variant == "lightning" and not args.no_cpu_baseline:
+        # the exact-similarity variant of the same step (two passes, the second timed)
+        xcfg = make_cfg("exact", args.global_score)
+        xcomp = Compressor(w.kv_cache, w.query_cache, w.score_cache, xcfg, layer_stride=min(chunk, 6),
+                           impl=args.kernel_impl)
+        xt = None
+        for i in range(2):
+            refresh()
+            xcomp.time_record.clear()
+            xcomp.compress_tables(seq_tables, seq_targets, seq_qids, seq_comp, timed=True)
+            xt = {k: v * 1e3 for k, v in xcomp.time_record.items() if k.endswith("_sum")}
+        n_tok = (BUDGET + 1) * BS
+        flops = 2.0 * n_tok * n_tok * D * units
+        red_ms = xt.get("redudancy_score_sum", 0.0)
+        exact = {"ms_per_step": sum(xt.values()), "stage_ms": xt,
+                 "similarity_tflops_dense_count": flops / (red_ms * 1e-3) / 1e12 if red_ms else None,
+                 "similarity_tflops_issued": flops * (BUDGET + 2) / (2.0 * (BUDGET + 1)) / (red_ms * 1e-3) / 1e12
+                 if red_ms else None}
+        del xcomp
+
     if rank == 0:
         peaks = {}
         pk = ROOT / "MEASURED_PEAKS.json"
         if pk.exists():
             peaks = json.loads(pk.read_text())
         hbm_peak = peaks.get("hbm_gbs", 6650.0)
-        # dominant kernel by the per-stage split
+        # dominant kernel by the per-stage split (mean over the timed steps)
         top = max(stage_ms, key=stage_ms.get) if stage_ms else "attention_score_sum"
         stage_key = {"attention_score_sum": "window_score", "redudancy_score_sum": "redundancy",
                      "topk_mask_sum": "select", "compress_kv_sum": "compact",
                      "global_score_sum": "window_score"}.get(top, "window_score")
         nlaunch = (L + chunk - 1) // chunk
         top_ms = stage_ms.get(top, ms_step) / nlaunch
-        # DRAM bytes per unit of each kernel from the committed ncu capture of a 1024-unit case
-        # (profiles/compress_op_tcgen05_kernels_b32_l4.md); traffic grows in proportion to the units
-        ncu_bytes_per_unit = {"window_score": 760.809e6 / 1024, "redundancy": 614.333e6 / 1024,
-                              "compact": 2072.943e6 / 1024, "select": 9.48e6 / 1024}
+        # DRAM bytes per unit of each kernel from the committed ncu capture of a small case
+        # (traffic grows in proportion to the units of a launch)
+        ncu_bytes_per_unit = {}
+        tf = ROOT / "profiles" / "compress_op_dram_bytes_per_unit.json"
+        if tf.exists():
+            ncu_bytes_per_unit = json.loads(tf.read_text()).get("bytes_per_unit", {})
         if stage_key == "redundancy" and args.variant == "exact":
             # algorithmic flops = the reference's dense N x N x D similarity product per unit; the
             # kernel skips the page tiles below the diagonal (S is symmetric), so it executes
@@ -831,12 +1024,18 @@ def main():
         else:
             achieved = stages[stage_key] * units / nlaunch / (top_ms * 1e-3) / 1e9
             traffic = None
-            if args.variant == "lightning" and args.kernel_impl != "simt":
+            if args.variant == "lightning" and args.kernel_impl != "simt" and stage_key in ncu_bytes_per_unit:
                 traffic = ncu_bytes_per_unit[stage_key] * units / nlaunch
             roofline = {"bound": "hbm", "kernel": stage_key, "achieved": achieved, "peak": hbm_peak,
                         "unit": "GB/s", "frac": achieved / hbm_peak,
                         "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback",
                         "traffic": traffic}
+        per_stage = {}
+        for sk, key in (("attention_score_sum", "window_score"), ("redudancy_score_sum", "redundancy"),
+                        ("topk_mask_sum", "select"), ("compress_kv_sum", "compact")):
+            if sk in stage_ms and stage_ms[sk] > 0 and stages.get(key):
+                gbs = stages[key] * units / (stage_ms[sk] * 1e-3) / 1e9
+                per_stage[key] = {"ms": stage_ms[sk], "gbs": gbs, "frac_of_hbm_peak": gbs / hbm_peak}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -849,22 +1048,34 @@ def main():
                 "units_per_gpu": units, "global_score": args.global_score,
                 "kernel_impl": args.kernel_impl, "layer_chunk": chunk,
                 "l2": "inputs (K/V pages of all sequences) are far larger than the 126 MB L2",
+                "steady_state": "between steps, outside the per-step events, the appended page of every "
+                                "sequence and the window queries are refilled with fresh N(0,1) data",
                 "parallelism": f"kv-head sharding x{world}, no data-path collective",
             },
             "units_per_s": units * world / (ms_step * 1e-3),
             "algorithmic_bytes_per_unit": stages, "moved_rows_per_unit": moved,
-            "stage_ms": stage_ms,
+            "moved_rows_per_unit_by_step": moved_steps,
+            "stage_ms": stage_ms, "stage_ms_total": sum(stage_ms.values()), "per_stage": per_stage,
+            "timed_region_s": region_s,
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms},
             "gpu_launches": launches,
             "clocks": clocks.summary(),
             "roofline": roofline,
         }
+        if eng is not None:
+            line["e2e_engine_call_shape"] = eng
+        if exact is not None:
+            line["exact_variant"] = exact
         if not args.no_cpu_baseline and world == 1:
             threads = os.cpu_count() or 1
-            gbs, secs, cu = cpu_baseline_sample(args.variant, args.global_score, threads)
+            gbs, secs, cu, sample = cpu_baseline_sample(args.variant, args.global_score, threads, keep_sample=True)
             line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
                                     "sample": f"oracle.compress on {cu} units (L=2,B=16,Hkv=8,9 pages,bf16), {secs:.2f}s per pass"}
+            line["parity"] = parity_on_sample(sample, cfg, args.kernel_impl, dev)
+            ref_gpu = reference_gpu_stage_times(sample, dev)
+            if ref_gpu is not None:
+                line["reference_gpu"] = ref_gpu
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -55,6 +55,10 @@ int zp_version(void);
  * kernels).  This call synchronises the device, stores the word in *code_out (0 = no error; else an
  * internal code naming the wait) and clears it when reset != 0. */
 int zp_device_error(int* code_out, int reset);
+/* The same word without a device-wide synchronisation: a 4-byte copy into host_out (pinned host
+ * memory) ordered on `stream`; the caller reads *host_out after it has synchronised that stream.
+ * The word is not cleared.  (No reference counterpart.) */
+int zp_device_error_async(int* host_out, void* stream);
 
 /* Replaces store_kvcache, zipage/layers/attention.py:12-50.
  * key/value [N, Hkv, D] (row stride given), caches contiguous [P*BS, Hkv, D];

@@ -49,6 +49,7 @@ SIGNATURES = {
     "zp_last_error": (C.c_char_p, []),
     "zp_version": (_I, []),
     "zp_device_error": (_I, [C.POINTER(C.c_int), _I]),
+    "zp_device_error_async": (_I, [_P, _P]),
     "zp_store_kv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _L, _L, _I, _P]),
     "zp_store_query": (_I, [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P]),
     "zp_window_score": (_I, [_P, _P, _P, _P, _P, _P] + [_I] * 8 + [_L] * 4 + [_F, _I, _I, _I, _P]),

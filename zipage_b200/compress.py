@@ -39,14 +39,15 @@ class CompressConfig:
 
 def compress_chunk(k_cache, v_cache, query_cache, score_cache, query_ids, block_tables,
                    target_block_tables, compressed, cfg: CompressConfig, impl="auto",
-                   workspace=None, return_debug=False, timers=None):
+                   workspace=None, return_debug=False, timers=None, return_keep=False):
     """Compress B sequences over the L layers of the given cache views, in place.
 
     k_cache/v_cache [L,P,BS,Hkv,D]; query_cache [L,C,QCL,Hq,D]; score_cache [L,P,BS,Hkv] or None;
     query_ids [B] int32; block_tables [B,NB] int32 (encoded: -1 pad, -(id)-2 last page);
     target_block_tables [B,budget+1] int32; compressed [B] bool.
     `timers`, if given, is a callable name -> context manager used to time the stages under the
-    reference's stage names (model_runner.py:425-430).
+    reference's stage names (model_runner.py:425-430).  `return_keep` returns the keep flags
+    [L,B,Hkv,NB,BS] the compaction ran with (for accounting; nothing extra is computed).
     """
     BS = k_cache.shape[2]
     stage = timers if timers is not None else (lambda name: _NULL)
@@ -78,15 +79,16 @@ def compress_chunk(k_cache, v_cache, query_cache, score_cache, query_ids, block_
                                 keep, block_tables, target_block_tables)
     if return_debug:
         return dict(scores=scores, red_logits=red_logits, final=final, keep=keep)
-    return None
+    return keep if return_keep else None
 
 
 def compress_batch(k_cache, v_cache, query_cache, score_cache, query_ids, block_tables,
                    target_block_tables, compressed, cfg: CompressConfig, impl="auto", workspace=None,
-                   update_tables=False):
+                   update_tables=False, return_workspace=False):
     """The same op as `compress_chunk` through the single C entry point `zp_compress_batch`
     (one host call, scratch from one workspace tensor).  Returns (new_table, context_len, next_slot)
-    device tensors when update_tables is set, else None."""
+    device tensors when update_tables is set, else None.  `return_workspace` returns the (possibly
+    newly grown) workspace tensor instead, for callers that keep it between calls."""
     import ctypes
 
     from . import _lib as L
@@ -127,6 +129,8 @@ def compress_batch(k_cache, v_cache, query_cache, score_cache, query_ids, block_
         sc.stride(1) if sc is not None else 0, ctypes.byref(pr), code, L.IMPL[impl], L.ptr(workspace),
         workspace.numel() * workspace.element_size(), L.stream_ptr()), "compress_batch")
     K._count(4 + int(cfg.use_global_score) + int(update_tables))
+    if return_workspace:
+        return workspace
     return outs if update_tables else None
 
 

@@ -65,3 +65,11 @@ extern "C" int zp_device_error(int* code_out, int reset) {
   }
   return ZP_OK;
 }
+
+extern "C" int zp_device_error_async(int* host_out, void* stream) {
+  int* word = zp::tc::device_error_word();
+  if (!word || !host_out) { zp::set_error("zp_device_error_async: no error word / null destination"); return ZP_ERR_CUDA; }
+  cudaError_t e = cudaMemcpyAsync(host_out, word, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) { zp::set_error("zp_device_error_async: %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
+  return ZP_OK;
+}

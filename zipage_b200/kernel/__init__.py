@@ -282,9 +282,11 @@ def compress_kv_and_score(key, value, score_cache, flag, block_table, target_blo
     _compact(key, value, score_cache, flag, block_table, target_block_table, "compress_kv+score")
 
 
-def update_tables(target_block_table, table_width=None):
+def update_tables(target_block_table, table_width=None, block_size=256):
     """Device-side table update after a compaction: returns (new_table [B,width] padded with -1,
-    context_len [B], next_slot [B]); host counterpart: zipage/engine/scheduler.py:150-156."""
+    context_len [B] = block_size*(NT-1)+1, next_slot [B] = page*block_size); host counterpart:
+    zipage/engine/scheduler.py:150-156.  `block_size` is the cache's page size (any multiple of
+    256 in the reference, zipage/config.py:48)."""
     B, NT = target_block_table.shape
     width = table_width or NT
     dev = target_block_table.device
@@ -292,7 +294,7 @@ def update_tables(target_block_table, table_width=None):
     ctx = torch.empty(B, dtype=torch.int32, device=dev)
     nxt = torch.empty(B, dtype=torch.int32, device=dev)
     L.check(L.load().zp_update_tables(L.ptr(_i32(target_block_table)), L.ptr(new_table), L.ptr(ctx),
-                                      L.ptr(nxt), B, NT, width, 256, L.stream_ptr()),
+                                      L.ptr(nxt), B, NT, width, int(block_size), L.stream_ptr()),
             "update_tables")
     _count()
     return new_table, ctx, nxt
