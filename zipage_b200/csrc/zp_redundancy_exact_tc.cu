@@ -418,15 +418,17 @@ redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmK, const XtPara
 #pragma unroll
             for (int j = 0; j < 32; ++j) raw[j] = (j == lane) ? 0u : raw[j];
           }
-          // maximum of the 32 values as a tree of 3-input maxima (depth 4)
-          float t[11];
+          // Largest positive accumulator of the 32 as a tree of 3-input INTEGER maxima (depth 4):
+          // the bound is positive, positive floats order like their bit patterns read as signed
+          // integers, and every negative float reads as a negative integer.
+          int t[11];
 #pragma unroll
           for (int j = 0; j < 10; ++j)
-            t[j] = fmax3(__uint_as_float(raw[3 * j]), __uint_as_float(raw[3 * j + 1]), __uint_as_float(raw[3 * j + 2]));
-          t[10] = fmaxf(__uint_as_float(raw[30]), __uint_as_float(raw[31]));
-          const float u0 = fmax3(t[0], t[1], t[2]), u1 = fmax3(t[3], t[4], t[5]);
-          const float u2 = fmax3(t[6], t[7], t[8]), u3 = fmaxf(t[9], t[10]);
-          if (fmaxf(fmax3(u0, u1, u2), u3) > thr_m * nmc) {
+            t[j] = __vimax3_s32((int)raw[3 * j], (int)raw[3 * j + 1], (int)raw[3 * j + 2]);
+          t[10] = max((int)raw[30], (int)raw[31]);
+          const int u0 = __vimax3_s32(t[0], t[1], t[2]), u1 = __vimax3_s32(t[3], t[4], t[5]);
+          const int u2 = __vimax3_s32(t[6], t[7], t[8]), u3 = max(t[9], t[10]);
+          if (__int_as_float(max(__vimax3_s32(u0, u1, u2), max(u3, 0))) > thr_m * nmc) {
             const int64_t ubase = rbase - (int64_t)mp * 256;
             const unsigned n0 = pg * 256 + ch * 128 + c * 32;
             const float* rnc = p.rn + ubase + n0;
@@ -442,7 +444,7 @@ redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmK, const XtPara
             }
           }
         };
-        if (!mbar_wait(&sh.tfull[g], use & 1, abortp, p.error_word, 304)) { ok = false; break; }
+        if (!mbar_wait<32>(&sh.tfull[g], use & 1, abortp, p.error_word, 304)) { ok = false; break; }
         ++use;
         fence_after_sync();
 #pragma unroll 1

@@ -194,7 +194,7 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
     auto sync_team = [&](int where) -> bool {
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh.team_bar[team]);
-      const bool ok_ = mbar_wait(&sh.team_bar[team], ph_team & 1, abortp, p.error_word, where);
+      const bool ok_ = mbar_wait<0>(&sh.team_bar[team], ph_team & 1, abortp, p.error_word, where);
       ++ph_team;
       return ok_;
     };
@@ -212,7 +212,7 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
         const int tt = t++;
         if ((tt & 1) != team) continue;   // the other team's page
         const int s = tt % NS, k = tt / NS;
-        if (!mbar_wait(&sh.full[s], k & 1, abortp, p.error_word, 302)) { ok = false; break; }
+        if (!mbar_wait<32>(&sh.full[s], k & 1, abortp, p.error_word, 302)) { ok = false; break; }
         {   // a warp covers exactly one 32-column chunk of the page
           const float nrm = fmaxf(round_to<T>(sqrtf(row_sumsq<T>(stage_ptr(s), myrow))), eps_t);
           tm.rn[myrow] = 1.f / nrm;
@@ -234,7 +234,7 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           const int use = (tt >> 1) * 2 + hh;
-          if (!mbar_wait(&sh.tfull[team], use & 1, abortp, p.error_word, 304)) { ok = false; break; }
+          if (!mbar_wait<32>(&sh.tfull[team], use & 1, abortp, p.error_word, 304)) { ok = false; break; }
           fence_after_sync();
           float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll 1
@@ -254,7 +254,10 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
             }
             // row sum: acc * (1/|k_n|) accumulated in four chains; and the threshold filter on the
             // raw accumulators: S > thr needs acc > thr * |k_m| * |k_n| >= thr * |k_m| * min|k_n|
-            float m0 = -INFINITY, m1 = -INFINITY;
+            // (the bound is positive, and positive floats order like their bit patterns read as
+            // signed integers while every negative float reads as a negative integer: the largest
+            // positive accumulator, if there is one, is found with 3-input integer maxima)
+            int m0 = 0, m1 = 0;
             const float4* rn4 = reinterpret_cast<const float4*>(tm.rn + cg * 32);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -263,10 +266,10 @@ redundancy_tc_kernel(const __grid_constant__ CUtensorMap tmK, const RtParams p) 
               const float a2 = __uint_as_float(raw[4 * j + 2]), a3 = __uint_as_float(raw[4 * j + 3]);
               s0 = fmaf(a0, f.x, s0); s1 = fmaf(a1, f.y, s1);
               s2 = fmaf(a2, f.z, s2); s3 = fmaf(a3, f.w, s3);
-              m0 = fmax3(m0, a0, a1);
-              m1 = fmax3(m1, a2, a3);
+              m0 = __vimax3_s32(m0, (int)raw[4 * j], (int)raw[4 * j + 1]);
+              m1 = __vimax3_s32(m1, (int)raw[4 * j + 2], (int)raw[4 * j + 3]);
             }
-            if (fmaxf(m0, m1) > thr_m[hh] * tm.nmin[cg]) {  // rare: look at the normalised values
+            if (__int_as_float(max(m0, m1)) > thr_m[hh] * tm.nmin[cg]) {  // rare: look at the normalised values
               const float* rnc = tm.rn + cg * 32;
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
