@@ -68,11 +68,15 @@ int zp_store_kv(const void* key, const void* value, void* k_cache, void* v_cache
                 int64_t key_stride0, int64_t value_stride0, int dtype, void* stream);
 
 /* Replaces store_query_cache, zipage/kernel/store_query_cache.py:7-68.
- * query [N, Hq, D]; query_cache [C, QCL, Hq, D] (one layer); triples [n, 3] int32 =
- * (row of query, query_id, window index). */
+ * query [n_query_rows, Hq, D]; query_cache [cache_seqs, window_len, Hq, D] (one layer); triples
+ * [n_triples, 3] int32 = (row of query, query_id, window index).  valid_count: NULL, or a device
+ * word holding how many leading triples are valid (a list built on the device into a buffer of
+ * fixed capacity, as zp_prepare_decode leaves it): the rest are not read.  A triple that names
+ * no row of `query` or no slot of the cache is skipped. */
 int zp_store_query(const void* query, void* query_cache, const int32_t* triples, int n_triples,
                    int num_heads, int head_dim, int64_t query_stride0, int64_t cache_stride_seq,
-                   int64_t cache_stride_slot, int dtype, void* stream);
+                   int64_t cache_stride_slot, int dtype, const int32_t* valid_count,
+                   int n_query_rows, int cache_seqs, int window_len, void* stream);
 
 /* Replaces attention_score, zipage/kernel/attention_score.py:8-250 (kernel + torch glue), without
  * the [L,B,Hq,QCL,NB,BS] logits buffer: softmax over the sequence of the window queries' logits,

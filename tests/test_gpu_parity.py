@@ -170,6 +170,32 @@ def test_store_kernels():
         K.store_query_cache(q.to(dev), torch.empty(0, device=dev, dtype=dtype), triples.to(dev))
 
 
+def test_store_query_ignores_the_unwritten_tail_of_a_device_built_list():
+    """A triple buffer of fixed capacity whose valid count lives in a device word (what
+    zp_prepare_decode leaves behind): rows past the count hold garbage and must store nothing;
+    triples that point outside the query rows or the cache are skipped, not dereferenced."""
+    from zipage_b200 import kernel as K
+    dev = _gpu()
+    g = torch.Generator().manual_seed(4)
+    Hq, D, QCL, C, N = 8, 128, 16, 4, 6
+    q = torch.randn(N, Hq, D, generator=g).to(torch.bfloat16).to(dev)
+    qc = torch.zeros(C, QCL, Hq, D, dtype=torch.bfloat16, device=dev)
+    triples = torch.tensor([[0, 2, 0], [5, 1, 15], [3, 0, 7],
+                            [1 << 28, 1 << 28, 1 << 28], [-5, -1, 99], [2, 3, 3]],   # garbage tail
+                           dtype=torch.int32, device=dev)
+    count = torch.tensor([3], dtype=torch.int32, device=dev)
+    K.store_query_cache(q, qc, triples, count)
+    want = torch.zeros_like(qc)
+    want[2, 0], want[1, 15], want[0, 7] = q[0], q[5], q[3]
+    assert torch.equal(qc, want)
+    # without a count every row is read, and the out-of-range ones are skipped
+    qc.zero_()
+    K.store_query_cache(q, qc, triples)
+    want[3, 3] = q[2]
+    torch.cuda.synchronize()
+    assert torch.equal(qc, want)
+
+
 def test_redundancy_functions_match_oracle():
     from oracle import zipage_oracle as O
     from zipage_b200 import kernel as K

@@ -51,7 +51,7 @@ SIGNATURES = {
     "zp_device_error": (_I, [C.POINTER(C.c_int), _I]),
     "zp_device_error_async": (_I, [_P, _P]),
     "zp_store_kv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _L, _L, _I, _P]),
-    "zp_store_query": (_I, [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P]),
+    "zp_store_query": (_I, [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P, _I, _I, _I, _P]),
     "zp_window_score": (_I, [_P, _P, _P, _P, _P, _P] + [_I] * 8 + [_L] * 4 + [_F, _I, _I, _I, _P]),
     "zp_window_score_workspace_bytes": (_Z, [_I] * 6),
     "zp_window_score_ws": (_I, [_P, _P, _P, _P, _P, _P] + [_I] * 8 + [_L] * 4 + [_F, _I, _I, _I, _P, _Z, _P]),

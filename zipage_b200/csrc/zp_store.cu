@@ -22,11 +22,18 @@ __global__ void store_kv_kernel(const char* __restrict__ key, const char* __rest
   }
 }
 
+// One block per triple.  Rows past *valid_count (when given) and triples that do not name a row of
+// `query` and a slot of the cache are skipped: a capacity-sized triple buffer whose tail was never
+// written (the device-built list of a replayed decode graph) stores nothing from that tail.
 __global__ void store_query_kernel(const char* __restrict__ query, char* __restrict__ query_cache,
                                    const int32_t* __restrict__ triples, int64_t q_stride_b,
-                                   int64_t c_stride_seq_b, int64_t c_stride_slot_b, int row_bytes) {
+                                   int64_t c_stride_seq_b, int64_t c_stride_slot_b, int row_bytes,
+                                   const int32_t* __restrict__ valid_count, int n_query_rows,
+                                   int cache_seqs, int window_len) {
   const int i = blockIdx.x;
+  if (valid_count && i >= *valid_count) return;
   const int row = triples[3 * i], qid = triples[3 * i + 1], idx = triples[3 * i + 2];
+  if (row < 0 || row >= n_query_rows || qid < 0 || qid >= cache_seqs || idx < 0 || idx >= window_len) return;
   const char* src = query + (int64_t)row * q_stride_b;
   char* dst = query_cache + (int64_t)qid * c_stride_seq_b + (int64_t)idx * c_stride_slot_b;
   for (int o = threadIdx.x * 16; o < row_bytes; o += blockDim.x * 16) st16(dst + o, ld16(src + o));
@@ -56,7 +63,8 @@ extern "C" int zp_store_kv(const void* key, const void* value, void* k_cache, vo
 extern "C" int zp_store_query(const void* query, void* query_cache, const int32_t* triples,
                               int n_triples, int num_heads, int head_dim, int64_t query_stride0,
                               int64_t cache_stride_seq, int64_t cache_stride_slot, int dtype,
-                              void* stream) {
+                              const int32_t* valid_count, int n_query_rows, int cache_seqs,
+                              int window_len, void* stream) {
   if (n_triples == 0) return ZP_OK;
   ZP_REQUIRE(query && query_cache && triples, "zp_store_query: null pointer");
   const size_t es = zp::dtype_size(dtype);
@@ -68,6 +76,7 @@ extern "C" int zp_store_query(const void* query, void* query_cache, const int32_
              "zp_store_query: pointers must be 16-byte aligned");
   zp::store_query_kernel<<<n_triples, 128, 0, (cudaStream_t)stream>>>(
       (const char*)query, (char*)query_cache, triples, query_stride0 * (int64_t)es,
-      cache_stride_seq * (int64_t)es, cache_stride_slot * (int64_t)es, row_bytes);
+      cache_stride_seq * (int64_t)es, cache_stride_slot * (int64_t)es, row_bytes, valid_count,
+      n_query_rows, cache_seqs, window_len);
   return zp::check_launch("zp_store_query");
 }

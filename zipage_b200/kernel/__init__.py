@@ -56,18 +56,22 @@ def store_kvcache(key, value, k_cache, v_cache, slot_mapping):
     _count()
 
 
-def store_query_cache(query, query_cache, slot_mapping):
-    """zipage/kernel/store_query_cache.py:35-68."""
+def store_query_cache(query, query_cache, slot_mapping, valid_count=None):
+    """zipage/kernel/store_query_cache.py:35-68.  `valid_count`: optional device int32 [1] with the
+    number of leading rows of `slot_mapping` that are valid (a device-built list of fixed
+    capacity); rows past it are not read."""
     if query_cache.numel() == 0:  # warm-up
         return
-    L.require_cuda(query, query_cache, slot_mapping)
-    _, H, D = query.shape
+    L.require_cuda(query, query_cache, slot_mapping, valid_count)
+    N, H, D = query.shape
     assert query.stride(-1) == 1 and query.stride(1) == D
     assert query_cache.stride(1) == H * D
     L.check(L.load().zp_store_query(L.ptr(query), L.ptr(query_cache), L.ptr(_i32(slot_mapping)),
                                     slot_mapping.shape[0], H, D, query.stride(0),
                                     query_cache.stride(0), query_cache.stride(1),
-                                    L.dtype_code(query_cache), L.stream_ptr()), "store_query_cache")
+                                    L.dtype_code(query_cache), L.ptr(valid_count), N,
+                                    query_cache.shape[0], query_cache.shape[1], L.stream_ptr()),
+            "store_query_cache")
     _count()
 
 

@@ -96,7 +96,9 @@ class Attention(nn.Module):
         if k_cache.numel() and v_cache.numel():
             store_kvcache(k, v, k_cache, v_cache, context.slot_mapping)
         if context.query_slot_mapping is not None:
-            store_query_cache(q, self.q_cache, context.query_slot_mapping)
+            # a device-built triple list has fixed capacity; only its first query_slot_count rows count
+            store_query_cache(q, self.q_cache, context.query_slot_mapping,
+                              getattr(context, "query_slot_count", None))
         return self.attend(q, k, v)
 
     def attend(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
