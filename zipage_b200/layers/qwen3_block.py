@@ -93,6 +93,13 @@ class Qwen3DecoderLayer(nn.Module):
     def __init__(self, config, comm=None):
         super().__init__()
         self.comm = comm
+        # The reference hands config.rope_scaling to its rope initialiser, which changes the
+        # frequencies and the attention scaling (zipage/layers/rotary_embedding.py:67-83).  Only
+        # the unscaled table is built here: a scaled configuration is refused rather than rotated
+        # with the wrong table.
+        rs = getattr(config, "rope_scaling", None)
+        if rs and rs.get("rope_type", rs.get("type", "default")) != "default":
+            raise NotImplementedError(f"rope_scaling {rs!r} is not supported (default rope only)")
         self.self_attn = Qwen3Attention(
             hidden_size=config.hidden_size, num_heads=config.num_attention_heads,
             num_kv_heads=config.num_key_value_heads, max_position=config.max_position_embeddings,
