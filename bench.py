@@ -45,8 +45,12 @@ def parse_args():
     ap.add_argument("--global-score", action="store_true")
     ap.add_argument("--kernel-impl", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode-step record of the default run")
+    ap.add_argument("--engine", action="store_true",
+                    help="also run the reference ENGINE (baseline/_ref) on a synthetic Qwen3-8B-shaped model, as it "
+                         "is and with this library's decode path bound, and report decode tokens/s (adds minutes)")
     ap.add_argument("--also-exact", action="store_true", help="time the exact variant as well")
-    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops", "prefill", "decode_step", "tp_allreduce"],
+    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops", "prefill", "decode_step", "tp_allreduce", "engine_decode"],
                     help="compress (default, the headline op), decode (paged decode attention kernel) or "
                          "step_ops (the element-wise ops of a decoder layer step and the sampler) or "
                          "prefill (varlen causal prefill attention, one layer) or decode_step (the decode "
@@ -360,7 +364,7 @@ def run_decode(args):
     }))
 
 
-def run_decode_step(args):
+def decode_step_record(args, own_group=True):
     """The decode forward of Qwen3-8B-shaped decoder blocks (hidden 4096, 32 q / 8 kv heads of 128,
     MLP 12288, bf16, random weights; cuBLAS projections, everything else this library's kernels)
     over compressed tables (context 2049..2304 tokens in 9 pages), timed launch by launch and as
@@ -383,7 +387,8 @@ def run_decode_step(args):
     if world > 1:
         import torch.distributed as dist
         from zipage_b200.layers.tp_comm import LibraryCommunicator, TPCommunicator
-        dist.init_process_group("nccl", device_id=dev)
+        if own_group:
+            dist.init_process_group("nccl", device_id=dev)
         rank = dist.get_rank()
         comm = TPCommunicator(max_bytes=min(args.batch, 256) * 4096 * 2, timeout_ms=2000)
         lib_comm = LibraryCommunicator()
@@ -488,13 +493,50 @@ def run_decode_step(args):
         peaks = json.loads(pk.read_text())
     hbm_peak = peaks.get("hbm_gbs", 6650.0)
     ach = (wbytes + kvbytes) / (ms_graph * 1e-3) / 1e9
+    # One compression of every sequence per 256 decode steps (a page fills, the table is back at
+    # budget + 1 pages): timed on this step's own caches through the host-facing call and folded
+    # into the rate the way the engine's generate() accounts decode throughput
+    # (zipage/engine/zipage_engine.py:255-265: tokens of the decode steps over the time between them).
+    from zipage_b200.engine.compressor import Compressor
+    qc.normal_()
+    ccomp = Compressor(kv, qc, None, make_cfg("lightning", False), layer_stride=8)
+    c_tables = table.tolist()
+    c_qids = qid.tolist()
+    c_ms = []
+    for i in range(3):
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        ccomp.compress_tables(c_tables, c_tables, c_qids, [True] * B)
+        c_ms.append((time.perf_counter() - t0) * 1e3)
+    compress_ms = min(c_ms[1:])
     if world > 1:
+        t = torch.tensor([compress_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        compress_ms = float(t.item())
+    tok_s_with_compress = 256.0 * B / (256.0 * ms_e2e + compress_ms) * 1e3
+    allreduce_bit_exact = None
+    if world > 1:
+        # the peer-memory all-reduce against the fp32 sum of the gathered inputs taken in rank order
+        xg = torch.Generator(device=dev).manual_seed(100 + rank)
+        x = torch.randn(B, 4096, device=dev, generator=xg).to(torch.bfloat16)
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x)
+        acc = parts[0].float()
+        for p_ in parts[1:]:
+            acc = acc + p_.float()
+        got = comm.all_reduce(x.clone())
+        flag = torch.tensor([int(torch.equal(got, acc.to(torch.bfloat16)))], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        allreduce_bit_exact = bool(flag.item())
         status = comm.status()
         comm.close()
-        dist.destroy_process_group()
+        if own_group:
+            dist.destroy_process_group()
         if rank != 0:
-            return
-    print(json.dumps({
+            return None
+    return ({
         "metric": "decode_step_tokens_per_s", "value": B / (ms_graph * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_graph, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -511,7 +553,65 @@ def run_decode_step(args):
         "roofline": {"bound": "hbm", "kernel": "whole step (this rank's weights + K/V read once)", "achieved": ach,
                      "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
                      "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback", "traffic": None},
-    }))
+        "compress_ms_per_256_steps": compress_ms,
+        "tokens_per_s_with_compression": tok_s_with_compress,
+        "all_reduce_bit_exact_vs_fp32_rank_order_sum": allreduce_bit_exact,
+    })
+
+
+def engine_decode_records(modes=("reference", "kernels", "graph"), requests=192, max_tokens=600):
+    """Decode tokens/s through the reference ENGINE (ZipLLM.generate of baseline/_ref: its scheduler,
+    block manager, prefill and sampler) on a synthetic Qwen3-8B-shaped model, 2300-token random
+    prompts, a budget of 8 pages, lightning redundancy + pooling, two compressions per request:
+    `reference` = the engine as it is (Triton + flash-attn), `kernels` = zipage_b200.kernel bound in
+    model_runner.py, `graph` = also the attention layer and the decode forward as replayed CUDA
+    graphs.  Each mode is a child process (tests/ref_engine.py); accounting is the engine's own
+    time_record (decode_sum + compress_sum)."""
+    out = {"workload": f"Qwen3-8B shapes, random-init bf16, {requests} concurrent requests, prompts of 2300 "
+                       f"uniform-random ids, {max_tokens} generated tokens each, budget 8 x 256, temperature 0.6"}
+    if not (ROOT / "baseline" / "_ref" / "zipage" / "llm.py").is_file():
+        out["unavailable"] = "the reference is not installed under baseline/_ref"
+        return out
+    common = ["--layers", "36", "--hidden", "4096", "--inter", "12288", "--hq", "32", "--hkv", "8", "--vocab", "151936",
+              "--requests", str(requests), "--prompt-len", "2300", "--max-tokens", str(max_tokens), "--budget", "8",
+              "--qcl", "32", "--lightning", "--pooling", "--max-model-len", "4096", "--model-dir", "/tmp/zp_q8b",
+              "--gpu-mem", "0.62", "--warmup-requests", "4"]
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT")}
+    for i, m in enumerate(modes):
+        res = Path("/tmp") / f"zp_engine_{m}.json"
+        try:
+            r = subprocess.run([sys.executable, str(ROOT / "tests" / "ref_engine.py"), "--mode", m, "--out", str(res),
+                                "--port", str(2411 + i), *common], capture_output=True, text=True, timeout=900, env=env)
+            if r.returncode != 0:
+                out[m] = {"unavailable": (r.stderr or r.stdout)[-300:]}
+                continue
+            d = json.loads(res.read_text())
+            e = d["engine_time_record"]
+            out[m] = {"decode_tokens_per_s": d["decode_tok_per_s"],
+                      "decode_tokens_per_s_excluding_compress": d["decode_tok_per_s_excluding_compress"],
+                      "prefill_tokens_per_s": d["prefill_tok_per_s"], "decode_s": e.get("decode_sum"),
+                      "compress_s": e.get("compress_sum"), "decode_tokens": d["decode_tokens"]}
+        except Exception as ex:
+            out[m] = {"unavailable": f"{type(ex).__name__}: {ex}"[:300]}
+    ref = out.get("reference", {}).get("decode_tokens_per_s")
+    for m in modes[1:]:
+        if ref and out.get(m, {}).get("decode_tokens_per_s"):
+            out[m]["vs_reference_engine"] = out[m]["decode_tokens_per_s"] / ref
+    return out
+
+
+def run_engine_decode(args):
+    rec = engine_decode_records()
+    g = rec.get("graph", {})
+    print(json.dumps({"metric": "engine_decode_tokens_per_s", "value": g.get("decode_tokens_per_s"), "unit": "tokens/s",
+                      "n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "config": {"workload": rec["workload"]},
+                      "modes": rec}))
+
+
+def run_decode_step(args):
+    rec = decode_step_record(args, own_group=True)
+    if rec is not None:
+        print(json.dumps(rec))
 
 
 def run_tp_allreduce(args):
@@ -783,6 +883,8 @@ def main():
         return run_decode_step(args)
     if args.workload == "tp_allreduce":
         return run_tp_allreduce(args)
+    if args.workload == "engine_decode":
+        return run_engine_decode(args)
 
     import torch
     import torch.distributed as dist
@@ -986,6 +1088,25 @@ def main():
                  if red_ms else None}
         del xcomp
 
+    # The other half of the metric: decode tokens/s at the 2048-token budget.  The compression
+    # workload is released first; the decode step (full depth, tensor-parallel over the ranks
+    # when there are several) then runs in this same process and process group.
+    decode = None
+    if not args.no_decode:
+        del w, comp, fresh, last_pages
+        small = xcomp = None
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        from types import SimpleNamespace
+        d_args = SimpleNamespace(**vars(args))
+        d_args.batch, d_args.layers = 256, 36
+        d_args.steps, d_args.warmup = max(args.steps, 10), max(args.warmup, 3)
+        try:
+            decode = decode_step_record(d_args, own_group=False)
+        except Exception as e:   # the headline line must still come out
+            decode = {"unavailable": f"{type(e).__name__}: {e}"[:300]} if rank == 0 else None
+
     if rank == 0:
         peaks = {}
         pk = ROOT / "MEASURED_PEAKS.json"
@@ -1063,6 +1184,10 @@ def main():
             "clocks": clocks.summary(),
             "roofline": roofline,
         }
+        if decode is not None:
+            line["decode"] = decode
+        if args.engine and world == 1:
+            line["engine_decode"] = engine_decode_records()
         if eng is not None:
             line["e2e_engine_call_shape"] = eng
         if exact is not None:

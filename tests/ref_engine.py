@@ -8,6 +8,12 @@ Modes
   kernels    zipage/engine/model_runner.py:19-27 import the compression kernels from zipage_b200.kernel
   full       `kernels` + the Attention layer (cache stores, prefill and decode attention) from
              zipage_b200.layers.attention, sharing the reference's Context module
+  steps      `full` + RMSNorm and SiluAndMul of the decoder blocks from zipage_b200.layers.step_ops
+              in place of the reference's torch.compile'd modules
+  graph      `full` + the decode step as replayed CUDA graphs: the
+             reference's scheduler, block manager, prefill, LM head and sampler stay; its decode
+             forward (ModelRunner.run for decode batches) goes through DecodeGraphRunner over
+             zipage_b200's Qwen3 blocks, which share the reference model's parameters and caches
 
 There is no tokenizer or checkpoint offline, so the model directory is synthesised: a Qwen3
 config.json, a word-level stub tokenizer (the engine only reads its eos / pad ids and decodes the
@@ -119,19 +125,80 @@ def bind(mode):
     for n in ["compress_kv", "compress_score", "attention_score", "raw_redudancy_score",
               "lightning_redudancy_score", "global_score", "window_mask", "topk_mask"]:
         setattr(mr, n, getattr(K, n))
-    if mode == "full":
+    if mode in ("full", "steps", "graph"):
         import zipage.layers.attention as ref_att
         import zipage.models.qwen3 as ref_qwen3
         import zipage.utils.context as ref_ctx
         import zipage_b200.layers.attention as our_att
-        our_att.get_context = ref_ctx.get_context      # the runner and the layer share one Context
+        # The runner and the layer share one Context.  The reference runner fills the reference's
+        # module; the graph runner of mode `graph` fills this library's: whichever holds a step.
+        import zipage_b200.utils.context as our_ctx
+
+        def shared_context():
+            c = our_ctx.get_context()
+            if c.is_prefill or c.context_lens is not None or c.slot_mapping is not None:
+                return c
+            return ref_ctx.get_context()
+        our_att.get_context = shared_context
         ref_qwen3.Attention = our_att.Attention
         ref_att.Attention = our_att.Attention
+    if mode == "steps":
+        import zipage.models.qwen3 as ref_qwen3
+        from zipage_b200.layers import step_ops
+        ref_qwen3.RMSNorm = step_ops.RMSNorm
+        ref_qwen3.SiluAndMul = step_ops.SiluAndMul
+
+
+def bind_graph_decode(llm, max_bs, max_model_len, qcl):
+    """ModelRunner.run for decode batches through DecodeGraphRunner (the reference's own graph
+    branch, zipage/engine/model_runner.py:709-724, raises ValueError).  The blocks are
+    zipage_b200.layers.qwen3_block.Qwen3Model with the reference model's parameter tensors (no
+    copy) and the runner's caches."""
+    import torch
+    import zipage.engine.model_runner as mr
+    from zipage_b200.engine.decode_graph import DecodeGraphRunner
+    from zipage_b200.layers.qwen3_block import Qwen3Model
+    runner = llm.model_runner
+    hf = runner.config.hf_config
+    inner = runner.model.model
+    with torch.device("meta"):
+        ours = Qwen3Model(hf)
+    for name, p in inner.named_parameters():
+        mod = ours
+        *path, attr = name.split(".")
+        for part in path:
+            mod = getattr(mod, part)
+        setattr(mod, attr, p)
+    ours.eval()
+    ours.bind_caches(runner.kv_cache, runner.query_cache)
+    with torch.cuda.stream(runner.run_stream):
+        dg = DecodeGraphRunner(ours, hf.hidden_size, max_bs=max_bs,
+                               max_num_blocks=(max_model_len + 255) // 256 + 1, query_cache_len=qcl,
+                               device="cuda")
+        dg.capture()
+    torch.cuda.synchronize()
+    orig_run = mr.ModelRunner.run
+
+    def run(self, seqs, is_prefill):
+        if is_prefill or len(seqs) > max_bs:
+            return orig_run(self, seqs, is_prefill)
+        with torch.cuda.stream(self.run_stream), torch.inference_mode():
+            pin = lambda data, dt: torch.tensor(data, dtype=dt, pin_memory=True).cuda(non_blocking=True)
+            ids = pin([s.last_token for s in seqs], torch.int64)
+            ntok = pin([len(s) for s in seqs], torch.int32)
+            qids = pin([s.query_id for s in seqs], torch.int32)
+            tables = self.prepare_block_tables(seqs)
+            past, temps = self.prepare_sample(seqs)
+            hidden = dg.run(ids, ntok, tables, qids)
+            logits = self.model.compute_logits(hidden)
+            return self.sampler(logits, temps, past).tolist()
+    mr.ModelRunner.run = run
+    return dg
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="reference", choices=["reference", "kernels", "full"])
+    ap.add_argument("--mode", default="reference", choices=["reference", "kernels", "full", "steps", "graph"])
     ap.add_argument("--out", required=True)
     ap.add_argument("--model-dir", default="/tmp/zp_synth_model")
     ap.add_argument("--layers", type=int, default=4)
@@ -160,6 +227,9 @@ def main():
     ap.add_argument("--max-model-len", type=int, default=8192)
     ap.add_argument("--port", type=int, default=2391)
     ap.add_argument("--gpu-mem", type=float, default=0.85)
+    ap.add_argument("--warmup-requests", type=int, default=0,
+                    help="an untimed generate() of that many requests first (Triton / Inductor compile, "
+                         "allocator warm-up); the time records are cleared after it")
     args = ap.parse_args()
 
     sys.path.insert(0, str(ROOT))
@@ -201,6 +271,9 @@ def main():
                  use_redudancy=args.lightning or args.exact, lightning_redudancy=args.lightning,
                  redudancy_lambda=0.5, use_global_score=args.global_score, enable_pooling=args.pooling,
                  enable_async_compress=args.async_compress, enable_prefix_cache=args.prefix_cache)
+    if args.mode == "graph":
+        bind_graph_decode(llm, min(args.max_num_seqs, max(args.requests, args.warmup_requests, 16)),
+                          args.max_model_len, args.qcl)
     g = torch.Generator().manual_seed(args.seed + 1)
     prompts = []
     for _ in range(args.requests):
@@ -208,6 +281,14 @@ def main():
             int(torch.randint(args.prompt_len, args.prompt_len_max + 1, (1,), generator=g))
         prompts.append(torch.randint(2, args.vocab, (n,), generator=g).tolist())
     sp = SamplingParams(temperature=args.temperature, max_tokens=args.max_tokens, ignore_eos=True)
+    if args.warmup_requests > 0:
+        # long enough to cross one compression: prompt of budget+1 full pages minus a few tokens
+        wl = (args.budget + 1) * 256 - 4
+        wp = [torch.randint(2, args.vocab, (wl,), generator=g).tolist() for _ in range(args.warmup_requests)]
+        llm.generate(wp, SamplingParams(temperature=args.temperature, max_tokens=8, ignore_eos=True), use_tqdm=True)
+        llm.time_record.clear()
+        llm.model_runner.time_record.clear()
+        steps.clear()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     outs = llm.generate(prompts, sp, use_tqdm=True)
