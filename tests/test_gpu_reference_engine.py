@@ -7,13 +7,15 @@ an exponential race that no two implementations reproduce, and its SamplingParam
 temperature 0):
   reference  as it is (Triton kernels, flash-attn), free running;
   kernels    with zipage_b200.kernel bound at the import sites of model_runner.py;
-  full       with the Attention layer (cache stores, prefill and decode attention) bound as well.
+  full       with the Attention layer (cache stores, prefill and decode attention) bound as well;
+  graph      with, on top of that, the decode forward replayed as CUDA graphs over this library's
+             decoder blocks (device-built step state, fused q/k norm + rope + cache stores).
 A random-init model has near-flat logits, so two correct bf16 implementations that differ in the
 last bit of one attention output — or that keep a different one of two keys tied at the top-k cut
 — diverge for good at the first near-tie of the arg-max; a free-running comparison then says
 nothing about the steps after it.  The bound runs are therefore teacher-forced on the reference's
 tokens (same caches, same positions, same compressions at the same steps) while their own arg-max
-is recorded at every step.  Checked for both bound runs:
+is recorded at every step.  Checked for every bound run:
   * the own arg-max equals the reference's token at EVERY step whose top-2 logit margin (in the
     reference run) exceeds 2e-2 of the logit spread — the bf16 tolerance of the path;
   * the number of steps below that margin, the number of differing tokens and the length of the
@@ -92,3 +94,5 @@ def test_greedy_256_steps_through_the_reference_engine(tmp_path):
     assert min(prefix) >= 169
     full = _run("full", tmp_path / "full.json", forced)
     compare(full, "compression kernels and attention layer bound")
+    graph = _run("graph", tmp_path / "graph.json", forced)
+    compare(graph, "decode step as CUDA graphs over this library's blocks")
