@@ -218,7 +218,8 @@ int zp_update_tables(const int32_t* target_table, int32_t* new_table, int32_t* c
 /* Replaces flash_attn_with_kvcache as called at zipage/layers/attention.py:95-103: one query token
  * per sequence over its paged K/V.  q,out [B, Hq, D]; caches [P, BS, Hkv, D] (page stride given);
  * cache_seqlens [B]; block_table [B, NBmax] (-1 padded).  Scratch from
- * zp_paged_decode_workspace_bytes. */
+ * zp_paged_decode_workspace_bytes.  With too little scratch for the split-KV form the call still
+ * succeeds, runs one block per (sequence, kv head) and leaves a note in zp_last_error. */
 size_t zp_paged_decode_workspace_bytes(int B, int Hq, int D, int max_splits);
 int zp_paged_decode(const void* q, const void* k_cache, const void* v_cache,
                     const int32_t* cache_seqlens, const int32_t* block_table, void* out, int B,

@@ -64,6 +64,13 @@ def test_noalloc_decode_matches_workspace_decode_twice():
         assert rc == 0, lib.zp_last_error()
         # same kernels and same split choice as the workspace entry point: identical bits
         assert torch.equal(new, refs[idx])
+        # and directly against the CPU oracle's softmax attention, within the tolerance the decode
+        # tests use (2e-2 of the largest output for bf16, 1e-3 for fp32)
+        from oracle import zipage_oracle as O
+        q, kc, vc, lens, table = (t.cpu() for t in cases[idx])
+        want = O.paged_decode_attention(q.unsqueeze(1), kc, vc, lens, table).squeeze(1).float()
+        tol = 1e-3 if q.dtype == torch.float32 else 2e-2
+        assert (new.cpu().float() - want).abs().max() <= tol * want.abs().max()
 
 
 def test_noalloc_decode_rejects_batches_beyond_the_builtin_scratch():

@@ -245,7 +245,13 @@ extern "C" int zp_paged_decode(const void* q, const void* k_cache, const void* v
   a.part = nullptr;
   if (a.nsplit > 1) {
     const size_t need = (size_t)B * Hkv * a.nsplit * zp::gp_of(G) * (D + 2) * sizeof(float);
-    if (!workspace || workspace_bytes < need) a.nsplit = 1;  // no scratch: run unsplit
+    if (!workspace || workspace_bytes < need) {
+      // no scratch: run unsplit (correct, but one block per (sequence, kv head) leaves a small
+      // batch on a few SMs); the call succeeds and the message says what happened
+      zp::set_error("zp_paged_decode: workspace of %zu bytes, %zu needed for %d splits: running unsplit",
+                    workspace_bytes, need, a.nsplit);
+      a.nsplit = 1;
+    }
     else a.part = reinterpret_cast<float*>(workspace);
   }
   cudaStream_t st = (cudaStream_t)stream;
