@@ -50,7 +50,7 @@ def parse_args():
                     help="also run the reference ENGINE (baseline/_ref) on a synthetic Qwen3-8B-shaped model, as it "
                          "is and with this library's decode path bound, and report decode tokens/s (adds minutes)")
     ap.add_argument("--also-exact", action="store_true", help="time the exact variant as well")
-    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops", "prefill", "decode_step", "tp_allreduce", "engine_decode"],
+    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops", "prefill", "decode_step", "tp_allreduce", "engine_decode", "long_prompt"],
                     help="compress (default, the headline op), decode (paged decode attention kernel) or "
                          "step_ops (the element-wise ops of a decoder layer step and the sampler) or "
                          "prefill (varlen causal prefill attention, one layer) or decode_step (the decode "
@@ -608,6 +608,74 @@ def run_engine_decode(args):
                       "modes": rec}))
 
 
+def run_long_prompt(args):
+    """First compression after a long prompt (config 5): Qwen3-32B attention shapes as ONE rank of a
+    TP=8 job sees them (64 layers, 8 query heads and 1 KV head of 128 per rank), `--batch` sequences
+    whose tables hold 64..128 full pages (16k..32k tokens) compressed into 8 (+1) pages, bf16, window
+    32 (G*QCL = 256 window rows: two passes of the window kernel), lightning and exact similarity;
+    and the varlen prefill attention of one 32 768-token prompt at the same per-rank head counts."""
+    import torch
+    from zipage_b200 import kernel as K
+    from zipage_b200.compress import CompressConfig, compress_chunk
+    from zipage_b200.engine.compressor import Compressor
+    from zipage_b200.layers.attention import varlen_prefill_attention
+    from zipage_b200.synthetic import make_compress_workload
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, L, hkv, hq = min(args.batch, 64), 64, 1, 8
+    g = torch.Generator().manual_seed(17)
+    pages = torch.randint(64, 129, (B,), generator=g).tolist()
+    pages[0], pages[1] = 128, 64
+    w = make_compress_workload(B, L, hkv, hq, D, QCL, BUDGET, pages_per_seq=pages, dtype=torch.bfloat16,
+                               device=dev, seed=5, compressed_prob=0.0, fresh_target_prob=0.5)
+    out = {}
+    chunk = 8   # layer_stride of the engine
+    for variant in ("lightning", "exact"):
+        cfg = make_cfg(variant, False)
+        comp = Compressor(w.kv_cache, w.query_cache, None, cfg, layer_stride=chunk)
+        tables = [[int(x) for x in row if x != -1] for row in w.tables_plain.cpu().tolist()]
+        targets = w.target_tables.cpu().tolist()
+        ts = None
+        for it in range(2):   # the compaction is in place: the second pass recompresses (same shapes, same work)
+            comp.time_record.clear()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            comp.compress_tables(tables, targets, w.query_ids.cpu().tolist(), [False] * B, timed=True)
+            wall = time.perf_counter() - t0
+            ts = {k: v * 1e3 for k, v in comp.time_record.items() if k.endswith("_sum")}
+        tok = sum(pages) * BS
+        flops = sum(2.0 * (p_ * BS) ** 2 * D for p_ in pages) * L * hkv
+        out[variant] = {"ms": sum(ts.values()), "wall_ms": wall * 1e3, "stage_ms": ts,
+                        "tokens_scored_per_s": tok * L / (sum(ts.values()) * 1e-3)}
+        if variant == "exact":
+            out[variant]["similarity_tflops_dense_count"] = flops / (ts["redudancy_score_sum"] * 1e-3) / 1e12
+        del comp
+    # prefill attention of one 32k prompt at the per-rank head counts
+    S = 32768
+    q = torch.randn(S, hq, D, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(S, hkv, D, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(S, hkv, D, device=dev, dtype=torch.bfloat16)
+    cu = torch.tensor([0, S], device=dev, dtype=torch.int32)
+    fn = lambda: varlen_prefill_attention(q, k, v, S, cu, S, cu, impl="tcgen05")
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    out["prefill_1x32768_8q_1kv"] = {"ms": ms, "tflops": 4.0 * D * (S * S / 2.0) * hq / (ms * 1e-3) / 1e12}
+    print(json.dumps({
+        "metric": "first_compression_ms", "value": out["lightning"]["ms"], "unit": "ms", "n_gpus": 1,
+        "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "first compression of long prompts, one TP=8 rank of Qwen3-32B (config 5)",
+                   "sequences": B, "layers": L, "pages_per_seq": "64..128", "kv_heads_per_rank": hkv,
+                   "q_heads_per_rank": hq, "window": QCL, "total_pages": sum(pages)},
+        "results": out}))
+
+
 def run_decode_step(args):
     rec = decode_step_record(args, own_group=True)
     if rec is not None:
@@ -885,6 +953,8 @@ def main():
         return run_tp_allreduce(args)
     if args.workload == "engine_decode":
         return run_engine_decode(args)
+    if args.workload == "long_prompt":
+        return run_long_prompt(args)
 
     import torch
     import torch.distributed as dist

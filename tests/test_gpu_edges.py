@@ -127,6 +127,60 @@ def test_oversized_row_is_rejected_cleanly():
         K.topk_mask(scores, 8 * BS)
 
 
+def test_config5_first_compression_from_128_and_64_pages():
+    """The long-prompt case at its own scale: tables of 128 and 64 full pages (32k / 16k tokens)
+    compressed into 8 (+1), one KV head with 8 query heads (a TP=8 rank of Qwen3-32B), window 32
+    (256 window rows: two passes of the tensor-core window kernel), bf16, lightning redundancy."""
+    from oracle.boundary import kept_set_report
+    from zipage_b200 import _lib
+    from zipage_b200.synthetic import make_compress_workload
+    dev = torch.device("cuda:0")
+    w = make_compress_workload(B=2, L=1, Hkv=1, Hq=8, QCL=32, budget=8, pages_per_seq=[128, 64],
+                               dtype=torch.bfloat16, device=dev, seed=9, compressed_prob=0.0,
+                               fresh_target_prob=1.0)
+    cfg = dict(budget_blocks=8, query_cache_len=32, use_redudancy=True, lightning_redudancy=True,
+               redudancy_lambda=0.5, enable_pooling=True)
+    (final_o, keep_o, ko, vo), dbg = _run_both(w, cfg, torch.bfloat16)
+    assert _lib.device_error() == 0
+    keep = dbg["keep"].cpu()
+    assert (keep.flatten(3).sum(-1) == 8 * BS).all()
+    rep = kept_set_report(final_o.reshape(1, 2, 1, -1), keep_o.reshape(1, 2, 1, -1), keep.reshape(1, 2, 1, -1),
+                          8 * BS, torch.bfloat16, dbg["oracle_parts"])
+    print(f"128 / 64 pages -> 8: {rep}")
+    assert rep["outside"] == 0 and rep["mismatch"] < 1e-3, rep
+
+
+def test_select_rows_too_long_for_two_arrays_recompute_the_redundancy():
+    """A row of 240 pages in bf16 with redundancy needs 2 x 120 KB of shared memory for scores and
+    scaled logits; the kernel then keeps only the scores there and recomputes the logits per pass.
+    Same kept set as the oracle's selection on the same scores."""
+    from oracle import zipage_oracle as O
+    from zipage_b200 import kernel as K
+    dev = torch.device("cuda:0")
+    NB = 240
+    g = torch.Generator().manual_seed(2)
+    scores = (torch.rand(1, 1, 2, NB, BS, generator=g) / (NB * BS)).to(torch.bfloat16)
+    red = torch.randn(1, 1, 2, NB, BS, generator=g).to(torch.bfloat16)
+    table = torch.arange(NB, dtype=torch.int32).view(1, NB)
+    table[0, -1] = -table[0, -1] - 2
+    comp = torch.zeros(1, dtype=torch.bool)
+    keep, final = K.select_keep(scores.to(dev), table.to(dev), comp.to(dev), 8 * BS, 16, red_logits=red.to(dev),
+                                redundancy="lightning", redudancy_lambda=0.5, redudancy_temperature=0.4,
+                                pooling_size=5, return_final=True)
+    s = O.pool_scores(scores.clone(), comp, 5, False)
+    r = red.view(1, 1, 2, -1).clone()
+    r = r.div_(0.4 * BS)
+    r = (r - r.max(dim=-1, keepdim=True).values).softmax(dim=-1).view(1, 1, 2, NB, BS)
+    f = O.combine_scores(s, r, 0.5).contiguous()
+    O.window_mask(f, table, 16)
+    O.pad_mask_(f, table)
+    fin = torch.isfinite(f.float())
+    assert torch.equal(final.cpu().float()[~fin], f.float()[~fin])
+    assert (final.cpu().float()[fin] - f.float()[fin]).abs().max() <= 2e-2 * f.float()[fin].abs().max()
+    want = O.topk_mask(final.cpu().view(1, 1, 2, -1), 8 * BS)
+    assert torch.equal(keep.cpu().view(1, 1, 2, -1), want)
+
+
 @pytest.mark.parametrize("variant", ["lightning", "exact", "none"])
 def test_single_entry_point_equals_stage_by_stage(variant):
     """zp_compress_batch (one C call) leaves the caches exactly as the stage-by-stage path does."""
@@ -149,3 +203,22 @@ def test_single_entry_point_equals_stage_by_stage(variant):
     assert torch.equal(a.kv_cache, b.kv_cache) and torch.equal(a.score_cache, b.score_cache)
     assert torch.equal(new_table, b.target_tables) and ctx.tolist() == [2 * BS + 1] * 3
     assert nxt.tolist() == (b.target_tables[:, -1] * BS).tolist()
+
+
+def test_exact_similarity_on_tables_longer_than_64_pages():
+    """The tensor-core kernel of the exact similarity walks tables of any length (the long-prompt
+    case: 64..128 pages); checked against the portable kernel, which the oracle pins, on a ragged
+    pair of 70 and 66 pages with padding inside the rectangle."""
+    from zipage_b200 import _lib, kernel as K
+    from zipage_b200.synthetic import make_compress_workload
+    dev = torch.device("cuda:0")
+    w = make_compress_workload(B=2, L=1, Hkv=2, Hq=8, QCL=16, budget=8, pages_per_seq=[70, 66],
+                               dtype=torch.bfloat16, device=dev, seed=13, compressed_prob=0.0, similar_keys=True)
+    a = K.redundancy_logits(w.kv_cache[0], w.block_tables, 0.5, exact=True, impl="tcgen05").float()
+    b = K.redundancy_logits(w.kv_cache[0], w.block_tables, 0.5, exact=True, impl="simt").float()
+    torch.cuda.synchronize()
+    assert _lib.device_error() == 0
+    fin = torch.isfinite(b)
+    assert torch.equal(torch.isfinite(a), fin)
+    assert (a[fin] - b[fin]).abs().max() <= 2e-2 * b[fin].abs().max()
+    assert (a[fin] != b[fin]).float().mean() < 0.05

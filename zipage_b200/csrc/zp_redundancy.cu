@@ -364,13 +364,6 @@ extern "C" int zp_redundancy_exact(const void* k_cache, const int32_t* block_tab
   float* stats = rowsum + n;
   int tc = zp::pick_tc(impl, dtype, D, BS, "zp_redundancy_exact");
   if (tc < 0) return tc;
-  if (tc && NB > 64) {  // the tcgen05 kernel keeps a 64-bit mask of valid pages
-    if (impl == ZP_IMPL_TCGEN05) {
-      zp::set_error("zp_redundancy_exact: the tcgen05 kernel handles at most 64 pages per sequence");
-      return ZP_ERR_UNSUPPORTED;
-    }
-    tc = 0;
-  }
   // zeroed: the subtrahends and, for the tcgen05 kernel, the latest-similar-key records
   cudaError_t e = cudaMemsetAsync(sub, 0, (tc ? 2 : 1) * n * sizeof(long long), st);
   if (e != cudaSuccess) { zp::set_error("zp_redundancy_exact: %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }

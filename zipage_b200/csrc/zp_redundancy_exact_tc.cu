@@ -390,8 +390,6 @@ redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmK, const XtPara
       const int unit = job / p.NB, mp = job - unit * p.NB;
       const int32_t* table = p.block_table + (int64_t)((unit / p.Hkv) % p.B) * p.NB;
       if (table[mp] == -1) continue;
-      uint64_t vmask = 0;   // valid column pages
-      for (int pg = mp; pg < p.NB; ++pg) vmask |= (uint64_t)(table[pg] != -1) << pg;
       const int64_t rbase = (int64_t)job * 256;   // = (unit * NB + row page) * 256
       // smallest |k| of this thread's four 32-column chunks, fetched one page ahead
       const float4* nmp = reinterpret_cast<const float4*>(p.nmin + ((int64_t)unit * p.NB) * 8) + ch;
@@ -407,7 +405,7 @@ redundancy_exact_tc_kernel(const __grid_constant__ CUtensorMap tmK, const XtPara
       const float thr_m = p.threshold / rn_m;
       const unsigned m_key = mp * 256 + g * 128 + r;
       for (int pg = mp; ok && pg < p.NB; ++pg) {
-        if (!((vmask >> pg) & 1)) continue;
+        if (table[pg] == -1) continue;   // padding (the entry is in L1: every role walks this row)
         const float4 nm4 = nm_next;
         nm_next = __ldg(nmp + min(pg + 1, p.NB - 1) * 2);
         const bool diag_page = pg == mp;

@@ -27,12 +27,16 @@ struct SelArgs {
   zp_select_params sp;
 };
 
-template <typename T>
+// RED_SMEM: the scaled redundancy logits of the row are staged in shared memory ([N] more
+// elements).  Without it they are recomputed from global memory in each of the three passes that
+// need them (same arithmetic, same rounding points), which halves the shared memory a row needs:
+// the form used for tables too long for both arrays.
+template <typename T, bool RED_SMEM>
 __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const SelArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int N = a.NB * a.BS;
   T* sS = reinterpret_cast<T*>(smem_raw);       // [N] scores -> final
-  T* sR = sS + N;                               // [N] redundancy (only if used)
+  T* sR = sS + N;                               // [N] redundancy (only if staged)
   __shared__ float red[32];
   __shared__ int hist[256];
   __shared__ int warp_tot[SEL_THREADS / 32];
@@ -75,25 +79,24 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const SelArgs a) {
     const T* gR = reinterpret_cast<const T*>(a.red) + (int64_t)unit * N;
     const float divisor = a.sp.redundancy_temperature *
                           (float)(a.sp.use_redundancy == 2 ? sh_nvalid * a.BS : a.BS);
+    // scaled logit of token i: from shared memory when staged, else recomputed
+    auto scaled = [&](int i) -> float {
+      return RED_SMEM ? Elem<T>::to_f32(sR[i]) : round_to<T>(Elem<T>::to_f32(gR[i]) / divisor);
+    };
     float m = -INFINITY;
     for (int i = tid; i < N; i += SEL_THREADS) {
       const float v = round_to<T>(Elem<T>::to_f32(gR[i]) / divisor);
-      sR[i] = Elem<T>::from_f32(v);
+      if (RED_SMEM) sR[i] = Elem<T>::from_f32(v);
       m = fmaxf(m, v);
     }
     m = block_max(m, red);
     float z = 0.f;
-    for (int i = tid; i < N; i += SEL_THREADS) z += expf(round_to<T>(Elem<T>::to_f32(sR[i]) - m));
+    for (int i = tid; i < N; i += SEL_THREADS) z += expf(round_to<T>(scaled(i) - m));
     z = block_sum(z, red);
-    float pm = 0.f;
+    // the largest probability belongs to the largest logit: exp(0) / z
+    const float pm = round_to<T>(1.0f / z);
     for (int i = tid; i < N; i += SEL_THREADS) {
-      const float pr = round_to<T>(expf(round_to<T>(Elem<T>::to_f32(sR[i]) - m)) / z);
-      sR[i] = Elem<T>::from_f32(pr);
-      pm = fmaxf(pm, pr);
-    }
-    if (a.sp.redundancy_max_norm) pm = block_max(pm, red);
-    for (int i = tid; i < N; i += SEL_THREADS) {
-      float pr = Elem<T>::to_f32(sR[i]);
+      float pr = round_to<T>(expf(round_to<T>(scaled(i) - m)) / z);
       if (a.sp.redundancy_max_norm) pr = round_to<T>(pr / pm);
       const float x = round_to<T>(Elem<T>::to_f32(sS[i]) * a.sp.redundancy_lambda);
       const float y = round_to<T>(pr * a.sp.redundancy_one_minus_lambda);
@@ -208,7 +211,12 @@ extern "C" int zp_select(const void* scores, const void* red_logits, const int32
   ZP_REQUIRE(params->query_cache_len >= 0 && params->query_cache_len <= BS,
              "zp_select: bad query_cache_len");
   const int N = NB * BS;
-  const size_t smem = (size_t)N * zp::dtype_size(dtype) * (params->use_redundancy ? 2 : 1);
+  // A row lives in shared memory: N scores, plus N scaled redundancy logits when they fit as well
+  // (else they are recomputed per pass).  200 KB hold 102 400 16-bit or 51 200 fp32 scores:
+  // tables of up to 400 / 200 pages of 256 tokens.
+  const size_t row = (size_t)N * zp::dtype_size(dtype);
+  const bool red_smem = params->use_redundancy && 2 * row <= 200 * 1024;
+  const size_t smem = red_smem ? 2 * row : row;
   if (smem > 200 * 1024) {
     zp::set_error("zp_select: %d tokens per row need %zu bytes of shared memory (max 204800)", N, smem);
     return ZP_ERR_UNSUPPORTED;
@@ -218,7 +226,7 @@ extern "C" int zp_select(const void* scores, const void* red_logits, const int32
   a.keep = keep_out; a.final_out = final_out;
   a.L = L; a.B = B; a.NB = NB; a.Hkv = Hkv; a.BS = BS; a.sp = *params;
   ZP_DISPATCH_DTYPE(dtype, T, {
-    auto kern = zp::select_kernel<T>;
+    void (*kern)(const zp::SelArgs) = red_smem ? zp::select_kernel<T, true> : zp::select_kernel<T, false>;
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) { zp::set_error("zp_select: %s", cudaGetErrorString(e)); return ZP_ERR_CUDA; }
