@@ -12,10 +12,11 @@ out is copied verbatim next to the installed ones.  Nothing is edited.
 Only the GPU tests that compare this library with the reference's own Triton kernels and
 engine read baseline/_ref, and only when it is present.
 
-usage: python baseline/install_reference.py [reference source tree]
+usage: python baseline/install_reference.py <reference source tree>
 """
 from __future__ import annotations
 
+import os
 import shutil
 import subprocess
 import sys
@@ -49,4 +50,7 @@ def install(src: Path) -> None:
 
 
 if __name__ == "__main__":
-    install(Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    source = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ZIPAGE_REFERENCE_SRC")
+    if not source:
+        sys.exit("usage: python baseline/install_reference.py <reference source tree> (or set ZIPAGE_REFERENCE_SRC)")
+    install(Path(source))
