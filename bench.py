@@ -50,7 +50,7 @@ def parse_args():
                     help="also run the reference ENGINE (baseline/_ref) on a synthetic Qwen3-8B-shaped model, as it "
                          "is and with this library's decode path bound, and report decode tokens/s (adds minutes)")
     ap.add_argument("--also-exact", action="store_true", help="time the exact variant as well")
-    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops", "prefill", "decode_step", "tp_allreduce", "engine_decode", "long_prompt"],
+    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops", "prefill", "decode_step", "tp_allreduce", "engine_decode", "long_prompt", "host_control"],
                     help="compress (default, the headline op), decode (paged decode attention kernel) or "
                          "step_ops (the element-wise ops of a decoder layer step and the sampler) or "
                          "prefill (varlen causal prefill attention, one layer) or decode_step (the decode "
@@ -58,6 +58,7 @@ def parse_args():
                          "tp_allreduce (the row-parallel projections' all-reduce + residual + RMSNorm over "
                          "peer memory against the library collective; needs --gpus >= 2 under torchrun)")
     ap.add_argument("--verbose", action="store_true", help="progress lines on stderr")
+    ap.add_argument("--requests", type=int, default=2048, help="concurrent requests of the host_control workload")
     ap.add_argument("--tokens", type=int, default=32768, help="tokens per call of the step_ops workload")
     return ap.parse_args()
 
@@ -937,10 +938,114 @@ def run_prefill(args):
     }))
 
 
+def run_host_control(args):
+    """Host time per decode step of the control plane at `--requests` concurrent requests: the
+    native scheduler's array calls (schedule, the runner's input arrays, postprocess) and, when an
+    installed copy of the reference is present under baseline/_ref, the reference's Python
+    Scheduler.schedule() + postprocess() on the same request stream (its prepare_decode list
+    building, model_runner.py:633-675, is not included: it needs the GPU runner).  No GPU work."""
+    import random
+    import statistics
+    import types
+    import numpy as np
+    from zipage_b200.engine import scheduler as own
+    n = args.requests
+    cfg = types.SimpleNamespace(max_num_seqs=n, max_num_batched_tokens=1 << 22, eos=-1, num_kvcache_blocks=n * 12,
+                                kvcache_block_size=256, max_cache_blocks_per_seq=8, enable_prefix_cache=False,
+                                max_concurrency=n, enable_hybrid_engine=False, query_cache_len=32)
+    rng = random.Random(0)
+    prompts = [[rng.randrange(1000) for _ in range(600 + (i % 200))] for i in range(n)]
+    steps = 2200      # every sequence crosses 2304 tokens: first compressions are inside the window
+
+    def drive_own():
+        s = own.Scheduler(cfg)
+        for p in prompts:
+            s.add(own.Sequence(p, own.SamplingParams(0.6, 100000, True)))
+        out = {k: np.empty(n, np.int32) for k in ("input_ids", "num_tokens", "query_ids")}
+        out["block_tables"] = np.empty((n, 10), np.int32)
+        tok = np.ones(n, np.int32)
+        times, compressions = [], 0
+        while True:
+            h, pf = s.schedule_batch()
+            if not pf:
+                break
+            s.mark_prefilled(h)
+            s.postprocess_batch(h, tok[:len(h)])
+        first = True
+        for _ in range(steps):
+            t0 = time.perf_counter()
+            if not first:
+                h, pf = s.schedule_batch()
+            first = False
+            d = s.decode_inputs(h, table_width=10, out=out)
+            due = s.compress_due(h)
+            if len(due):
+                compressions += len(due)
+                s.compress_inputs(due, table_width=10)
+                s.postprocess_batch(due)
+            s.postprocess_batch(h, tok[:len(h)])
+            times.append(time.perf_counter() - t0)
+        return times, compressions
+
+    def drive_reference():
+        ref = ROOT / "baseline" / "_ref"
+        if not (ref / "zipage" / "engine" / "scheduler.py").exists():
+            return None
+        sys.path.insert(0, str(ref))
+        try:
+            from zipage.engine.scheduler import Scheduler
+            from zipage.engine.sequence import Sequence
+            from zipage.sampling_params import SamplingParams
+        except Exception:
+            return None
+        s = Scheduler(cfg)
+        for p in prompts:
+            s.add(Sequence(p, SamplingParams(temperature=0.6, max_tokens=100000, ignore_eos=True)))
+        while True:
+            seqs, pf = s.schedule()
+            if not pf:
+                break
+            for q in seqs:
+                q.num_cached_tokens = len(q)
+            s.postprocess(seqs, [1] * len(seqs))
+        times, first = [], True
+        for _ in range(steps):
+            t0 = time.perf_counter()
+            if not first:
+                seqs, pf = s.schedule()
+            first = False
+            due = [q for q in seqs if q.require_compress]
+            if due:
+                s.postprocess(due)
+            s.postprocess(seqs, [1] * len(seqs))
+            times.append(time.perf_counter() - t0)
+        return times
+
+    t_own, compressions = drive_own()
+    t_ref = drive_reference()
+    rec = {
+        "metric": "host_control_ms_per_decode_step", "value": statistics.mean(t_own) * 1e3, "unit": "ms",
+        "n_gpus": 0, "steps": steps, "warmup": 0, "ms_per_step": statistics.mean(t_own) * 1e3,
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "int32", "data": "synthetic",
+        "config": {"workload": f"host control plane, {n} concurrent requests of 600..800 prompt tokens decoded past "
+                               "their first compression (budget 8 pages)", "requests": n},
+        "native": {"mean_ms": statistics.mean(t_own) * 1e3, "median_ms": statistics.median(t_own) * 1e3,
+                   "max_ms": max(t_own) * 1e3, "compressions": compressions,
+                   "calls_per_step": "schedule + decode_inputs + postprocess (+ compress_inputs + postprocess when due)"},
+        "reference_python": None if t_ref is None else {
+            "mean_ms": statistics.mean(t_ref) * 1e3, "median_ms": statistics.median(t_ref) * 1e3,
+            "max_ms": max(t_ref) * 1e3, "calls_per_step": "Scheduler.schedule + postprocess (no prepare_decode)"},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(rec))
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload == "host_control":
+        return run_host_control(args)
     if args.workload == "prefill":
         return run_prefill(args)
     if args.workload == "decode":

@@ -1,0 +1,207 @@
+"""Host control plane (native scheduler + page manager) against the reference's Python objects.
+
+Golden: tests/golden/sched_traces.json holds, for every scenario of tests/sched_trace.py, the
+running CRC of the unmodified reference's whole host state after every step (made by
+tests/golden/make_sched_golden.py).  Where the reference itself can be imported (an installed
+copy under baseline/_ref), two more seeds are compared live, step by step.  No GPU anywhere.
+"""
+import json
+import random
+import sys
+import zlib
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent
+sys.path.insert(0, str(HERE))
+
+import sched_trace as T  # noqa: E402
+from zipage_b200.engine.scheduler import BlockManager, SamplingParams, Scheduler, Sequence, SequenceStatus  # noqa: E402
+
+GOLDEN = json.loads((HERE / "golden" / "sched_traces.json").read_text())
+
+
+def _fold(trace, every=25):
+    raised = bool(trace) and trace[-1] == "raised"
+    steps = trace[:-1] if raised else trace
+    run, marks = 0, []
+    for i, c in enumerate(steps):
+        run = zlib.crc32(c.to_bytes(4, "little"), run)
+        if (i + 1) % every == 0:
+            marks.append(run)
+    marks.append(run)
+    return len(steps), marks, raised
+
+
+@pytest.mark.parametrize("scenario", sorted(T.SCENARIOS))
+def test_state_after_every_step_equals_the_reference(scenario):
+    want = GOLDEN["traces"][scenario]
+    steps, marks, raised = _fold(T.run_trace(Scheduler, Sequence, SamplingParams, scenario, seed=0, max_steps=3000))
+    first = next((i for i, (a, b) in enumerate(zip(marks, want["marks"])) if a != b), None)
+    assert first is None, f"state differs from the reference's within steps {first * 25}..{first * 25 + 24}"
+    assert (steps, raised) == (want["steps"], want["raised"])
+
+
+def test_block_hash_known_answers():
+    for case in GOLDEN["hashes"]:
+        assert BlockManager.compute_hash(case["tokens"], case["prefix"]) == case["hash"]
+
+
+def _reference_classes():
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "zipage" / "engine" / "scheduler.py").exists():
+        pytest.skip("the reference is not installed under baseline/_ref")
+    sys.path.insert(0, str(ref))
+    try:
+        from zipage.engine.scheduler import Scheduler as RS
+        from zipage.engine.sequence import Sequence as RQ
+        from zipage.sampling_params import SamplingParams as RP
+    except Exception as e:  # its imports pull in torch extensions that may be absent
+        pytest.skip(f"the reference does not import here: {e!r}")
+    return RS, RQ, RP
+
+
+@pytest.mark.parametrize("scenario", ["prefix_cache_tight", "hybrid_tight_pool_preempts", "async_compress",
+                                      "eos_and_late_arrivals"])
+def test_live_against_the_installed_reference(scenario):
+    RS, RQ, RP = _reference_classes()
+    for seed in (1, 2):
+        want = T.run_trace(RS, RQ, RP, scenario, seed=seed, max_steps=2500)
+        got = T.run_trace(Scheduler, Sequence, SamplingParams, scenario, seed=seed, max_steps=2500)
+        first = next((i for i, (a, b) in enumerate(zip(want, got)) if a != b), None)
+        assert first is None and len(want) == len(got), (scenario, seed, first)
+
+
+def _running_scheduler(n=24, seed=3, **over):
+    cfg = T.make_config(**over)
+    rng = random.Random(seed)
+    s = Scheduler(cfg)
+    seqs = [Sequence([rng.randrange(5000) for _ in range(rng.randint(40, 900))],
+                     SamplingParams(0.6, rng.randint(300, 1200), True)) for _ in range(n)]
+    for q in seqs:
+        s.add(q)
+    return s, seqs, rng
+
+
+def test_array_calls_agree_with_the_sequence_attributes():
+    s, seqs, rng = _running_scheduler()
+    compressions = 0
+    for step in range(1400):
+        handles, is_prefill = s.schedule_batch()
+        if is_prefill:
+            s.mark_prefilled(handles)
+        else:
+            due = [h for h in handles.tolist() if s._seqs[h].require_compress]
+            assert s.compress_due(handles).tolist() == due
+            if due:
+                compressions += len(due)
+                c = s.compress_inputs(due)
+                for i, h in enumerate(due):
+                    q = s._seqs[h]
+                    t = q.block_table
+                    want = t[:-1] + [-t[-1] - 2] + [-1] * (c["tables"].shape[1] - len(t))
+                    assert c["tables"][i].tolist() == want
+                    assert c["targets"][i].tolist() == q.new_block_table
+                    assert c["query_ids"][i] == q.query_id and bool(c["compressed"][i]) == q.compressed
+                s.postprocess_batch(due)
+            d = s.decode_inputs(handles, table_width=6)
+            for i, h in enumerate(handles.tolist()):
+                q = s._seqs[h]
+                assert d["input_ids"][i] == q.last_token and d["num_tokens"][i] == len(q)
+                assert d["query_ids"][i] == q.query_id
+                t = q.block_table
+                assert d["block_tables"][i].tolist() == t + [-1] * (6 - len(t))
+                # what the device-side bookkeeping derives from these (model_runner.py:633-675)
+                assert (len(t) - 1) * 256 + q.last_block_num_tokens == len(q) or q.compressed
+        s.postprocess_batch(handles, np.asarray([rng.randrange(5000) for _ in handles], np.int32))
+        if s.is_finished():
+            break
+    assert s.is_finished() and compressions > 10
+    assert all(q.status == SequenceStatus.FINISHED and q.block_table == [] for q in seqs)
+    c = s.counts()
+    assert c[2] == 260 and c[3] == 0 and c[4] == 64      # every block and query slot came back
+
+
+def test_postprocess_consumes_the_callers_token_list_like_the_reference():
+    s, seqs, _ = _running_scheduler(n=4)
+    scheduled, is_prefill = s.schedule()
+    for q in scheduled:
+        q.num_cached_tokens = len(q)
+    tokens = [11, 12, 13, 14, 99]
+    s.postprocess(scheduled, tokens)
+    assert tokens == [99] and [q.last_token for q in scheduled] == [11, 12, 13, 14]
+    assert scheduled[0].completion_token_ids == [11] and scheduled[0].num_completion_tokens == 1
+
+
+def test_errors_are_reported_not_swallowed():
+    from zipage_b200 import _hostlib as H
+    s, seqs, _ = _running_scheduler(n=2)
+    with pytest.raises(H.SchedulerError):
+        s.postprocess_batch(np.asarray([57], np.int32), np.asarray([1], np.int32))   # unknown handle
+    long = Sequence(list(range(600)), SamplingParams(0.6, 10, True))     # three blocks
+    s.add(long)
+    s.schedule_batch()
+    with pytest.raises(H.SchedulerError):
+        s.decode_inputs(np.asarray([long._h], np.int32), table_width=2)   # table wider than the output
+    lib = H.load()
+    assert lib.zp_sched_schedule(s._obj, None, 0, None) == -1 and b"null" in lib.zp_sched_last_error()
+    assert lib.zp_sched_create(None) is None
+    with pytest.raises(AssertionError):      # the reference asserts here too (scheduler.py:137)
+        q = seqs[0]
+        while not q.compressed:
+            hs, pf = s.schedule_batch()
+            if pf:
+                s.mark_prefilled(hs)
+            due = [h for h in hs.tolist() if s._seqs[h].require_compress]
+            s.postprocess_batch(due)
+            s.postprocess_batch(hs, np.zeros(len(hs), np.int32))
+        s.preempt(q)
+
+
+def _replica_main(rank, world, port, tmp):
+    """Tensor-parallel ranks each run their own scheduler replica: the sampled tokens are the same
+    on every rank (the sharded sampler leaves every rank with the winners), so the replicas take the
+    same decisions and no per-step message from rank 0 is needed (the reference pickles the
+    scheduled sequences into shared memory every step, model_runner.py:151-203)."""
+    import os
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    s, seqs, _ = _running_scheduler(n=16, seed=5, num_kvcache_blocks=60, enable_prefix_cache=True)
+    ok, steps = True, 0
+    while not s.is_finished() and steps < 1500:
+        handles, is_prefill = s.schedule_batch()
+        if is_prefill:
+            s.mark_prefilled(handles)
+        else:
+            s.postprocess_batch([h for h in handles.tolist() if s._seqs[h].require_compress])
+        # every rank draws candidates for its own shard of the vocabulary; the largest key wins
+        g = torch.Generator().manual_seed(steps * world + rank)
+        keys = torch.randint(0, 1 << 20, (len(handles),), generator=g) * 4096 + torch.randint(0, 1024, (len(handles),), generator=g) * world + rank
+        dist.all_reduce(keys, op=dist.ReduceOp.MAX)
+        tokens = (keys % 4096).to(torch.int32).numpy()
+        d = s.decode_inputs(handles, table_width=5)
+        state = torch.tensor([zlib.crc32(handles.tobytes() + tokens.tobytes() + d["block_tables"].tobytes()
+                                         + d["num_tokens"].tobytes() + d["query_ids"].tobytes())], dtype=torch.int64)
+        every = [torch.zeros_like(state) for _ in range(world)]
+        dist.all_gather(every, state)
+        ok = ok and all(int(e) == int(state) for e in every)
+        s.postprocess_batch(handles, tokens)
+        steps += 1
+    if rank == 0:
+        Path(tmp).write_text("ok" if ok and s.is_finished() else f"diverged or unfinished after {steps} steps")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_scheduler_replicas_on_two_ranks_stay_in_step_gloo(tmp_path):
+    import os
+    import torch.multiprocessing as mp
+    port = 31500 + os.getpid() % 2000
+    res = tmp_path / "result.txt"
+    mp.spawn(_replica_main, args=(2, port, str(res)), nprocs=2, join=True)
+    assert res.read_text() == "ok"
