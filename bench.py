@@ -58,6 +58,8 @@ def parse_args():
                          "tp_allreduce (the row-parallel projections' all-reduce + residual + RMSNorm over "
                          "peer memory against the library collective; needs --gpus >= 2 under torchrun)")
     ap.add_argument("--verbose", action="store_true", help="progress lines on stderr")
+    ap.add_argument("--engine-modes", default="reference,kernels,graph",
+                    help="modes of the engine_decode workload (tests/ref_engine.py): reference, kernels, full, graph, native")
     ap.add_argument("--requests", type=int, default=2048, help="concurrent requests of the host_control workload")
     ap.add_argument("--tokens", type=int, default=32768, help="tokens per call of the step_ops workload")
     return ap.parse_args()
@@ -566,7 +568,7 @@ def engine_decode_records(modes=("reference", "kernels", "graph"), requests=192,
     prompts, a budget of 8 pages, lightning redundancy + pooling, two compressions per request:
     `reference` = the engine as it is (Triton + flash-attn), `kernels` = zipage_b200.kernel bound in
     model_runner.py, `graph` = also the attention layer and the decode forward as replayed CUDA
-    graphs.  Each mode is a child process (tests/ref_engine.py); accounting is the engine's own
+    graphs, `native` = also the native scheduler and page manager in place of the engine's.  Each mode is a child process (tests/ref_engine.py); accounting is the engine's own
     time_record (decode_sum + compress_sum)."""
     out = {"workload": f"Qwen3-8B shapes, random-init bf16, {requests} concurrent requests, prompts of 2300 "
                        f"uniform-random ids, {max_tokens} generated tokens each, budget 8 x 256, temperature 0.6"}
@@ -591,18 +593,19 @@ def engine_decode_records(modes=("reference", "kernels", "graph"), requests=192,
             out[m] = {"decode_tokens_per_s": d["decode_tok_per_s"],
                       "decode_tokens_per_s_excluding_compress": d["decode_tok_per_s_excluding_compress"],
                       "prefill_tokens_per_s": d["prefill_tok_per_s"], "decode_s": e.get("decode_sum"),
-                      "compress_s": e.get("compress_sum"), "decode_tokens": d["decode_tokens"]}
+                      "compress_s": e.get("compress_sum"), "decode_tokens": d["decode_tokens"],
+                      "wall_s": d["wall_s"], "generated_tokens_per_wall_s": d["generated_tokens"] / d["wall_s"]}
         except Exception as ex:
             out[m] = {"unavailable": f"{type(ex).__name__}: {ex}"[:300]}
     ref = out.get("reference", {}).get("decode_tokens_per_s")
-    for m in modes[1:]:
+    for m in modes:
         if ref and out.get(m, {}).get("decode_tokens_per_s"):
             out[m]["vs_reference_engine"] = out[m]["decode_tokens_per_s"] / ref
     return out
 
 
 def run_engine_decode(args):
-    rec = engine_decode_records()
+    rec = engine_decode_records(tuple(args.engine_modes.split(",")))
     g = rec.get("graph", {})
     print(json.dumps({"metric": "engine_decode_tokens_per_s", "value": g.get("decode_tokens_per_s"), "unit": "tokens/s",
                       "n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "config": {"workload": rec["workload"]},

@@ -61,8 +61,10 @@ int zp_sched_schedule(void* sched, int32_t* out_handles, int capacity, int32_t* 
 
 /* Scheduler.postprocess(seqs, token_ids) (scheduler.py:143-167); token_ids may be null (the
  * call after a compression).  `now` is the wall-clock time stored as time_prefilled /
- * time_finished. */
+ * time_finished.  Returns how many of the sequences finished in this call;
+ * zp_sched_last_finished() lists them (returns the count, writes only when it fits). */
 int zp_sched_postprocess(void* sched, const int32_t* handles, int n, const int32_t* token_ids, double now);
+int zp_sched_last_finished(void* sched, int32_t* out, int capacity);
 
 /* Scheduler.preempt(seq) (scheduler.py:136-141). */
 int zp_sched_preempt(void* sched, int handle);
@@ -82,6 +84,8 @@ int zp_sched_counts(void* sched, int32_t out[8]);
  * num_cached_tokens, last_token, query_id, require_compress, compressed, prefilled, max_tokens,
  * ignore_eos, len(block_table), len(new_block_table), len(block_to_release), 0, 0. */
 int zp_sched_seq_info(void* sched, int handle, int32_t out[16]);
+/* The same for n sequences: out[n][16]. */
+int zp_sched_seq_info_batch(void* sched, const int32_t* handles, int n, int32_t* out);
 /* times[0..1] = time_prefilled, time_finished; temperature */
 int zp_sched_seq_times(void* sched, int handle, double times[2], float* temperature);
 int zp_sched_seq_set_num_cached(void* sched, int handle, int num_cached_tokens);

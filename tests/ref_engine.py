@@ -125,7 +125,7 @@ def bind(mode):
     for n in ["compress_kv", "compress_score", "attention_score", "raw_redudancy_score",
               "lightning_redudancy_score", "global_score", "window_mask", "topk_mask"]:
         setattr(mr, n, getattr(K, n))
-    if mode in ("full", "steps", "graph"):
+    if mode in ("full", "steps", "graph", "native"):
         import zipage.layers.attention as ref_att
         import zipage.models.qwen3 as ref_qwen3
         import zipage.utils.context as ref_ctx
@@ -178,16 +178,33 @@ def bind_graph_decode(llm, max_bs, max_model_len, qcl):
         dg.capture()
     torch.cuda.synchronize()
     orig_run = mr.ModelRunner.run
+    from zipage_b200.engine import scheduler as own
+    native = isinstance(llm.scheduler, own.Scheduler)
+    width = (max_model_len + 255) // 256 + 1
+    if native:   # the scheduler fills pinned arrays for the whole batch in one call
+        staged = {"input_ids": torch.empty(max_bs, dtype=torch.int32).pin_memory(),
+                  "num_tokens": torch.empty(max_bs, dtype=torch.int32).pin_memory(),
+                  "query_ids": torch.empty(max_bs, dtype=torch.int32).pin_memory(),
+                  "block_tables": torch.empty(max_bs, width, dtype=torch.int32).pin_memory()}
+        views = {k: v.numpy() for k, v in staged.items()}
 
     def run(self, seqs, is_prefill):
         if is_prefill or len(seqs) > max_bs:
             return orig_run(self, seqs, is_prefill)
         with torch.cuda.stream(self.run_stream), torch.inference_mode():
             pin = lambda data, dt: torch.tensor(data, dtype=dt, pin_memory=True).cuda(non_blocking=True)
-            ids = pin([s.last_token for s in seqs], torch.int64)
-            ntok = pin([len(s) for s in seqs], torch.int32)
-            qids = pin([s.query_id for s in seqs], torch.int32)
-            tables = self.prepare_block_tables(seqs)
+            if native:
+                n = len(seqs)
+                d = llm.scheduler.decode_inputs(llm.scheduler._handles_of(seqs), table_width=width, out=views)
+                ids = staged["input_ids"][:n].cuda(non_blocking=True)
+                ntok = staged["num_tokens"][:n].cuda(non_blocking=True)
+                qids = staged["query_ids"][:n].cuda(non_blocking=True)
+                tables = staged["block_tables"][:n, :d["widest"]].cuda(non_blocking=True)
+            else:
+                ids = pin([s.last_token for s in seqs], torch.int64)
+                ntok = pin([len(s) for s in seqs], torch.int32)
+                qids = pin([s.query_id for s in seqs], torch.int32)
+                tables = self.prepare_block_tables(seqs)
             past, temps = self.prepare_sample(seqs)
             hidden = dg.run(ids, ntok, tables, qids)
             logits = self.model.compute_logits(hidden)
@@ -196,9 +213,19 @@ def bind_graph_decode(llm, max_bs, max_model_len, qcl):
     return dg
 
 
+def bind_native_scheduler():
+    """The engine's Scheduler / Sequence replaced by this library's native ones (same constructor
+    argument, calls and attributes): zipage/engine/zipage_engine.py:12-13 imports the names the
+    engine uses, so binding them there before ZipLLM is built is the whole swap."""
+    import zipage.engine.zipage_engine as ze
+    from zipage_b200.engine import scheduler as own
+    ze.Scheduler = own.Scheduler
+    ze.Sequence = own.Sequence
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="reference", choices=["reference", "kernels", "full", "steps", "graph"])
+    ap.add_argument("--mode", default="reference", choices=["reference", "kernels", "full", "steps", "graph", "native"])
     ap.add_argument("--out", required=True)
     ap.add_argument("--model-dir", default="/tmp/zp_synth_model")
     ap.add_argument("--layers", type=int, default=4)
@@ -246,6 +273,8 @@ def main():
 
     transformers_compat()
     bind(args.mode)
+    if args.mode == "native":
+        bind_native_scheduler()
     import zipage.layers.sampler as ref_sampler
     from zipage.llm import ZipLLM
     from zipage.sampling_params import SamplingParams
@@ -271,7 +300,7 @@ def main():
                  use_redudancy=args.lightning or args.exact, lightning_redudancy=args.lightning,
                  redudancy_lambda=0.5, use_global_score=args.global_score, enable_pooling=args.pooling,
                  enable_async_compress=args.async_compress, enable_prefix_cache=args.prefix_cache)
-    if args.mode == "graph":
+    if args.mode in ("graph", "native"):
         bind_graph_decode(llm, min(args.max_num_seqs, max(args.requests, args.warmup_requests, 16)),
                           args.max_model_len, args.qcl)
     g = torch.Generator().manual_seed(args.seed + 1)

@@ -1,7 +1,7 @@
 """Greedy decode through the reference ENGINE: 256 steps across a compression, token by token.
 
 The unmodified reference engine (zipage.ZipLLM.generate from baseline/_ref: scheduler, block
-manager, model runner, Qwen3 model) runs a seeded random-init Qwen3-shaped model three times on
+manager, model runner, Qwen3 model) runs a seeded random-init Qwen3-shaped model several times on
 the same uniform-random prompts, with argmax in place of its sampler (the reference's sampler is
 an exponential race that no two implementations reproduce, and its SamplingParams refuses
 temperature 0):
@@ -9,7 +9,9 @@ temperature 0):
   kernels    with zipage_b200.kernel bound at the import sites of model_runner.py;
   full       with the Attention layer (cache stores, prefill and decode attention) bound as well;
   graph      with, on top of that, the decode forward replayed as CUDA graphs over this library's
-             decoder blocks (device-built step state, fused q/k norm + rope + cache stores).
+             decoder blocks (device-built step state, fused q/k norm + rope + cache stores);
+  native     with, on top of that, the engine's Scheduler / Sequence replaced by the native host
+             control plane (the runner's decode inputs come from one array call).
 A random-init model has near-flat logits, so two correct bf16 implementations that differ in the
 last bit of one attention output — or that keep a different one of two keys tied at the top-k cut
 — diverge for good at the first near-tie of the arg-max; a free-running comparison then says
@@ -96,3 +98,7 @@ def test_greedy_256_steps_through_the_reference_engine(tmp_path):
     compare(full, "compression kernels and attention layer bound")
     graph = _run("graph", tmp_path / "graph.json", forced)
     compare(graph, "decode step as CUDA graphs over this library's blocks")
+    native = _run("native", tmp_path / "native.json", forced)
+    compare(native, "the same with the native scheduler and page manager in place of the engine's")
+    # same requests, same tokens fed back: the native scheduler took the same decisions
+    assert native["engine_time_record"].get("compress_reqs") == graph["engine_time_record"].get("compress_reqs")

@@ -116,7 +116,9 @@ def test_array_calls_agree_with_the_sequence_attributes():
                 assert d["block_tables"][i].tolist() == t + [-1] * (6 - len(t))
                 # what the device-side bookkeeping derives from these (model_runner.py:633-675)
                 assert (len(t) - 1) * 256 + q.last_block_num_tokens == len(q) or q.compressed
-        s.postprocess_batch(handles, np.asarray([rng.randrange(5000) for _ in handles], np.int32))
+        done = s.postprocess_batch(handles, np.asarray([rng.randrange(5000) for _ in handles], np.int32))
+        assert sorted(done.tolist()) == sorted(h for h in handles.tolist() if s._seqs[h].status == SequenceStatus.FINISHED)
+        assert all(s._seqs[h].is_finished for h in done.tolist())
         if s.is_finished():
             break
     assert s.is_finished() and compressions > 10

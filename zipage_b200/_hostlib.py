@@ -30,11 +30,13 @@ SIGNATURES = {
     "zp_sched_add": (_I, [_P, _P, _I, C.c_float, _I, _I]),
     "zp_sched_schedule": (_I, [_P, _P, _I, _P]),
     "zp_sched_postprocess": (_I, [_P, _P, _I, _P, _D]),
+    "zp_sched_last_finished": (_I, [_P, _P, _I]),
     "zp_sched_preempt": (_I, [_P, _I]),
     "zp_sched_mark_prefilled": (_I, [_P, _P, _I]),
     "zp_sched_release": (_I, [_P, _I]),
     "zp_sched_counts": (_I, [_P, _P]),
     "zp_sched_seq_info": (_I, [_P, _I, _P]),
+    "zp_sched_seq_info_batch": (_I, [_P, _P, _I, _P]),
     "zp_sched_seq_times": (_I, [_P, _I, _P, _P]),
     "zp_sched_seq_set_num_cached": (_I, [_P, _I, _I]),
     "zp_sched_seq_list": (_I, [_P, _I, _I, _P, _I]),

@@ -120,6 +120,7 @@ struct Sched {
   std::deque<int32_t> free_qids;
   int32_t used_qids = 0;
   std::unordered_map<uint64_t, int32_t> hash_to_block;
+  std::vector<int32_t> last_finished;   // handles that finished in the latest postprocess call
 
   // ---- Sequence properties (sequence.py:62-76) ----
   int num_blocks(const Seq& s) const { return (s.num_tokens + cfg.block_size - 1) / cfg.block_size; }
@@ -410,6 +411,7 @@ int Sched::schedule(int32_t* out, int cap, int32_t* is_prefill) {
 // postprocess (scheduler.py:143-167)
 int Sched::postprocess(const int32_t* hs, int n, const int32_t* toks, double now) {
   const int BS = cfg.block_size;
+  last_finished.clear();
   for (int i = 0; i < n; ++i) {
     const int h = hs[i];
     if (h < 0 || h >= (int)seqs.size()) return fail(ZP_SCHED_ERR_ARG, "postprocess: bad handle %d", h);
@@ -439,10 +441,11 @@ int Sched::postprocess(const int32_t* hs, int n, const int32_t* toks, double now
         running.remove(seqs, h);
         s.where = 0;
         deallocate_qid(s);
+        last_finished.push_back(h);
       }
     }
   }
-  return 0;
+  return (int)last_finished.size();
 }
 
 }  // namespace host
@@ -509,6 +512,11 @@ int zp_sched_postprocess(void* sched, const int32_t* handles, int n, const int32
   return S(sched)->postprocess(handles, n, token_ids, now);
 }
 
+int zp_sched_last_finished(void* sched, int32_t* out, int capacity) {
+  if (!sched) return fail(ZP_SCHED_ERR_ARG, "zp_sched_last_finished: null argument");
+  return copy_out(S(sched)->last_finished, out, capacity);
+}
+
 int zp_sched_preempt(void* sched, int handle) {
   if (!sched || bad_handle(S(sched), handle)) return fail(ZP_SCHED_ERR_ARG, "zp_sched_preempt: bad handle");
   Sched* s = S(sched);
@@ -555,6 +563,15 @@ int zp_sched_seq_info(void* sched, int handle, int32_t out[16]) {
                          q.require_compress, q.compressed, q.prefilled, q.max_tokens, q.ignore_eos,
                          (int32_t)q.table.size(), (int32_t)q.new_table.size(), (int32_t)q.to_release.size(), 0, 0};
   memcpy(out, v, sizeof(v));
+  return 0;
+}
+
+int zp_sched_seq_info_batch(void* sched, const int32_t* handles, int n, int32_t* out) {
+  if (!sched || (n > 0 && (!handles || !out))) return fail(ZP_SCHED_ERR_ARG, "zp_sched_seq_info_batch: null argument");
+  for (int i = 0; i < n; ++i) {
+    const int rc = zp_sched_seq_info(sched, handles[i], out + (size_t)i * 16);
+    if (rc < 0) return rc;
+  }
   return 0;
 }
 

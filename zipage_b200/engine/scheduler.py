@@ -58,9 +58,13 @@ class Sequence:
         self.request_id = next(Sequence.counter)
         self._prompt = [int(t) for t in token_ids]
         self._params = sampling_params
+        self.temperature = sampling_params.temperature     # never change: kept on the handle
+        self.max_tokens = sampling_params.max_tokens
+        self.ignore_eos = sampling_params.ignore_eos
         self._sched = None
         self._h = -1
         self._cache = {}
+        self._finished = False
 
     # -- native state -------------------------------------------------------------------------
     # Reads are cached until the scheduler's next mutating call (its epoch), so a runner that
@@ -93,18 +97,16 @@ class Sequence:
         H.check(self._sched._lib.zp_sched_seq_times(self._sched._obj, self._h, t, C.byref(temp)), "seq_times")
         return t[0], t[1], temp.value
 
-    _FIELD = {"num_tokens": 1, "num_prompt_tokens": 2, "num_cached_tokens": 3, "last_token": 4,
-              "query_id": 5, "max_tokens": 9}
-    _FLAG = {"require_compress": 6, "compressed": 7, "prefilled": 8, "ignore_eos": 10}
+    _FIELD = {"num_tokens": 1, "num_prompt_tokens": 2, "num_cached_tokens": 3, "last_token": 4, "query_id": 5}
+    _FLAG = {"require_compress": 6, "compressed": 7, "prefilled": 8}
 
     def __getattr__(self, name):   # only reached for names that are not plain attributes
         if name in Sequence._FIELD or name in Sequence._FLAG:
             if self.__dict__.get("_sched") is None:   # not added yet: the constructor's values
                 p = self.__dict__["_prompt"]
                 before = {"num_tokens": len(p), "num_prompt_tokens": len(p), "num_cached_tokens": 0,
-                          "last_token": p[-1], "query_id": -1, "max_tokens": self._params.max_tokens,
-                          "require_compress": False, "compressed": False, "prefilled": False,
-                          "ignore_eos": self._params.ignore_eos}
+                          "last_token": p[-1], "query_id": -1,
+                          "require_compress": False, "compressed": False, "prefilled": False}
                 return before[name]
             info = self._info()
             return info[Sequence._FIELD[name]] if name in Sequence._FIELD else bool(info[Sequence._FLAG[name]])
@@ -129,10 +131,6 @@ class Sequence:
     @property
     def block_to_release(self):
         return [] if self._sched is None else self._list(2)
-
-    @property
-    def temperature(self):
-        return self._params.temperature if self._sched is None else self._times()[2]
 
     @property
     def time_prefilled(self):
@@ -162,7 +160,8 @@ class Sequence:
 
     @property
     def is_finished(self):
-        return self.status == SequenceStatus.FINISHED
+        # a sequence finishes only inside Scheduler.postprocess, which flags its handle
+        return self._finished
 
     @property
     def num_completion_tokens(self):
@@ -318,7 +317,14 @@ class Scheduler:
 
     def schedule(self):
         handles, is_prefill = self.schedule_batch()
-        return [self._seqs[h] for h in handles.tolist()], is_prefill
+        seqs = [self._seqs[h] for h in handles.tolist()]
+        # the engine looks at every scheduled sequence right away (zipage_engine.py:101-105): fetch
+        # their scalar state in one call instead of one call per sequence
+        info = np.empty((max(len(seqs), 1), 16), dtype=np.int32)
+        H.check(self._lib.zp_sched_seq_info_batch(self._obj, _ptr(handles), len(seqs), _ptr(info)), "seq_info_batch")
+        for q, row in zip(seqs, info.tolist()):
+            q._cache["info"] = (self._epoch, row)
+        return seqs, is_prefill
 
     def postprocess(self, seqs, token_ids=None):
         n = len(seqs)
@@ -342,14 +348,21 @@ class Scheduler:
         return self._handles[:n].copy(), bool(flag.value)
 
     def postprocess_batch(self, handles, token_ids=None, now=None):
+        """-> the handles that finished in this call (int32 array)."""
         handles = np.ascontiguousarray(handles, dtype=np.int32)
         toks = None if token_ids is None else np.ascontiguousarray(token_ids, dtype=np.int32)
         if toks is not None and len(toks) != len(handles):
             raise ValueError("one token per sequence")
         self._epoch += 1
-        H.check(self._lib.zp_sched_postprocess(self._obj, _ptr(handles), len(handles),
-                                               None if toks is None else _ptr(toks),
-                                               time.time() if now is None else now), "postprocess")
+        n = H.check(self._lib.zp_sched_postprocess(self._obj, _ptr(handles), len(handles),
+                                                   None if toks is None else _ptr(toks),
+                                                   time.time() if now is None else now), "postprocess")
+        done = np.empty(max(n, 1), dtype=np.int32)
+        if n:
+            H.check(self._lib.zp_sched_last_finished(self._obj, _ptr(done), n), "last_finished")
+            for h in done[:n].tolist():
+                object.__setattr__(self._seqs[h], "_finished", True)
+        return done[:n]
 
     def mark_prefilled(self, handles):
         handles = np.ascontiguousarray(handles, dtype=np.int32)
