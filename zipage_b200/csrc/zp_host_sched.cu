@@ -127,11 +127,23 @@ struct Sched {
   int last_block_num_tokens(const Seq& s) const { return s.num_tokens - (num_blocks(s) - 1) * cfg.block_size; }
 
   // ---- BlockManager ----
+  // Block.reset (block_manager.py:20-23).  The reference leaves the block's old hash in
+  // hash_to_block_id for ever; a later lookup that finds it compares token lists and misses.  Here
+  // the entry is dropped (when it still points at this block), which gives the same misses and
+  // keeps the map no larger than the number of blocks.
+  void reset_block(int id) {
+    Block& b = blocks[id];
+    if (b.has_hash) {
+      auto it = hash_to_block.find(b.hash);
+      if (it != hash_to_block.end() && it->second == id) hash_to_block.erase(it);
+    }
+    b.reset();
+  }
   void allocate_block(int id) {            // block_manager.py:59-66
     free_blocks.remove(blocks, id);
     blocks[id].is_free = false;
     ++used_blocks;
-    blocks[id].reset();
+    reset_block(id);
   }
   void deallocate_block(int id) {          // :68-74
     Block& b = blocks[id];
@@ -243,7 +255,7 @@ int Sched::may_compress(Seq& s, bool* ok) {
     return fail(ZP_SCHED_ERR_STATE, "may_compress: %d destination pages, expected %d", (int)s.new_table.size(), MB);
   s.to_release.assign(s.table.begin(), s.table.begin() + nps);
   s.to_release.insert(s.to_release.end(), s.table.begin() + hi, s.table.end());
-  for (int i = lo; i < hi; ++i) blocks[s.table[i]].reset();
+  for (int i = lo; i < hi; ++i) reset_block(s.table[i]);
   s.require_compress = 1;
   *ok = true;
   return 0;
