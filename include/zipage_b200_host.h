@@ -112,6 +112,17 @@ uint64_t zp_sched_hash_tokens(const int32_t* token_ids, int n, int has_prefix, u
 int zp_sched_decode_inputs(void* sched, const int32_t* handles, int n, int32_t* input_ids,
                            int32_t* num_tokens, int32_t* query_ids, int32_t* block_tables, int table_width);
 
+/* Inputs of one prefill step (ModelRunner.prepare_prefill, model_runner.py:352-422).
+ * zp_sched_prefill_sizes: out[0..3] = new tokens of all n sequences, window rows they store,
+ * max_seqlen_q, max_seqlen_k.  zp_sched_prefill_inputs fills input_ids / positions / slot_mapping
+ * (one entry per new token), cu_seqlens_q / cu_seqlens_k (n + 1 entries) and the window-store
+ * triples (row of the flattened batch, query slot, window index; three int32 each), marks the
+ * sequences prefilled (num_cached_tokens = len) and returns the number of triples. */
+int zp_sched_prefill_sizes(void* sched, const int32_t* handles, int n, int32_t out[4]);
+int zp_sched_prefill_inputs(void* sched, const int32_t* handles, int n, int32_t* input_ids, int32_t* positions,
+                            int32_t* slot_mapping, int32_t* cu_seqlens_q, int32_t* cu_seqlens_k,
+                            int32_t* query_triples);
+
 /* The handles among `handles` whose sequence has require_compress set, in order (the filter of
  * zipage_engine.py:101-105).  Returns how many. */
 int zp_sched_compress_due(void* sched, const int32_t* handles, int n, int32_t* out_handles);

@@ -1,0 +1,130 @@
+"""The serving loop built from this library only (zipage_b200/engine/native_engine.py: native
+scheduler, varlen prefill through the decoder blocks, graph-replayed decode, Compressor, LM head)
+against the unmodified reference ENGINE on the same seeded model and prompts.
+
+As in test_gpu_reference_engine.py the comparison is teacher-forced: the native loop is fed the
+reference run's tokens while its own arg-max, top-2 margin and logit spread are recorded at every
+step; the own arg-max must equal the reference's token wherever the reference's margin exceeds
+2e-2 of the logit spread (the bf16 tolerance of the path).  That the loop takes the same steps as
+the reference engine (one prefill batch, then every decode step with all requests, compressions
+at the same steps) follows from the scheduler's state parity (tests/test_host_scheduler.py) and
+shows here in the step counts.  A second, free-running pass checks that graph replay and
+launch-by-launch decode give the same tokens.
+"""
+import json
+import subprocess
+import sys
+import types
+from pathlib import Path
+
+import pytest
+import torch
+
+import ref_binding as RB
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+STEPS = 256
+SHAPE = dict(layers=4, hidden=1024, inter=2048, hq=8, hkv=2, vocab=2048, seed=0)
+MODEL_DIR = Path("/tmp/zp_synth_model")      # the directory tests/ref_engine.py writes by default
+
+
+def _engine(graph, greedy=True, max_bs=16):
+    from safetensors.torch import load_file
+    from zipage_b200.compress import CompressConfig
+    from zipage_b200.engine.native_engine import NativeEngine, full_state_from_hf
+    from zipage_b200.layers.qwen3_block import Qwen3Model
+    dev = torch.device("cuda")
+    hf = {}
+    for f in sorted(MODEL_DIR.glob("*.safetensors")):
+        hf.update(load_file(str(f)))
+    full, lm_head = full_state_from_hf(hf)
+    cfg = types.SimpleNamespace(hidden_size=SHAPE["hidden"], num_attention_heads=SHAPE["hq"],
+                                num_key_value_heads=SHAPE["hkv"], head_dim=128, intermediate_size=SHAPE["inter"],
+                                hidden_act="silu", rms_norm_eps=1e-6, vocab_size=SHAPE["vocab"],
+                                num_hidden_layers=SHAPE["layers"], max_position_embeddings=40960, rope_theta=1e6)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(dev):
+            model = Qwen3Model(cfg).eval()
+    finally:
+        torch.set_default_dtype(prev)
+    model.load_full_state({k: v.to(dev) for k, v in full.items()})
+    blocks, slots = 64, 8
+    kv = torch.zeros((2, SHAPE["layers"], blocks, 256, SHAPE["hkv"], 128), dtype=torch.bfloat16, device=dev)
+    qc = torch.zeros((SHAPE["layers"], slots, 16, SHAPE["hq"], 128), dtype=torch.bfloat16, device=dev)
+    model.bind_caches(kv, qc)
+    sched_cfg = types.SimpleNamespace(max_num_seqs=16, max_num_batched_tokens=32768, eos=1, num_kvcache_blocks=blocks,
+                                      kvcache_block_size=256, max_cache_blocks_per_seq=2, enable_prefix_cache=False,
+                                      max_concurrency=slots, enable_hybrid_engine=False, query_cache_len=16)
+    ccfg = CompressConfig(budget_blocks=2, query_cache_len=16, use_redudancy=True, lightning_redudancy=True,
+                          redudancy_lambda=0.5, enable_pooling=True)
+    return NativeEngine(model, lm_head.to(dev), kv, qc, sched_cfg, ccfg, SHAPE["hidden"], max_bs=max_bs,
+                        max_model_len=8192, greedy=greedy, graph=graph)
+
+
+def _prompts(n=4, length=600):
+    g = torch.Generator().manual_seed(SHAPE["seed"] + 1)       # as tests/ref_engine.py draws them
+    return [torch.randint(2, SHAPE["vocab"], (length,), generator=g).tolist() for _ in range(n)]
+
+
+def _requests(prompts):
+    from zipage_b200.engine.scheduler import SamplingParams, Sequence
+    return [Sequence(p, SamplingParams(0.6, STEPS, True)) for p in prompts]
+
+
+def test_native_engine_against_the_reference_engine(tmp_path):
+    ok, why = RB.reference_available()
+    if not ok:
+        pytest.skip(why)
+    out = tmp_path / "ref.json"
+    cmd = [sys.executable, str(ROOT / "tests" / "ref_engine.py"), "--mode", "reference", "--out", str(out),
+           "--greedy", "--lightning", "--pooling", "--requests", "4", "--prompt-len", "600",
+           "--max-tokens", str(STEPS), "--budget", "2", "--qcl", "16"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    if r.returncode != 0:
+        pytest.skip("the reference engine does not start on this machine: " + (r.stdout + r.stderr)[-600:])
+    ref = json.loads(out.read_text())
+    assert all(len(t) == STEPS for t in ref["tokens"])
+
+    # the reference's sampler is also called once while the engine warms up, before any request
+    ref_steps = ref["steps"][-STEPS:]
+    assert len(ref["steps"]) in (STEPS, STEPS + 1)
+    eng = _engine(graph=True)
+    eng.forced = iter([s["tokens"] for s in ref_steps])
+    eng.argmax_log = []
+    seqs = _requests(_prompts())
+    got = eng.generate(seqs)
+    assert [got[s._h] for s in seqs] == ref["tokens"]               # the forced tokens, all 256 of each
+    assert len(eng.argmax_log) == STEPS                              # one prefill + 255 decode steps
+    assert eng.time_record["compress_reqs"] == 4                     # every request crossed 769 tokens once
+    total = mism = unexplained = near = 0
+    for a, b in zip(ref_steps, eng.argmax_log):
+        for ta, tb, m, s in zip(a["tokens"], b["tokens"], a["margin"], a["spread"]):
+            total += 1
+            near += m <= 2e-2 * s
+            if ta != tb:
+                mism += 1
+                unexplained += m > 2e-2 * s
+    print(f"native engine: {total} sampled tokens, own arg-max differs on {mism}, {unexplained} of them at a "
+          f"margin above 2e-2 of the logit spread ({near} steps are below it)")
+    assert unexplained == 0 and mism <= 0.05 * total
+    c = eng.scheduler.counts()
+    assert c[7] == 1 and c[3] == 0                                   # finished, every block returned
+
+
+def test_graph_replay_and_launch_by_launch_give_the_same_tokens():
+    if not MODEL_DIR.exists():
+        sys.path.insert(0, str(ROOT / "tests"))
+        import ref_engine
+        ref_engine.make_model_dir(MODEL_DIR, **SHAPE)
+        (MODEL_DIR / "tag").write_text("-".join(str(SHAPE[k]) for k in ("layers", "hidden", "inter", "hq", "hkv", "vocab", "seed")))
+    runs = []
+    for graph in (True, False):
+        eng = _engine(graph=graph)
+        seqs = _requests(_prompts(n=3, length=700))
+        got = eng.generate(seqs)
+        runs.append([got[s._h] for s in seqs])
+        assert eng.time_record["compress_reqs"] == 3 and all(len(t) == STEPS for t in runs[-1])
+    assert runs[0] == runs[1]

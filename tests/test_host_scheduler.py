@@ -207,3 +207,65 @@ def test_scheduler_replicas_on_two_ranks_stay_in_step_gloo(tmp_path):
     res = tmp_path / "result.txt"
     mp.spawn(_replica_main, args=(2, port, str(res)), nprocs=2, join=True)
     assert res.read_text() == "ok"
+
+
+def _prepare_prefill_lists(seqs, block_size, qcl):
+    """The list building of ModelRunner.prepare_prefill / get_query_slot_mapping
+    (zipage/engine/model_runner.py:319-339, :352-388), restated on the reference's attribute names."""
+    ids, pos, slots, triples, cu_q, cu_k = [], [], [], [], [0], [0]
+    for s in seqs:
+        seqlen, cached = len(s), s.num_cached_tokens
+        toks = s.token_ids
+        ids += toks[cached:]
+        pos += list(range(cached, seqlen))
+        lq = seqlen - cached
+        if s.query_id != -1:
+            nb = (lq + block_size - 1) // block_size
+            if nb and lq - (nb - 1) * block_size > block_size - qcl:
+                start = nb * block_size - qcl
+                triples += [(cu_q[-1] + p, s.query_id, i) for i, p in enumerate(range(start, lq))]
+        cu_q.append(cu_q[-1] + lq)
+        cu_k.append(cu_k[-1] + seqlen)
+        table = s.block_table
+        for i in range(cached // block_size, s.num_blocks):
+            start = table[i] * block_size
+            slots += list(range(start, start + (block_size if i != s.num_blocks - 1 else s.last_block_num_tokens)))
+    return ids, pos, slots, triples, cu_q, cu_k
+
+
+@pytest.mark.parametrize("prefix_cache", [False, True])
+def test_prefill_inputs_equal_the_reference_list_building(prefix_cache):
+    rng = random.Random(21)
+    cfg = T.make_config(enable_prefix_cache=prefix_cache, num_kvcache_blocks=200, max_num_seqs=16,
+                        max_num_batched_tokens=6000)
+    s = Scheduler(cfg)
+    shared = [rng.randrange(5000) for _ in range(512)]
+    lengths = [40, 225, 250, 256, 257, 480, 500, 512, 700, 760, 1000, 1023, 1300]   # around the window limits
+    for n in lengths * 2:
+        toks = [rng.randrange(5000) for _ in range(n)]
+        if prefix_cache and n > 600:
+            toks[:512] = shared
+        s.add(Sequence(toks, SamplingParams(0.6, 4, True)))
+    seen_cached = seen_rows = batches = 0
+    while True:
+        seqs, is_prefill = s.schedule()
+        if not is_prefill:
+            break
+        batches += 1
+        seen_cached += sum(q.num_cached_tokens > 0 for q in seqs)
+        want = _prepare_prefill_lists(seqs, 256, 32)
+        got = s.prefill_inputs(s._handles_of(seqs))
+        assert got["input_ids"].tolist() == want[0] and got["positions"].tolist() == want[1]
+        assert got["slot_mapping"].tolist() == want[2]
+        assert [tuple(r) for r in got["query_triples"].tolist()] == want[3]
+        assert got["cu_seqlens_q"].tolist() == want[4] and got["cu_seqlens_k"].tolist() == want[5]
+        assert got["max_seqlen_q"] == max(b - a for a, b in zip(want[4], want[4][1:]))
+        assert got["max_seqlen_k"] == max(len(q) for q in seqs)
+        assert (got["block_tables"] is not None) == (want[5][-1] > want[4][-1])
+        if got["block_tables"] is not None:
+            for row, q in zip(got["block_tables"].tolist(), seqs):
+                assert [b for b in row if b >= 0] == q.block_table
+        assert all(q.num_cached_tokens == len(q) for q in seqs)      # marked prefilled
+        seen_rows += len(want[3])
+        s.postprocess(seqs, [1] * len(seqs))
+    assert batches >= 2 and seen_rows > 0 and (seen_cached > 0) == prefix_cache

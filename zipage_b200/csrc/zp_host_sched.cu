@@ -5,6 +5,7 @@
 // intrusive doubly linked list over indices, so popleft / pop / append / appendleft / remove(x)
 // are all O(1) (the reference's deque.remove is a linear search), and one call hands the runner
 // the index arrays of a whole step.
+#include <climits>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
@@ -659,6 +660,81 @@ int zp_sched_decode_inputs(void* sched, const int32_t* handles, int n, int32_t* 
     for (int j = len; j < table_width; ++j) row[j] = -1;
   }
   return widest;
+}
+
+// number of window rows a prefill of `seqlen_q` new tokens stores (model_runner.py:328-339)
+static int prefill_window_rows(const Sched* s, const Seq& q, int seqlen_q, int* start) {
+  const int BS = s->cfg.block_size, QCL = s->cfg.query_cache_len;
+  if (q.query_id == -1 || seqlen_q <= 0) return 0;
+  const int nb = (seqlen_q + BS - 1) / BS;
+  const int last = seqlen_q - (nb - 1) * BS;
+  if (last <= BS - QCL) return 0;
+  *start = nb * BS - QCL;
+  return seqlen_q - *start;
+}
+
+int zp_sched_prefill_sizes(void* sched, const int32_t* handles, int n, int32_t out[4]) {
+  if (!sched || !out || (n > 0 && !handles)) return fail(ZP_SCHED_ERR_ARG, "zp_sched_prefill_sizes: null argument");
+  const Sched* s = S(sched);
+  int64_t tokens = 0, rows = 0;
+  int maxq = 0, maxk = 0;
+  for (int i = 0; i < n; ++i) {
+    if (bad_handle(s, handles[i])) return fail(ZP_SCHED_ERR_ARG, "zp_sched_prefill_sizes: bad handle %d", handles[i]);
+    const Seq& q = s->seqs[handles[i]];
+    const int lq = q.num_tokens - q.num_cached;
+    int start = 0;
+    tokens += lq;
+    rows += prefill_window_rows(s, q, lq, &start);
+    if (lq > maxq) maxq = lq;
+    if (q.num_tokens > maxk) maxk = q.num_tokens;
+  }
+  if (tokens > INT32_MAX) return fail(ZP_SCHED_ERR_ARG, "zp_sched_prefill_sizes: more than 2^31 tokens");
+  out[0] = (int32_t)tokens; out[1] = (int32_t)rows; out[2] = maxq; out[3] = maxk;
+  return 0;
+}
+
+int zp_sched_prefill_inputs(void* sched, const int32_t* handles, int n, int32_t* input_ids, int32_t* positions,
+                            int32_t* slot_mapping, int32_t* cu_seqlens_q, int32_t* cu_seqlens_k,
+                            int32_t* query_triples) {
+  if (!sched || (n > 0 && (!handles || !input_ids || !positions || !slot_mapping || !cu_seqlens_q || !cu_seqlens_k)))
+    return fail(ZP_SCHED_ERR_ARG, "zp_sched_prefill_inputs: null argument");
+  Sched* s = S(sched);
+  const int BS = s->cfg.block_size;
+  int64_t t = 0, rows = 0;
+  if (n > 0) { cu_seqlens_q[0] = 0; cu_seqlens_k[0] = 0; }
+  for (int i = 0; i < n; ++i) {
+    if (bad_handle(s, handles[i])) return fail(ZP_SCHED_ERR_ARG, "zp_sched_prefill_inputs: bad handle %d", handles[i]);
+    Seq& q = s->seqs[handles[i]];
+    const int len = q.num_tokens, cached = q.num_cached, lq = len - cached;
+    if (lq < 0 || (int)q.tokens.size() < len)
+      return fail(ZP_SCHED_ERR_STATE, "zp_sched_prefill_inputs: sequence %d holds %d tokens, %d cached", handles[i], len, cached);
+    int start = 0;
+    const int wr = prefill_window_rows(s, q, lq, &start);
+    if (wr > 0 && !query_triples) return fail(ZP_SCHED_ERR_ARG, "zp_sched_prefill_inputs: window rows but no triple array");
+    for (int k = 0; k < wr; ++k) {
+      int32_t* tr = query_triples + (rows + k) * 3;
+      tr[0] = (int32_t)(t + start + k); tr[1] = q.query_id; tr[2] = k;
+    }
+    rows += wr;
+    for (int k = 0; k < lq; ++k) { input_ids[t + k] = q.tokens[cached + k]; positions[t + k] = cached + k; }
+    // slots of the blocks that are not cached yet (model_runner.py:379-386)
+    const int nb = s->num_blocks(q), last = s->last_block_num_tokens(q);
+    if (!q.table.empty()) {
+      if ((int)q.table.size() < nb) return fail(ZP_SCHED_ERR_STATE, "zp_sched_prefill_inputs: sequence %d has %d blocks, needs %d", handles[i], (int)q.table.size(), nb);
+      int64_t w = t;
+      for (int b = cached / BS; b < nb; ++b) {
+        const int cnt = (b != nb - 1) ? BS : last;
+        const int32_t base = q.table[b] * BS;
+        for (int k = 0; k < cnt; ++k) slot_mapping[w++] = base + k;
+      }
+      if (w - t != lq) return fail(ZP_SCHED_ERR_STATE, "zp_sched_prefill_inputs: sequence %d: %d slots for %d tokens (cached tokens must be whole blocks)", handles[i], (int)(w - t), lq);
+      q.num_cached = len;          // model_runner.py:387
+    }
+    t += lq;
+    cu_seqlens_q[i + 1] = (int32_t)t;
+    cu_seqlens_k[i + 1] = cu_seqlens_k[i] + len;
+  }
+  return (int)rows;
 }
 
 int zp_sched_compress_due(void* sched, const int32_t* handles, int n, int32_t* out_handles) {

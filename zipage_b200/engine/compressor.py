@@ -66,8 +66,10 @@ class Compressor:
         return self._pin_i32, self._pin_u8
 
     # -- list-based variant -------------------------------------------------------------------
-    def compress_tables(self, tables, targets, query_ids, compressed, timed=False):
-        """tables: per-sequence page lists (plain ids, last entry = the page holding the window);
+    def compress_tables(self, tables, targets, query_ids, compressed, timed=False, encoded=False):
+        """tables: per-sequence page lists (plain ids, last entry = the page holding the window), or,
+        with `encoded`, the rectangular table already padded with -1 and with the last page written
+        as -(id)-2 (what the native scheduler's compress_inputs returns; arrays are fine);
         targets: per-sequence destination pages (budget+1 each).  Returns (new_tables, context_lens)
         as host lists read back from the device-side table update.  With `timed` the stages run
         as separate launches between CUDA events and `time_record` gets the reference's keys
@@ -75,7 +77,7 @@ class Compressor:
         B = len(tables)
         if B == 0:
             return [], []
-        enc = encode_block_tables(tables)
+        enc = tables if encoded else encode_block_tables(tables)
         nb, nt = len(enc[0]), len(targets[0])
         # one pinned block: [tables B*nb | targets B*nt | qids B | out: new tables B*nt | ctx B]
         o_t, o_g, o_q = 0, B * nb, B * nb + B * nt

@@ -384,6 +384,36 @@ class Scheduler:
         out["widest"] = widest
         return out
 
+    def prefill_inputs(self, handles):
+        """One prefill step's host arrays (model_runner.py:352-422): dict(input_ids, positions,
+        slot_mapping [new tokens], cu_seqlens_q, cu_seqlens_k [n + 1], query_triples [rows, 3],
+        max_seqlen_q, max_seqlen_k, block_tables or None).  `block_tables` ([n, widest], -1 padded)
+        is set when some sequence starts from cached prefix blocks, as in the reference.  Marks the
+        sequences prefilled."""
+        handles = np.ascontiguousarray(handles, dtype=np.int32)
+        n = len(handles)
+        sizes = (C.c_int32 * 4)()
+        H.check(self._lib.zp_sched_prefill_sizes(self._obj, _ptr(handles), n, sizes), "prefill_sizes")
+        tokens, rows = sizes[0], sizes[1]
+        out = {"input_ids": np.empty(max(tokens, 1), np.int32), "positions": np.empty(max(tokens, 1), np.int32),
+               "slot_mapping": np.empty(max(tokens, 1), np.int32), "cu_seqlens_q": np.zeros(n + 1, np.int32),
+               "cu_seqlens_k": np.zeros(n + 1, np.int32), "query_triples": np.empty((max(rows, 1), 3), np.int32)}
+        tables = None
+        width = (sizes[3] + self.block_size - 1) // self.block_size + 1
+        d = self.decode_inputs(handles, table_width=width)
+        self._epoch += 1
+        got = H.check(self._lib.zp_sched_prefill_inputs(
+            self._obj, _ptr(handles), n, _ptr(out["input_ids"]), _ptr(out["positions"]), _ptr(out["slot_mapping"]),
+            _ptr(out["cu_seqlens_q"]), _ptr(out["cu_seqlens_k"]), _ptr(out["query_triples"])), "prefill_inputs")
+        assert got == rows
+        for k in ("input_ids", "positions", "slot_mapping"):
+            out[k] = out[k][:tokens]
+        out["query_triples"] = out["query_triples"][:rows]
+        if n and out["cu_seqlens_k"][-1] > out["cu_seqlens_q"][-1]:
+            tables = d["block_tables"][:, :d["widest"]]
+        out.update(max_seqlen_q=sizes[2], max_seqlen_k=sizes[3], block_tables=tables)
+        return out
+
     def compress_due(self, handles):
         """The handles among `handles` whose sequence waits for a compression (int32 array)."""
         handles = np.ascontiguousarray(handles, dtype=np.int32)
