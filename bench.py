@@ -50,7 +50,7 @@ def parse_args():
                     help="also run the reference ENGINE (baseline/_ref) on a synthetic Qwen3-8B-shaped model, as it "
                          "is and with this library's decode path bound, and report decode tokens/s (adds minutes)")
     ap.add_argument("--also-exact", action="store_true", help="time the exact variant as well")
-    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops", "prefill", "decode_step", "tp_allreduce", "engine_decode", "long_prompt", "host_control"],
+    ap.add_argument("--workload", default="compress", choices=["compress", "decode", "step_ops", "prefill", "decode_step", "tp_allreduce", "engine_decode", "long_prompt", "host_control", "native_engine"],
                     help="compress (default, the headline op), decode (paged decode attention kernel) or "
                          "step_ops (the element-wise ops of a decoder layer step and the sampler) or "
                          "prefill (varlen causal prefill attention, one layer) or decode_step (the decode "
@@ -60,6 +60,7 @@ def parse_args():
     ap.add_argument("--verbose", action="store_true", help="progress lines on stderr")
     ap.add_argument("--engine-modes", default="reference,kernels,graph",
                     help="modes of the engine_decode workload (tests/ref_engine.py): reference, kernels, full, graph, native")
+    ap.add_argument("--engine-requests", type=int, default=192, help="concurrent requests of the native_engine workload")
     ap.add_argument("--requests", type=int, default=2048, help="concurrent requests of the host_control workload")
     ap.add_argument("--tokens", type=int, default=32768, help="tokens per call of the step_ops workload")
     return ap.parse_args()
@@ -941,6 +942,92 @@ def run_prefill(args):
     }))
 
 
+def run_native_engine(args):
+    """Decode tokens/s through the serving loop built from this library only
+    (zipage_b200/engine/native_engine.py): same workload and accounting as the engine_decode
+    workload (Qwen3-8B shapes, random-init bf16, `--engine-requests` concurrent requests with
+    2300-token prompts, 600 sampled tokens each at temperature 0.6, budget 8 pages, lightning
+    redundancy + pooling; decode tokens over decode_sum + compress_sum).  Under torchrun the loop
+    runs tensor-parallel: every rank its own scheduler replica, all-reduces over peer memory,
+    sampling over the sharded vocabulary."""
+    import torch
+    from types import SimpleNamespace
+    from zipage_b200.compress import CompressConfig
+    from zipage_b200.engine.native_engine import NativeEngine
+    from zipage_b200.engine.scheduler import SamplingParams, Sequence
+    from zipage_b200.layers.qwen3_block import Qwen3Model
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    comm, rank = None, 0
+    R, PROMPT, GEN = args.engine_requests, 2300, 600
+    if world > 1:
+        import torch.distributed as dist
+        from zipage_b200.layers.tp_comm import TPCommunicator
+        dist.init_process_group("nccl", device_id=dev)
+        rank = dist.get_rank()
+        comm = TPCommunicator(max_bytes=256 * 4096 * 2, timeout_ms=2000, large_messages="library")
+    Ln = min(args.layers, 36)
+    cfg = SimpleNamespace(hidden_size=4096, num_attention_heads=HQ, num_key_value_heads=HKV, head_dim=D,
+                          intermediate_size=12288, hidden_act="silu", rms_norm_eps=1e-6, vocab_size=151936,
+                          num_hidden_layers=Ln, max_position_embeddings=40960, rope_theta=1e6)
+    torch.manual_seed(1)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(dev):
+            model = Qwen3Model(cfg, comm).eval()
+    finally:
+        torch.set_default_dtype(prev)
+    pages = R * (BUDGET + 2) + 64
+    kv = torch.zeros((2, Ln, pages, BS, HKV // world, D), dtype=torch.bfloat16, device=dev)
+    qc = torch.zeros((Ln, R, QCL, HQ // world, D), dtype=torch.bfloat16, device=dev)
+    model.bind_caches(kv, qc)
+    lm_head = torch.empty((cfg.vocab_size // world, cfg.hidden_size), dtype=torch.bfloat16, device=dev).normal_(0, 0.02)
+    sched_cfg = SimpleNamespace(max_num_seqs=R, max_num_batched_tokens=32768, eos=-1, num_kvcache_blocks=pages,
+                                kvcache_block_size=BS, max_cache_blocks_per_seq=BUDGET, enable_prefix_cache=False,
+                                max_concurrency=R, enable_hybrid_engine=False, query_cache_len=QCL)
+    ccfg = CompressConfig(budget_blocks=BUDGET, query_cache_len=QCL, use_redudancy=True, lightning_redudancy=True,
+                          redudancy_lambda=0.5, enable_pooling=True)
+    eng = NativeEngine(model, lm_head, kv, qc, sched_cfg, ccfg, cfg.hidden_size, comm=comm, max_bs=R,
+                       max_model_len=4096, greedy=False)
+    g = torch.Generator().manual_seed(1)
+    sp = SamplingParams(0.6, GEN, True)
+
+    def requests(n, length, max_tokens):
+        return [Sequence(torch.randint(2, cfg.vocab_size, (length,), generator=g).tolist(),
+                         SamplingParams(0.6, max_tokens, True)) for _ in range(n)]
+    eng.generate(requests(4, (BUDGET + 1) * BS - 4, 8))      # warm-up across one compression
+    eng.time_record.clear()
+    torch.cuda.synchronize()
+    with ClockSampler(dev.index or 0) as clocks:
+        t0 = time.perf_counter()
+        out = eng.generate(requests(R, PROMPT, GEN))
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+    tr = eng.time_record
+    gen = sum(len(v) for v in out.values())
+    decode_s = tr["decode_sum"] + tr["compress_sum"]
+    status = comm.status() if comm is not None else 0
+    if rank == 0:
+        print(json.dumps({
+            "metric": "engine_decode_tokens_per_s", "value": tr["decode_tokens"] / decode_s, "unit": "tokens/s",
+            "n_gpus": world, "steps": int(tr["decode_tokens"] // R), "warmup": 1, "ms_per_step": decode_s / (tr["decode_tokens"] / R) * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"own serving loop, Qwen3-8B shapes ({Ln} blocks), random-init bf16, {R} concurrent requests, "
+                                   f"prompts of {PROMPT} uniform-random ids, {GEN} sampled tokens each, budget {BUDGET} x {BS}, "
+                                   "lightning redundancy + pooling", "parallelism": f"tp{world}"},
+            "decode_tokens": int(tr["decode_tokens"]), "decode_s": tr["decode_sum"], "compress_s": tr["compress_sum"],
+            "compressions": int(tr["compress_reqs"]), "prefill_tokens_per_s": R * PROMPT / tr["prefill_sum"],
+            "decode_tokens_per_s_excluding_compress": tr["decode_tokens"] / tr["decode_sum"],
+            "wall_s": wall, "generated_tokens": gen, "generated_tokens_per_wall_s": gen / wall,
+            "comm_status": status, "clocks": clocks.summary(),
+        }))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_host_control(args):
     """Host time per decode step of the control plane at `--requests` concurrent requests: the
     native scheduler's array calls (schedule, the runner's input arrays, postprocess) and, when an
@@ -1049,6 +1136,8 @@ def main():
         return run_reference(args)
     if args.workload == "host_control":
         return run_host_control(args)
+    if args.workload == "native_engine":
+        return run_native_engine(args)
     if args.workload == "prefill":
         return run_prefill(args)
     if args.workload == "decode":

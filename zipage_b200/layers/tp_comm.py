@@ -22,10 +22,13 @@ ALGO = {"auto": 0, "one_shot": 1, "two_shot": 2, "flagged_lines": 3}
 
 
 class TPCommunicator:
-    def __init__(self, group=None, max_bytes=8 << 20, timeout_ms=10000, device=None):
-        """One per (process group, stream of use).  `max_bytes`: the largest message.  Every rank
-        of `group` must sit on its own GPU of one node."""
+    def __init__(self, group=None, max_bytes=8 << 20, timeout_ms=10000, device=None, large_messages=None):
+        """One per (process group, stream of use).  `max_bytes`: the largest message of the
+        peer-memory kernels.  Every rank of `group` must sit on its own GPU of one node.
+        `large_messages="library"`: messages above `max_bytes` (prefill batches) take the
+        `torch.distributed` route instead of failing."""
         self.group = group
+        self.large = LibraryCommunicator(group) if large_messages == "library" else None
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.max_bytes = max_bytes
@@ -49,6 +52,8 @@ class TPCommunicator:
         `out` is None, as dist.all_reduce."""
         L.require_cuda(x, out)
         assert x.is_contiguous() and (out is None or (out.is_contiguous() and out.shape == x.shape))
+        if self.large is not None and x.numel() * x.element_size() > self.max_bytes:
+            return self.large.all_reduce(x, out)
         out = x if out is None else out
         L.check(L.load().zp_all_reduce(self._h, L.ptr(x), L.ptr(out), x.numel(), L.dtype_code(x), ALGO[algo],
                                        L.stream_ptr()), "all_reduce")
@@ -58,6 +63,8 @@ class TPCommunicator:
     def all_reduce_add_rms_norm(self, x, residual, weight, eps, algo="auto"):
         """(RMSNorm(all_reduce(x) + residual) * weight, all_reduce(x) + residual)."""
         L.require_cuda(x, residual, weight)
+        if self.large is not None and x.numel() * x.element_size() > self.max_bytes:
+            return self.large.all_reduce_add_rms_norm(x, residual, weight, eps)
         H = x.shape[-1]
         x2, r2 = x.reshape(-1, H), residual.reshape(-1, H)
         assert x2.is_contiguous() and r2.is_contiguous() and weight.is_contiguous()
