@@ -46,6 +46,7 @@ def parse_args():
     ap.add_argument("--kernel-impl", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-step record of the default run")
+    ap.add_argument("--no-serving-loop", action="store_true", help="skip the serving-loop record of the default run")
     ap.add_argument("--engine", action="store_true",
                     help="also run the reference ENGINE (baseline/_ref) on a synthetic Qwen3-8B-shaped model, as it "
                          "is and with this library's decode path bound, and report decode tokens/s (adds minutes)")
@@ -942,7 +943,7 @@ def run_prefill(args):
     }))
 
 
-def run_native_engine(args):
+def native_engine_record(args, own_group=True):
     """Decode tokens/s through the serving loop built from this library only
     (zipage_b200/engine/native_engine.py): same workload and accounting as the engine_decode
     workload (Qwen3-8B shapes, random-init bf16, `--engine-requests` concurrent requests with
@@ -964,7 +965,8 @@ def run_native_engine(args):
     if world > 1:
         import torch.distributed as dist
         from zipage_b200.layers.tp_comm import TPCommunicator
-        dist.init_process_group("nccl", device_id=dev)
+        if own_group:
+            dist.init_process_group("nccl", device_id=dev)
         rank = dist.get_rank()
         comm = TPCommunicator(max_bytes=256 * 4096 * 2, timeout_ms=2000, large_messages="library")
     Ln = min(args.layers, 36)
@@ -1009,8 +1011,9 @@ def run_native_engine(args):
     gen = sum(len(v) for v in out.values())
     decode_s = tr["decode_sum"] + tr["compress_sum"]
     status = comm.status() if comm is not None else 0
+    rec = None
     if rank == 0:
-        print(json.dumps({
+        rec = {
             "metric": "engine_decode_tokens_per_s", "value": tr["decode_tokens"] / decode_s, "unit": "tokens/s",
             "n_gpus": world, "steps": int(tr["decode_tokens"] // R), "warmup": 1, "ms_per_step": decode_s / (tr["decode_tokens"] / R) * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -1022,8 +1025,18 @@ def run_native_engine(args):
             "decode_tokens_per_s_excluding_compress": tr["decode_tokens"] / tr["decode_sum"],
             "wall_s": wall, "generated_tokens": gen, "generated_tokens_per_wall_s": gen / wall,
             "comm_status": status, "clocks": clocks.summary(),
-        }))
-    if world > 1:
+        }
+    if comm is not None:
+        comm.close()
+    return rec
+
+
+def run_native_engine(args):
+    rec = native_engine_record(args, own_group=True)
+    if rec is not None:
+        print(json.dumps(rec))
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()
 
@@ -1358,7 +1371,7 @@ def main():
     # The other half of the metric: decode tokens/s at the 2048-token budget.  The compression
     # workload is released first; the decode step (full depth, tensor-parallel over the ranks
     # when there are several) then runs in this same process and process group.
-    decode = None
+    decode = serving = None
     if not args.no_decode:
         del w, comp, fresh, last_pages
         small = xcomp = None
@@ -1373,6 +1386,15 @@ def main():
             decode = decode_step_record(d_args, own_group=False)
         except Exception as e:   # the headline line must still come out
             decode = {"unavailable": f"{type(e).__name__}: {e}"[:300]} if rank == 0 else None
+        # ... and the same through a whole serving loop (scheduler, prefill, graph decode,
+        # compressions when they fall due, sampler), tensor-parallel under torchrun
+        if not args.no_serving_loop:
+            gc.collect()
+            torch.cuda.empty_cache()
+            try:
+                serving = native_engine_record(d_args, own_group=False)
+            except Exception as e:
+                serving = {"unavailable": f"{type(e).__name__}: {e}"[:300]} if rank == 0 else None
 
     if rank == 0:
         peaks = {}
@@ -1453,6 +1475,8 @@ def main():
         }
         if decode is not None:
             line["decode"] = decode
+        if serving is not None:
+            line["serving_loop"] = serving
         if args.engine and world == 1:
             line["engine_decode"] = engine_decode_records()
         if eng is not None:
