@@ -29,7 +29,7 @@ SHAPE = dict(layers=4, hidden=1024, inter=2048, hq=8, hkv=2, vocab=2048, seed=0)
 MODEL_DIR = Path("/tmp/zp_synth_model")      # the directory tests/ref_engine.py writes by default
 
 
-def _engine(graph, greedy=True, max_bs=16):
+def _engine(graph, greedy=True, max_bs=16, prefix_cache=False):
     from safetensors.torch import load_file
     from zipage_b200.compress import CompressConfig
     from zipage_b200.engine.native_engine import NativeEngine, full_state_from_hf
@@ -56,7 +56,7 @@ def _engine(graph, greedy=True, max_bs=16):
     qc = torch.zeros((SHAPE["layers"], slots, 16, SHAPE["hq"], 128), dtype=torch.bfloat16, device=dev)
     model.bind_caches(kv, qc)
     sched_cfg = types.SimpleNamespace(max_num_seqs=16, max_num_batched_tokens=32768, eos=1, num_kvcache_blocks=blocks,
-                                      kvcache_block_size=256, max_cache_blocks_per_seq=2, enable_prefix_cache=False,
+                                      kvcache_block_size=256, max_cache_blocks_per_seq=2, enable_prefix_cache=prefix_cache,
                                       max_concurrency=slots, enable_hybrid_engine=False, query_cache_len=16)
     ccfg = CompressConfig(budget_blocks=2, query_cache_len=16, use_redudancy=True, lightning_redudancy=True,
                           redudancy_lambda=0.5, enable_pooling=True)
@@ -114,12 +114,17 @@ def test_native_engine_against_the_reference_engine(tmp_path):
     assert c[7] == 1 and c[3] == 0                                   # finished, every block returned
 
 
-def test_graph_replay_and_launch_by_launch_give_the_same_tokens():
-    if not MODEL_DIR.exists():
+def _ensure_model():
+    tag = "-".join(str(SHAPE[k]) for k in ("layers", "hidden", "inter", "hq", "hkv", "vocab", "seed"))
+    if not (MODEL_DIR / "tag").exists() or (MODEL_DIR / "tag").read_text() != tag:
         sys.path.insert(0, str(ROOT / "tests"))
         import ref_engine
         ref_engine.make_model_dir(MODEL_DIR, **SHAPE)
-        (MODEL_DIR / "tag").write_text("-".join(str(SHAPE[k]) for k in ("layers", "hidden", "inter", "hq", "hkv", "vocab", "seed")))
+        (MODEL_DIR / "tag").write_text(tag)
+
+
+def test_graph_replay_and_launch_by_launch_give_the_same_tokens():
+    _ensure_model()
     runs = []
     for graph in (True, False):
         eng = _engine(graph=graph)
@@ -128,3 +133,45 @@ def test_graph_replay_and_launch_by_launch_give_the_same_tokens():
         runs.append([got[s._h] for s in seqs])
         assert eng.time_record["compress_reqs"] == 3 and all(len(t) == STEPS for t in runs[-1])
     assert runs[0] == runs[1]
+
+
+def test_prefix_cache_reuses_pages_and_gives_the_same_tokens():
+    """Requests that share a 512-token prefix: with the prefix cache the later ones start from
+    the first one's pages (prefill over the paged keys, zipage/layers/attention.py:82-93 with
+    block_table), without it every prompt is recomputed.  The cached run is fed the plain run's
+    tokens; its own arg-max must agree wherever the plain run's top-2 margin is above tolerance."""
+    _ensure_model()
+    g = torch.Generator().manual_seed(7)
+    shared = torch.randint(2, SHAPE["vocab"], (512,), generator=g).tolist()
+    prompts = [shared + torch.randint(2, SHAPE["vocab"], (n,), generator=g).tolist() for n in (90, 140, 200)]
+    plain = _engine(graph=True)
+    plain.argmax_log = []
+    seqs = _requests(prompts)
+    out = plain.generate(seqs)
+    want = [out[s._h] for s in seqs]
+
+    cached = _engine(graph=True, prefix_cache=True)
+    reused = []
+    real_prefill = cached._prefill
+
+    def spy(handles):
+        reused.extend(int(cached.scheduler._seqs[h].num_cached_tokens) for h in handles.tolist())
+        return real_prefill(handles)
+    cached._prefill = spy
+    cached.forced = iter([s["tokens"] for s in plain.argmax_log])
+    cached.argmax_log = []
+    seqs2 = _requests(prompts)
+    got = cached.generate(seqs2)
+    have = [got[s._h] for s in seqs2]
+    first = [next((i for i, (a, b) in enumerate(zip(x, y)) if a != b), None) for x, y in zip(have, want)]
+    sizes = ([len(s["tokens"]) for s in plain.argmax_log], [len(s["tokens"]) for s in cached.argmax_log])
+    assert have == want, (first, [len(x) for x in have], sizes[0][:4], sizes[1][:4], len(sizes[0]), len(sizes[1]))
+    assert sorted(reused) == [0, 512, 512]            # two of the three started from the shared pages
+    mism = unexplained = 0
+    for a, b in zip(plain.argmax_log, cached.argmax_log):
+        for ta, tb, m, sp in zip(a["tokens"], b["tokens"], a["margin"], a["spread"]):
+            if ta != tb:
+                mism += 1
+                unexplained += m > 2e-2 * sp
+    print(f"prefix cache: own arg-max differs on {mism} of {3 * STEPS} tokens, {unexplained} above the margin")
+    assert unexplained == 0 and mism <= 0.05 * 3 * STEPS

@@ -89,7 +89,7 @@ class NativeEngine:
         if self.argmax_log is not None:
             lf = logits.float()
             top = lf.topk(2, dim=-1)
-            self.argmax_log.append({"tokens": top.indices[:, 0].tolist(),
+            self.argmax_log.append({"tokens": logits.argmax(dim=-1).tolist(),   # what `greedy` emits
                                     "margin": (top.values[:, 0] - top.values[:, 1]).tolist(),
                                     "spread": (lf.max(dim=-1).values - lf.min(dim=-1).values).tolist()})
         if self.forced is not None:
