@@ -175,3 +175,16 @@ def test_prefix_cache_reuses_pages_and_gives_the_same_tokens():
                 unexplained += m > 2e-2 * sp
     print(f"prefix cache: own arg-max differs on {mism} of {3 * STEPS} tokens, {unexplained} above the margin")
     assert unexplained == 0 and mism <= 0.05 * 3 * STEPS
+
+
+def test_tensor_parallel_loop_against_the_single_gpu_loop(world=2):
+    """tests/native_engine_tp_worker.py under torch.distributed.run: one scheduler replica per rank,
+    all-reduces over peer memory, prefill batches through the library route."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    r = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+         "--master-addr", "127.0.0.1", "--master-port", str(29700 + world),
+         str(ROOT / "tests" / "native_engine_tp_worker.py")], capture_output=True, text=True, timeout=900)
+    print(r.stdout[-600:])
+    assert r.returncode == 0 and "TP_ENGINE_OK" in r.stdout, (r.stdout + r.stderr)[-3000:]
