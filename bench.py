@@ -62,6 +62,9 @@ def parse_args():
     ap.add_argument("--engine-modes", default="reference,kernels,graph",
                     help="modes of the engine_decode workload (tests/ref_engine.py): reference, kernels, full, graph, native")
     ap.add_argument("--engine-requests", type=int, default=192, help="concurrent requests of the native_engine workload")
+    ap.add_argument("--engine-prompt", type=int, default=2300, help="prompt tokens per request (native_engine)")
+    ap.add_argument("--engine-gen", type=int, default=600, help="generated tokens per request (native_engine)")
+    ap.add_argument("--engine-prefix-cache", action="store_true", help="prefix cache on (native_engine)")
     ap.add_argument("--requests", type=int, default=2048, help="concurrent requests of the host_control workload")
     ap.add_argument("--tokens", type=int, default=32768, help="tokens per call of the step_ops workload")
     return ap.parse_args()
@@ -961,7 +964,7 @@ def native_engine_record(args, own_group=True):
     torch.cuda.set_device(dev)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     comm, rank = None, 0
-    R, PROMPT, GEN = args.engine_requests, 2300, 600
+    R, PROMPT, GEN = args.engine_requests, args.engine_prompt, args.engine_gen
     if world > 1:
         import torch.distributed as dist
         from zipage_b200.layers.tp_comm import TPCommunicator
@@ -982,12 +985,18 @@ def native_engine_record(args, own_group=True):
     finally:
         torch.set_default_dtype(prev)
     pages = R * (BUDGET + 2) + 64
+    lm_head = torch.empty((cfg.vocab_size // world, cfg.hidden_size), dtype=torch.bfloat16, device=dev).normal_(0, 0.02)
+    # no more pages than fit beside the weights (the scheduler then admits and preempts as the
+    # reference's does when blocks run out)
+    page_bytes = 2 * Ln * BS * (HKV // world) * D * 2
+    free = torch.cuda.mem_get_info(dev)[0] - R * Ln * QCL * (HQ // world) * D * 2 - (32 << 30)
+    pages = max(R * 3, min(pages, int(free // page_bytes)))
     kv = torch.zeros((2, Ln, pages, BS, HKV // world, D), dtype=torch.bfloat16, device=dev)
     qc = torch.zeros((Ln, R, QCL, HQ // world, D), dtype=torch.bfloat16, device=dev)
     model.bind_caches(kv, qc)
-    lm_head = torch.empty((cfg.vocab_size // world, cfg.hidden_size), dtype=torch.bfloat16, device=dev).normal_(0, 0.02)
     sched_cfg = SimpleNamespace(max_num_seqs=R, max_num_batched_tokens=32768, eos=-1, num_kvcache_blocks=pages,
-                                kvcache_block_size=BS, max_cache_blocks_per_seq=BUDGET, enable_prefix_cache=False,
+                                kvcache_block_size=BS, max_cache_blocks_per_seq=BUDGET,
+                                enable_prefix_cache=bool(args.engine_prefix_cache),
                                 max_concurrency=R, enable_hybrid_engine=False, query_cache_len=QCL)
     ccfg = CompressConfig(budget_blocks=BUDGET, query_cache_len=QCL, use_redudancy=True, lightning_redudancy=True,
                           redudancy_lambda=0.5, enable_pooling=True)
@@ -1019,7 +1028,8 @@ def native_engine_record(args, own_group=True):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"own serving loop, Qwen3-8B shapes ({Ln} blocks), random-init bf16, {R} concurrent requests, "
                                    f"prompts of {PROMPT} uniform-random ids, {GEN} sampled tokens each, budget {BUDGET} x {BS}, "
-                                   "lightning redundancy + pooling", "parallelism": f"tp{world}"},
+                                   "lightning redundancy + pooling", "parallelism": f"tp{world}",
+                       "kv_pages": pages, "prefix_cache": bool(args.engine_prefix_cache)},
             "decode_tokens": int(tr["decode_tokens"]), "decode_s": tr["decode_sum"], "compress_s": tr["compress_sum"],
             "compressions": int(tr["compress_reqs"]), "prefill_tokens_per_s": R * PROMPT / tr["prefill_sum"],
             "decode_tokens_per_s_excluding_compress": tr["decode_tokens"] / tr["decode_sum"],
