@@ -12,7 +12,9 @@
  * Plain host code: no CUDA call, no device pointer.  Sequences are addressed by the handle
  * zp_sched_add() returns (a small non-negative integer, never reused).  Every function returns
  * a count or 0 on success and a negative ZP_SCHED_ERR_* code on failure; zp_sched_last_error()
- * holds the message.  A scheduler object is not thread safe.
+ * holds the message (per thread).  Every call on a scheduler object takes that object's lock, so
+ * calls from two threads are serialised (the reference engine's asynchronous mode calls
+ * postprocess from its compression thread, zipage_engine.py:88-96).
  */
 #ifndef ZIPAGE_B200_HOST_H
 #define ZIPAGE_B200_HOST_H
@@ -61,10 +63,10 @@ int zp_sched_schedule(void* sched, int32_t* out_handles, int capacity, int32_t* 
 
 /* Scheduler.postprocess(seqs, token_ids) (scheduler.py:143-167); token_ids may be null (the
  * call after a compression).  `now` is the wall-clock time stored as time_prefilled /
- * time_finished.  Returns how many of the sequences finished in this call;
- * zp_sched_last_finished() lists them (returns the count, writes only when it fits). */
-int zp_sched_postprocess(void* sched, const int32_t* handles, int n, const int32_t* token_ids, double now);
-int zp_sched_last_finished(void* sched, int32_t* out, int capacity);
+ * time_finished.  Returns how many of the sequences finished in this call and writes their
+ * handles to finished_out (room for n; may be null). */
+int zp_sched_postprocess(void* sched, const int32_t* handles, int n, const int32_t* token_ids, double now,
+                         int32_t* finished_out);
 
 /* Scheduler.preempt(seq) (scheduler.py:136-141). */
 int zp_sched_preempt(void* sched, int handle);

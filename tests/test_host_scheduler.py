@@ -269,3 +269,44 @@ def test_prefill_inputs_equal_the_reference_list_building(prefix_cache):
         seen_rows += len(want[3])
         s.postprocess(seqs, [1] * len(seqs))
     assert batches >= 2 and seen_rows > 0 and (seen_cached > 0) == prefix_cache
+
+
+def test_calls_from_a_second_thread_are_serialised():
+    """The reference engine's asynchronous mode touches the scheduler from its compression thread
+    (zipage_engine.py:88-96).  A second thread reads queues, counters and sequence state as fast as
+    it can while the main thread runs a whole scenario: the run must end in the golden state."""
+    import threading
+    stop = threading.Event()
+    seen = []
+    holder = {}
+
+    class Watched(Scheduler):
+        def __init__(self, config):
+            super().__init__(config)
+            holder["s"] = self
+
+    def reader():
+        n = 0
+        while not stop.is_set():
+            s = holder.get("s")
+            if s is None:
+                continue
+            c = s.counts()
+            s._queue(1), s._queue(2), s._queue(3)
+            for q in list(s._seqs)[:8]:
+                q._cache.clear()
+                _ = (q.num_tokens, q.block_table)
+            assert c[2] + c[3] == s._cfg.num_blocks        # a consistent snapshot: free + used = all
+            n += 1
+        seen.append(n)
+
+    t = threading.Thread(target=reader)
+    t.start()
+    try:
+        steps, marks, raised = _fold(T.run_trace(Watched, Sequence, SamplingParams, "prefix_cache_tight", seed=0,
+                                                 max_steps=3000))
+    finally:
+        stop.set()
+        t.join()
+    want = GOLDEN["traces"]["prefix_cache_tight"]
+    assert marks == want["marks"] and steps == want["steps"] and seen and seen[0] > 100

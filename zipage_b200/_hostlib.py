@@ -29,8 +29,7 @@ SIGNATURES = {
     "zp_sched_destroy": (None, [_P]),
     "zp_sched_add": (_I, [_P, _P, _I, C.c_float, _I, _I]),
     "zp_sched_schedule": (_I, [_P, _P, _I, _P]),
-    "zp_sched_postprocess": (_I, [_P, _P, _I, _P, _D]),
-    "zp_sched_last_finished": (_I, [_P, _P, _I]),
+    "zp_sched_postprocess": (_I, [_P, _P, _I, _P, _D, _P]),
     "zp_sched_preempt": (_I, [_P, _I]),
     "zp_sched_mark_prefilled": (_I, [_P, _P, _I]),
     "zp_sched_release": (_I, [_P, _I]),

@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <cstring>
 #include <deque>
+#include <mutex>
 #include <unordered_map>
 #include <vector>
 
@@ -122,6 +123,10 @@ struct Sched {
   int32_t used_qids = 0;
   std::unordered_map<uint64_t, int32_t> hash_to_block;
   std::vector<int32_t> last_finished;   // handles that finished in the latest postprocess call
+  // The reference engine's asynchronous mode calls postprocess() from its compression thread
+  // while the main thread schedules (zipage_engine.py:88-96, :137-186); Python's interpreter lock
+  // serialises its own objects, a foreign call releases that lock, so every entry point locks here.
+  std::mutex mu;
 
   // ---- Sequence properties (sequence.py:62-76) ----
   int num_blocks(const Seq& s) const { return (s.num_tokens + cfg.block_size - 1) / cfg.block_size; }
@@ -476,6 +481,13 @@ static int copy_out(const std::vector<int32_t>& v, int32_t* out, int capacity) {
   return (int)v.size();
 }
 
+static void seq_info_unlocked(const Seq& q, int32_t* out) {
+  const int32_t v[16] = {q.status, q.num_tokens, q.num_prompt, q.num_cached, q.last_token, q.query_id,
+                         q.require_compress, q.compressed, q.prefilled, q.max_tokens, q.ignore_eos,
+                         (int32_t)q.table.size(), (int32_t)q.new_table.size(), (int32_t)q.to_release.size(), 0, 0};
+  memcpy(out, v, sizeof(v));
+}
+
 extern "C" {
 
 const char* zp_sched_last_error(void) { return zp::host::g_err; }
@@ -499,6 +511,8 @@ void zp_sched_destroy(void* sched) { delete S(sched); }
 
 int zp_sched_add(void* sched, const int32_t* token_ids, int n_tokens, float temperature, int max_tokens,
                  int ignore_eos) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || !token_ids || n_tokens < 1) return fail(ZP_SCHED_ERR_ARG, "zp_sched_add: null argument or empty prompt");
   Sched* s = S(sched);
   s->seqs.emplace_back();
@@ -516,21 +530,25 @@ int zp_sched_add(void* sched, const int32_t* token_ids, int n_tokens, float temp
 }
 
 int zp_sched_schedule(void* sched, int32_t* out_handles, int capacity, int32_t* is_prefill) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || !out_handles || !is_prefill) return fail(ZP_SCHED_ERR_ARG, "zp_sched_schedule: null argument");
   return S(sched)->schedule(out_handles, capacity, is_prefill);
 }
 
-int zp_sched_postprocess(void* sched, const int32_t* handles, int n, const int32_t* token_ids, double now) {
+int zp_sched_postprocess(void* sched, const int32_t* handles, int n, const int32_t* token_ids, double now,
+                         int32_t* finished_out) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || (n > 0 && !handles)) return fail(ZP_SCHED_ERR_ARG, "zp_sched_postprocess: null argument");
-  return S(sched)->postprocess(handles, n, token_ids, now);
-}
-
-int zp_sched_last_finished(void* sched, int32_t* out, int capacity) {
-  if (!sched) return fail(ZP_SCHED_ERR_ARG, "zp_sched_last_finished: null argument");
-  return copy_out(S(sched)->last_finished, out, capacity);
+  const int done = S(sched)->postprocess(handles, n, token_ids, now);
+  if (done > 0 && finished_out) memcpy(finished_out, S(sched)->last_finished.data(), sizeof(int32_t) * done);
+  return done;
 }
 
 int zp_sched_preempt(void* sched, int handle) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || bad_handle(S(sched), handle)) return fail(ZP_SCHED_ERR_ARG, "zp_sched_preempt: bad handle");
   Sched* s = S(sched);
   Seq& q = s->seqs[handle];
@@ -541,6 +559,8 @@ int zp_sched_preempt(void* sched, int handle) {
 }
 
 int zp_sched_mark_prefilled(void* sched, const int32_t* handles, int n) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || (n > 0 && !handles)) return fail(ZP_SCHED_ERR_ARG, "zp_sched_mark_prefilled: null argument");
   Sched* s = S(sched);
   for (int i = 0; i < n; ++i) {
@@ -551,6 +571,8 @@ int zp_sched_mark_prefilled(void* sched, const int32_t* handles, int n) {
 }
 
 int zp_sched_release(void* sched, int handle) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || bad_handle(S(sched), handle)) return fail(ZP_SCHED_ERR_ARG, "zp_sched_release: bad handle");
   Seq& q = S(sched)->seqs[handle];
   if (q.status != ZP_SEQ_FINISHED) return fail(ZP_SCHED_ERR_STATE, "zp_sched_release: sequence %d is not finished", handle);
@@ -559,6 +581,8 @@ int zp_sched_release(void* sched, int handle) {
 }
 
 int zp_sched_counts(void* sched, int32_t out[8]) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || !out) return fail(ZP_SCHED_ERR_ARG, "zp_sched_counts: null argument");
   const Sched* s = S(sched);
   out[0] = s->waiting.count; out[1] = s->running.count;
@@ -570,25 +594,26 @@ int zp_sched_counts(void* sched, int32_t out[8]) {
 }
 
 int zp_sched_seq_info(void* sched, int handle, int32_t out[16]) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || !out || bad_handle(S(sched), handle)) return fail(ZP_SCHED_ERR_ARG, "zp_sched_seq_info: bad argument");
-  const Seq& q = S(sched)->seqs[handle];
-  const int32_t v[16] = {q.status, q.num_tokens, q.num_prompt, q.num_cached, q.last_token, q.query_id,
-                         q.require_compress, q.compressed, q.prefilled, q.max_tokens, q.ignore_eos,
-                         (int32_t)q.table.size(), (int32_t)q.new_table.size(), (int32_t)q.to_release.size(), 0, 0};
-  memcpy(out, v, sizeof(v));
+  seq_info_unlocked(S(sched)->seqs[handle], out);
   return 0;
 }
 
 int zp_sched_seq_info_batch(void* sched, const int32_t* handles, int n, int32_t* out) {
   if (!sched || (n > 0 && (!handles || !out))) return fail(ZP_SCHED_ERR_ARG, "zp_sched_seq_info_batch: null argument");
+  std::unique_lock<std::mutex> lock_(S(sched)->mu);
   for (int i = 0; i < n; ++i) {
-    const int rc = zp_sched_seq_info(sched, handles[i], out + (size_t)i * 16);
-    if (rc < 0) return rc;
+    if (bad_handle(S(sched), handles[i])) return fail(ZP_SCHED_ERR_ARG, "zp_sched_seq_info_batch: bad handle %d", handles[i]);
+    seq_info_unlocked(S(sched)->seqs[handles[i]], out + (size_t)i * 16);
   }
   return 0;
 }
 
 int zp_sched_seq_times(void* sched, int handle, double times[2], float* temperature) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || !times || bad_handle(S(sched), handle)) return fail(ZP_SCHED_ERR_ARG, "zp_sched_seq_times: bad argument");
   const Seq& q = S(sched)->seqs[handle];
   times[0] = q.time_prefilled; times[1] = q.time_finished;
@@ -597,12 +622,16 @@ int zp_sched_seq_times(void* sched, int handle, double times[2], float* temperat
 }
 
 int zp_sched_seq_set_num_cached(void* sched, int handle, int num_cached_tokens) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || bad_handle(S(sched), handle)) return fail(ZP_SCHED_ERR_ARG, "zp_sched_seq_set_num_cached: bad handle");
   S(sched)->seqs[handle].num_cached = num_cached_tokens;
   return 0;
 }
 
 int zp_sched_seq_list(void* sched, int handle, int which, int32_t* out, int capacity) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || bad_handle(S(sched), handle) || which < 0 || which > 3)
     return fail(ZP_SCHED_ERR_ARG, "zp_sched_seq_list: bad argument");
   const Seq& q = S(sched)->seqs[handle];
@@ -610,6 +639,8 @@ int zp_sched_seq_list(void* sched, int handle, int which, int32_t* out, int capa
 }
 
 int zp_sched_queue(void* sched, int which, int32_t* out, int capacity) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || which < 0 || which > 3) return fail(ZP_SCHED_ERR_ARG, "zp_sched_queue: bad argument");
   const Sched* s = S(sched);
   if (which == 3) {
@@ -627,6 +658,8 @@ int zp_sched_queue(void* sched, int which, int32_t* out, int capacity) {
 }
 
 int zp_sched_block_info(void* sched, int block_id, int32_t out[2], uint64_t* hash) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || !out || block_id < 0 || block_id >= (int)S(sched)->blocks.size())
     return fail(ZP_SCHED_ERR_ARG, "zp_sched_block_info: bad argument");
   const zp::host::Block& b = S(sched)->blocks[block_id];
@@ -642,6 +675,8 @@ uint64_t zp_sched_hash_tokens(const int32_t* token_ids, int n, int has_prefix, u
 
 int zp_sched_decode_inputs(void* sched, const int32_t* handles, int n, int32_t* input_ids,
                            int32_t* num_tokens, int32_t* query_ids, int32_t* block_tables, int table_width) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || (n > 0 && (!handles || !input_ids || !num_tokens || !query_ids || !block_tables)))
     return fail(ZP_SCHED_ERR_ARG, "zp_sched_decode_inputs: null argument");
   const Sched* s = S(sched);
@@ -674,6 +709,8 @@ static int prefill_window_rows(const Sched* s, const Seq& q, int seqlen_q, int* 
 }
 
 int zp_sched_prefill_sizes(void* sched, const int32_t* handles, int n, int32_t out[4]) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || !out || (n > 0 && !handles)) return fail(ZP_SCHED_ERR_ARG, "zp_sched_prefill_sizes: null argument");
   const Sched* s = S(sched);
   int64_t tokens = 0, rows = 0;
@@ -696,6 +733,8 @@ int zp_sched_prefill_sizes(void* sched, const int32_t* handles, int n, int32_t o
 int zp_sched_prefill_inputs(void* sched, const int32_t* handles, int n, int32_t* input_ids, int32_t* positions,
                             int32_t* slot_mapping, int32_t* cu_seqlens_q, int32_t* cu_seqlens_k,
                             int32_t* query_triples) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || (n > 0 && (!handles || !input_ids || !positions || !slot_mapping || !cu_seqlens_q || !cu_seqlens_k)))
     return fail(ZP_SCHED_ERR_ARG, "zp_sched_prefill_inputs: null argument");
   Sched* s = S(sched);
@@ -738,6 +777,8 @@ int zp_sched_prefill_inputs(void* sched, const int32_t* handles, int n, int32_t*
 }
 
 int zp_sched_compress_due(void* sched, const int32_t* handles, int n, int32_t* out_handles) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || (n > 0 && (!handles || !out_handles))) return fail(ZP_SCHED_ERR_ARG, "zp_sched_compress_due: null argument");
   const Sched* s = S(sched);
   int k = 0;
@@ -750,6 +791,8 @@ int zp_sched_compress_due(void* sched, const int32_t* handles, int n, int32_t* o
 
 int zp_sched_compress_inputs(void* sched, const int32_t* handles, int n, int32_t* tables, int table_width,
                              int32_t* targets, int target_width, int32_t* query_ids, uint8_t* compressed) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
   if (!sched || (n > 0 && (!handles || !tables || !targets || !query_ids || !compressed)))
     return fail(ZP_SCHED_ERR_ARG, "zp_sched_compress_inputs: null argument");
   const Sched* s = S(sched);

@@ -354,14 +354,12 @@ class Scheduler:
         if toks is not None and len(toks) != len(handles):
             raise ValueError("one token per sequence")
         self._epoch += 1
+        done = np.empty(max(len(handles), 1), dtype=np.int32)
         n = H.check(self._lib.zp_sched_postprocess(self._obj, _ptr(handles), len(handles),
                                                    None if toks is None else _ptr(toks),
-                                                   time.time() if now is None else now), "postprocess")
-        done = np.empty(max(n, 1), dtype=np.int32)
-        if n:
-            H.check(self._lib.zp_sched_last_finished(self._obj, _ptr(done), n), "last_finished")
-            for h in done[:n].tolist():
-                object.__setattr__(self._seqs[h], "_finished", True)
+                                                   time.time() if now is None else now, _ptr(done)), "postprocess")
+        for h in done[:n].tolist():
+            object.__setattr__(self._seqs[h], "_finished", True)
         return done[:n]
 
     def mark_prefilled(self, handles):
