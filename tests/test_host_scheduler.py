@@ -310,3 +310,35 @@ def test_calls_from_a_second_thread_are_serialised():
         t.join()
     want = GOLDEN["traces"]["prefix_cache_tight"]
     assert marks == want["marks"] and steps == want["steps"] and seen and seen[0] > 100
+
+
+def test_random_configurations_live_against_the_installed_reference():
+    """Differential run over random scheduler configurations and request streams (block pool,
+    budget, prefix cache, hybrid engine, slots, batch limits, window length, EOS, shared prefixes,
+    asynchronous compression, late arrivals): every step's state equal to the reference's."""
+    RS, RQ, RP = _reference_classes()
+    rng = random.Random(2024)
+    try:
+        for it in range(14):
+            over = dict(num_kvcache_blocks=rng.choice([24, 40, 64, 100, 200]),
+                        max_cache_blocks_per_seq=rng.choice([1, 2, 3, 4]),
+                        enable_prefix_cache=rng.random() < 0.5, enable_hybrid_engine=rng.random() < 0.4,
+                        max_concurrency=rng.choice([2, 4, 8, 32]), max_num_seqs=rng.choice([4, 8, 16, 64]),
+                        max_num_batched_tokens=rng.choice([1200, 3000, 16384]),
+                        query_cache_len=rng.choice([16, 32, 64]), eos=rng.choice([-1, 3]))
+            wl = dict(n=rng.choice([6, 12, 24]), prompt=(rng.choice([10, 100, 250]), rng.choice([300, 600, 1100])),
+                      max_tokens=(rng.choice([5, 100]), rng.choice([300, 700])), ignore_eos=rng.random() < 0.6,
+                      vocab=rng.choice([12, 5000]))
+            if rng.random() < 0.5:
+                wl["shared_prefix"] = (256, 512)
+            if rng.random() < 0.3:
+                wl["async_delay"] = rng.choice([1, 2, 5])
+            if rng.random() < 0.3:
+                wl["arrive_every"] = rng.choice([3, 20])
+            T.SCENARIOS["random"] = (over, wl)
+            want = T.run_trace(RS, RQ, RP, "random", seed=it, max_steps=1200)
+            got = T.run_trace(Scheduler, Sequence, SamplingParams, "random", seed=it, max_steps=1200)
+            first = next((i for i, (a, b) in enumerate(zip(want, got)) if a != b), None)
+            assert first is None and len(want) == len(got), (it, over, wl, first)
+    finally:
+        T.SCENARIOS.pop("random", None)
