@@ -319,7 +319,7 @@ def test_random_configurations_live_against_the_installed_reference():
     RS, RQ, RP = _reference_classes()
     rng = random.Random(2024)
     try:
-        for it in range(14):
+        for it in range(8):
             over = dict(num_kvcache_blocks=rng.choice([24, 40, 64, 100, 200]),
                         max_cache_blocks_per_seq=rng.choice([1, 2, 3, 4]),
                         enable_prefix_cache=rng.random() < 0.5, enable_hybrid_engine=rng.random() < 0.4,
