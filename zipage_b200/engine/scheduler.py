@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import ctypes as C
 import time
+from contextlib import contextmanager
 from dataclasses import dataclass
 from enum import Enum
 from itertools import count
@@ -142,8 +143,8 @@ class Sequence:
 
     def set_num_cached_tokens(self, value):
         """The one field the model runner writes (model_runner.py:387)."""
-        H.check(self._sched._lib.zp_sched_seq_set_num_cached(self._sched._obj, self._h, int(value)), "set_num_cached")
-        self._cache.pop("info", None)
+        with self._sched._mutating():
+            H.check(self._sched._lib.zp_sched_seq_set_num_cached(self._sched._obj, self._h, int(value)), "set_num_cached")
 
     def __setattr__(self, name, value):
         if name == "num_cached_tokens":
@@ -268,6 +269,17 @@ class Scheduler:
             self._lib.zp_sched_destroy(obj)
 
     # -- helpers --------------------------------------------------------------------------------
+    @contextmanager
+    def _mutating(self):
+        """Cached reads of the handles are keyed by this epoch.  It moves before AND after a call
+        that changes native state: a read that another thread starts in between stores its (old)
+        result under an epoch that is already over when the call returns."""
+        self._epoch += 1
+        try:
+            yield
+        finally:
+            self._epoch += 1
+
     def counts(self):
         out = (C.c_int32 * 8)()
         H.check(self._lib.zp_sched_counts(self._obj, out), "counts")
@@ -321,9 +333,10 @@ class Scheduler:
         # the engine looks at every scheduled sequence right away (zipage_engine.py:101-105): fetch
         # their scalar state in one call instead of one call per sequence
         info = np.empty((max(len(seqs), 1), 16), dtype=np.int32)
+        epoch = self._epoch       # taken before the read: a change meanwhile makes these entries stale
         H.check(self._lib.zp_sched_seq_info_batch(self._obj, _ptr(handles), len(seqs), _ptr(info)), "seq_info_batch")
         for q, row in zip(seqs, info.tolist()):
-            q._cache["info"] = (self._epoch, row)
+            q._cache["info"] = (epoch, row)
         return seqs, is_prefill
 
     def postprocess(self, seqs, token_ids=None):
@@ -335,17 +348,17 @@ class Scheduler:
         self.postprocess_batch(self._handles_of(seqs), toks)
 
     def preempt(self, seq: Sequence):
-        self._epoch += 1
-        H.check(self._lib.zp_sched_preempt(self._obj, seq._h), "preempt")
+        with self._mutating():
+            H.check(self._lib.zp_sched_preempt(self._obj, seq._h), "preempt")
 
     # -- array calls ----------------------------------------------------------------------------
     def schedule_batch(self):
         """-> (handles of the scheduled sequences as an int32 array, is_prefill)."""
         flag = C.c_int32(0)
-        self._epoch += 1
-        n = H.check(self._lib.zp_sched_schedule(self._obj, _ptr(self._handles), len(self._handles), C.byref(flag)),
-                    "schedule")
-        return self._handles[:n].copy(), bool(flag.value)
+        with self._mutating():
+            n = H.check(self._lib.zp_sched_schedule(self._obj, _ptr(self._handles), len(self._handles),
+                                                    C.byref(flag)), "schedule")
+            return self._handles[:n].copy(), bool(flag.value)
 
     def postprocess_batch(self, handles, token_ids=None, now=None):
         """-> the handles that finished in this call (int32 array)."""
@@ -353,19 +366,19 @@ class Scheduler:
         toks = None if token_ids is None else np.ascontiguousarray(token_ids, dtype=np.int32)
         if toks is not None and len(toks) != len(handles):
             raise ValueError("one token per sequence")
-        self._epoch += 1
         done = np.empty(max(len(handles), 1), dtype=np.int32)
-        n = H.check(self._lib.zp_sched_postprocess(self._obj, _ptr(handles), len(handles),
-                                                   None if toks is None else _ptr(toks),
-                                                   time.time() if now is None else now, _ptr(done)), "postprocess")
+        with self._mutating():
+            n = H.check(self._lib.zp_sched_postprocess(self._obj, _ptr(handles), len(handles),
+                                                       None if toks is None else _ptr(toks),
+                                                       time.time() if now is None else now, _ptr(done)), "postprocess")
         for h in done[:n].tolist():
             object.__setattr__(self._seqs[h], "_finished", True)
         return done[:n]
 
     def mark_prefilled(self, handles):
         handles = np.ascontiguousarray(handles, dtype=np.int32)
-        self._epoch += 1
-        H.check(self._lib.zp_sched_mark_prefilled(self._obj, _ptr(handles), len(handles)), "mark_prefilled")
+        with self._mutating():
+            H.check(self._lib.zp_sched_mark_prefilled(self._obj, _ptr(handles), len(handles)), "mark_prefilled")
 
     def decode_inputs(self, handles, table_width=None, out=None):
         """One decode step's host arrays: dict(input_ids, num_tokens, query_ids, block_tables
@@ -399,10 +412,10 @@ class Scheduler:
         tables = None
         width = (sizes[3] + self.block_size - 1) // self.block_size + 1
         d = self.decode_inputs(handles, table_width=width)
-        self._epoch += 1
-        got = H.check(self._lib.zp_sched_prefill_inputs(
-            self._obj, _ptr(handles), n, _ptr(out["input_ids"]), _ptr(out["positions"]), _ptr(out["slot_mapping"]),
-            _ptr(out["cu_seqlens_q"]), _ptr(out["cu_seqlens_k"]), _ptr(out["query_triples"])), "prefill_inputs")
+        with self._mutating():
+            got = H.check(self._lib.zp_sched_prefill_inputs(
+                self._obj, _ptr(handles), n, _ptr(out["input_ids"]), _ptr(out["positions"]), _ptr(out["slot_mapping"]),
+                _ptr(out["cu_seqlens_q"]), _ptr(out["cu_seqlens_k"]), _ptr(out["query_triples"])), "prefill_inputs")
         assert got == rows
         for k in ("input_ids", "positions", "slot_mapping"):
             out[k] = out[k][:tokens]
