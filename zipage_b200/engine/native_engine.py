@@ -18,6 +18,7 @@ from collections import defaultdict
 import numpy as np
 import torch
 
+from .. import _lib as L
 from ..layers.step_ops import sample
 from ..utils.context import reset_context, set_context
 from .compressor import Compressor
@@ -70,7 +71,10 @@ class NativeEngine:
         self._staged = {"input_ids": pin(max_bs), "num_tokens": pin(max_bs), "query_ids": pin(max_bs),
                         "block_tables": pin(max_bs, self.width)}
         self._views = {k: v.numpy() for k, v in self._staged.items()}
+        if sched_config.max_num_seqs > max_bs:
+            raise ValueError(f"max_num_seqs {sched_config.max_num_seqs} exceeds the {max_bs} rows of the decode graphs")
         self._tokens_host = torch.empty(max(max_bs, sched_config.max_num_seqs), dtype=torch.int64).pin_memory()
+        self._pin_err = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._temps = {}            # handle -> temperature
 
     # -- requests -------------------------------------------------------------------------------
@@ -101,7 +105,14 @@ class NativeEngine:
             seed = self.seed * 1000003 + self.step_no
             tok = self.comm.sample(logits, temps, seed=seed) if self.comm is not None else sample(logits, temps, seed=seed)
         self._tokens_host[:n].copy_(tok, non_blocking=True)
+        # a tensor-core kernel whose bounded wait ran out (prefill attention) leaves its code in the
+        # device error word: read it with the tokens, on this stream only
+        L.check(L.load().zp_device_error_async(L.ptr(self._pin_err), L.stream_ptr()), "device_error")
         torch.cuda.current_stream().synchronize()
+        if int(self._pin_err[0]) != 0:
+            code = int(self._pin_err[0])
+            L.device_error(reset=True)
+            raise L.ZipageError(f"a kernel of this step gave up on a barrier wait (code {code})")
         return self._tokens_host[:n].numpy().astype(np.int32)
 
     @torch.inference_mode()
