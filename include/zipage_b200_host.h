@@ -3,7 +3,7 @@
  * A native request scheduler and page (block) manager with the behaviour of the reference's
  * Python ones, step for step: zipage/engine/scheduler.py:10-167 (Scheduler),
  * zipage/engine/block_manager.py:26-210 (BlockManager), zipage/engine/sequence.py:14-119
- * (Sequence state).  At 2048 concurrent requests the reference spends 3 to 5 ms of Python per
+ * (Sequence state).  At 2048 concurrent requests the reference spends 1.6 to 4 ms of Python per
  * decode step in schedule() + postprocess() alone, before it builds the step's index lists
  * (zipage/engine/model_runner.py:633-675) — the same order as the GPU time of the step itself.
  * Here a step is two C calls on arrays (schedule, postprocess) and one more that fills the

@@ -326,6 +326,7 @@ class Scheduler:
         self._seqs.append(seq)
         object.__setattr__(seq, "_h", h)
         object.__setattr__(seq, "_sched", self)
+        object.__setattr__(seq, "_prompt", None)     # the tokens live in the native object from here on
 
     def schedule(self):
         handles, is_prefill = self.schedule_batch()
