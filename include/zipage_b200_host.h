@@ -114,6 +114,9 @@ uint64_t zp_sched_hash_tokens(const int32_t* token_ids, int n, int has_prefix, u
 int zp_sched_decode_inputs(void* sched, const int32_t* handles, int n, int32_t* input_ids,
                            int32_t* num_tokens, int32_t* query_ids, int32_t* block_tables, int table_width);
 
+/* The sampling temperatures of n sequences (ModelRunner.prepare_sample, model_runner.py:692-697). */
+int zp_sched_temperatures(void* sched, const int32_t* handles, int n, float* out);
+
 /* Inputs of one prefill step (ModelRunner.prepare_prefill, model_runner.py:352-422).
  * zp_sched_prefill_sizes: out[0..3] = new tokens of all n sequences, window rows they store,
  * max_seqlen_q, max_seqlen_k.  zp_sched_prefill_inputs fills input_ids / positions / slot_mapping

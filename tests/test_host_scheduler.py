@@ -114,6 +114,7 @@ def test_array_calls_agree_with_the_sequence_attributes():
                     assert c["targets"][i].tolist() == q.new_block_table
                     assert c["query_ids"][i] == q.query_id and bool(c["compressed"][i]) == q.compressed
                 s.postprocess_batch(due)
+            assert s.temperatures(handles).tolist() == [np.float32(0.6)] * len(handles)
             d = s.decode_inputs(handles, table_width=6)
             for i, h in enumerate(handles.tolist()):
                 q = s._seqs[h]

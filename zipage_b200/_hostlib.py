@@ -43,6 +43,7 @@ SIGNATURES = {
     "zp_sched_block_info": (_I, [_P, _I, _P, _P]),
     "zp_sched_hash_tokens": (C.c_uint64, [_P, _I, _I, C.c_uint64]),
     "zp_sched_decode_inputs": (_I, [_P, _P, _I, _P, _P, _P, _P, _I]),
+    "zp_sched_temperatures": (_I, [_P, _P, _I, _P]),
     "zp_sched_prefill_sizes": (_I, [_P, _P, _I, _P]),
     "zp_sched_prefill_inputs": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, _P]),
     "zp_sched_compress_due": (_I, [_P, _P, _I, _P]),

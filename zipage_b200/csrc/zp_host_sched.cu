@@ -776,6 +776,18 @@ int zp_sched_prefill_inputs(void* sched, const int32_t* handles, int n, int32_t*
   return (int)rows;
 }
 
+int zp_sched_temperatures(void* sched, const int32_t* handles, int n, float* out) {
+  std::unique_lock<std::mutex> lock_;
+  if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);
+  if (!sched || (n > 0 && (!handles || !out))) return fail(ZP_SCHED_ERR_ARG, "zp_sched_temperatures: null argument");
+  const Sched* s = S(sched);
+  for (int i = 0; i < n; ++i) {
+    if (bad_handle(s, handles[i])) return fail(ZP_SCHED_ERR_ARG, "zp_sched_temperatures: bad handle %d", handles[i]);
+    out[i] = s->seqs[handles[i]].temperature;
+  }
+  return 0;
+}
+
 int zp_sched_compress_due(void* sched, const int32_t* handles, int n, int32_t* out_handles) {
   std::unique_lock<std::mutex> lock_;
   if (sched) lock_ = std::unique_lock<std::mutex>(S(sched)->mu);

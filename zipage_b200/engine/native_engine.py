@@ -75,12 +75,12 @@ class NativeEngine:
             raise ValueError(f"max_num_seqs {sched_config.max_num_seqs} exceeds the {max_bs} rows of the decode graphs")
         self._tokens_host = torch.empty(max(max_bs, sched_config.max_num_seqs), dtype=torch.int64).pin_memory()
         self._pin_err = torch.zeros(1, dtype=torch.int32).pin_memory()
-        self._temps = {}            # handle -> temperature
+        self._temps_host = torch.empty(max(max_bs, sched_config.max_num_seqs), dtype=torch.float32).pin_memory()
+        self._temps_view = self._temps_host.numpy()
 
     # -- requests -------------------------------------------------------------------------------
     def add_request(self, seq):
         self.scheduler.add(seq)
-        self._temps[seq._h] = float(seq.temperature)
         return seq._h
 
     def is_finished(self):
@@ -101,7 +101,8 @@ class NativeEngine:
         if self.greedy:
             tok = logits.argmax(dim=-1)
         else:
-            temps = torch.tensor([self._temps[h] for h in handles.tolist()], dtype=torch.float32).to(self.device)
+            self.scheduler.temperatures(handles, out=self._temps_view)
+            temps = self._temps_host[:n].to(self.device, non_blocking=True)
             seed = self.seed * 1000003 + self.step_no
             tok = self.comm.sample(logits, temps, seed=seed) if self.comm is not None else sample(logits, temps, seed=seed)
         self._tokens_host[:n].copy_(tok, non_blocking=True)

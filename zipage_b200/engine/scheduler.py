@@ -396,6 +396,13 @@ class Scheduler:
         out["widest"] = widest
         return out
 
+    def temperatures(self, handles, out=None):
+        """float32 array of the sequences' sampling temperatures (`out`: a preallocated one)."""
+        handles = np.ascontiguousarray(handles, dtype=np.int32)
+        out = np.empty(max(len(handles), 1), dtype=np.float32) if out is None else out
+        H.check(self._lib.zp_sched_temperatures(self._obj, _ptr(handles), len(handles), _ptr(out)), "temperatures")
+        return out[:len(handles)]
+
     def prefill_inputs(self, handles):
         """One prefill step's host arrays (model_runner.py:352-422): dict(input_ids, positions,
         slot_mapping [new tokens], cu_seqlens_q, cu_seqlens_k [n + 1], query_triples [rows, 3],
