@@ -350,3 +350,52 @@ def test_random_configurations_live_against_the_installed_reference():
             assert first is None and len(want) == len(got), (it, over, wl, first)
     finally:
         T.SCENARIOS.pop("random", None)
+
+
+def test_page_accounting_invariants_hold_at_every_step():
+    """Independent of the reference: at every step of a run with a small page pool, prefix sharing
+    and preemptions, (a) free + used = all pages, (b) a page's reference count equals the number of
+    live tables (block_table, or new_block_table / block_to_release of a pending compression) that
+    hold it, (c) free pages are held by no table, (d) no table is longer than the budget + 1 pages
+    after its first compression, (e) query slots are unique among running sequences."""
+    from collections import Counter
+    rng = random.Random(77)
+    cfg = T.make_config(enable_prefix_cache=True, num_kvcache_blocks=48, max_concurrency=12, enable_hybrid_engine=True)
+    s = Scheduler(cfg)
+    shared = [rng.randrange(5000) for _ in range(512)]
+    seqs = []
+    for i in range(20):
+        toks = [rng.randrange(5000) for _ in range(rng.randint(300, 900))]
+        if i % 2 and len(toks) > 520:
+            toks[:512] = shared
+        seqs.append(Sequence(toks, SamplingParams(0.6, rng.randint(200, 800), True)))
+        s.add(seqs[-1])
+    steps = preempted = 0
+    while not s.is_finished() and steps < 4000:
+        scheduled, is_prefill = s.schedule()
+        if is_prefill:
+            s.mark_prefilled(s._handles_of(scheduled))
+        else:
+            due = [q for q in scheduled if q.require_compress]
+            if due and steps % 3 == 0:            # otherwise the compression stays pending for a while
+                s.postprocess(due)
+            scheduled = [q for q in scheduled if not q.require_compress]
+        s.postprocess(scheduled, [rng.randrange(5000) for _ in scheduled])
+        steps += 1
+        c = s.counts()
+        assert c[2] + c[3] == 48
+        held = Counter()
+        for q in seqs:
+            pending = q.require_compress
+            pages = set(q.block_table) | (set(q.new_block_table) | set(q.block_to_release) if pending else set())
+            held.update(pages)
+            if q.compressed and not pending:
+                assert len(q.block_table) <= cfg.max_cache_blocks_per_seq + 1
+        free = set(s.block_manager.free_block_ids)
+        assert len(free) == c[2] and not (free & set(held))
+        for page, n in held.items():
+            assert s.block_manager.block_state(page)[0] == n, (steps, page, n)
+        slots = [q.query_id for q in s.running if q.query_id != -1]
+        assert len(slots) == len(set(slots)) and len(slots) + len(s.free_query_ids) == 12
+        preempted += sum(1 for q in s.waiting if q.num_completion_tokens > 0)
+    assert s.is_finished() and preempted > 0
